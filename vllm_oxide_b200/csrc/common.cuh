@@ -1,0 +1,59 @@
+// Shared helpers of the kernel modules: element types, loads that widen to float, the error
+// convention of the C entry points.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and a stream, launches on
+// that stream and returns 0 or a cudaError_t value; it never allocates and never synchronises.
+// Element types of activations, weights and cache are chosen by an integer code so that one
+// library serves the 32-bit and the bfloat16 engine.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define VOB_F32 0
+#define VOB_BF16 1
+
+#define VOB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Status codes beyond cudaError_t (which stays below 1000).
+#define VOB_ERR_BAD_ARG 2001       // a size or code the kernel refuses
+#define VOB_ERR_UNSUPPORTED 2002   // a size outside what this kernel was built for
+
+static inline int vob_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return (int)e;
+}
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+    static constexpr int code = VOB_F32;
+    __device__ static inline float load(const float* p) { return *p; }
+    __device__ static inline void store(float* p, float v) { *p = v; }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+    static constexpr int code = VOB_BF16;
+    __device__ static inline float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ static inline void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ inline float ld_f(const T* p) { return ElemTraits<T>::load(p); }
+template <typename T> __device__ inline void st_f(T* p, float v) { ElemTraits<T>::store(p, v); }
+
+__device__ inline float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ inline float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Dispatch on an element code: the statement given uses the type ElemT.
+#define VOB_DISPATCH_ELEM(code, ...)                                   \
+    do {                                                               \
+        if ((code) == VOB_F32) { using ElemT = float; __VA_ARGS__; }       \
+        else if ((code) == VOB_BF16) { using ElemT = __nv_bfloat16; __VA_ARGS__; } \
+        else return VOB_ERR_BAD_ARG;                                   \
+    } while (0)

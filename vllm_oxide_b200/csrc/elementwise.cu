@@ -1,0 +1,227 @@
+// Memory-bound row kernels of a decoder step: embedding gather, residual add + RMSNorm,
+// rotary positions + cache write, SwiGLU.
+//
+// Conventions: the residual stream is float32 in both engines; `act` tensors (inputs of the
+// matrix products, q/k/v, the cache) are float32 or bfloat16 by an element code. All
+// reductions, rotation angles and the activation are float32. One block works on one row, so a
+// row's result does not depend on what else is in the batch.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// Embedding gather: out[t, :] = table[tokens[t], :]   (float32 out)
+// Reference op: crates/engine/src/backend/cpu/mod.rs:172-180.
+// Launch: one block per token, 256 threads. Bound: memory (2 * h * 4 bytes per token).
+// A token outside [0, vocab) writes zeros and raises *err_flag (the host checks ids first).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int h, int vocab, int* err_flag) {
+    int t = blockIdx.x;
+    int tok = tokens[t];
+    bool ok = tok >= 0 && tok < vocab;
+    if (!ok && threadIdx.x == 0 && err_flag) atomicExch(err_flag, 1);
+    const T* src = table + (size_t)(ok ? tok : 0) * h;
+    float* dst = out + (size_t)t * h;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = ok ? ld_f(src + i) : 0.f;
+}
+
+VOB_EXPORT int vob_embed(const void* table, int table_code, const int* tokens, float* out, int T, int h,
+                         int vocab, int* err_flag, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (h <= 0 || vocab <= 0) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(table_code, embed_kernel<ElemT><<<T, 256, 0, stream>>>((const ElemT*)table, tokens, out, h, vocab, err_flag));
+    return vob_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add + RMSNorm:
+//   x = resid[src] (+ delta[src]);  if no row list: resid[src] = x  (the residual sum, float32)
+//   out[r] = w * (x * 1/sqrt(mean(x^2) + eps))
+// Reference ops: add (crates/engine/src/backend/cpu/mod.rs:351-358) followed by rmsnorm
+// (:182-197); the weight multiplies last, as there. With a row list (`rows`, R entries) only
+// those rows are normalised (gather_rows + rmsnorm, crates/engine/src/model.rs:335-342) and
+// the residual is left untouched.
+// Launch: one block per output row, 256 threads, h floats of shared memory; the row is read
+// once. Sum of squares: per-thread strided partial sums, then a fixed tree, so a row's value is
+// the same in every batch. Bound: memory.
+// ---------------------------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const float* __restrict__ weight, const int* __restrict__ rows,
+                                   TO* __restrict__ out, int h, float eps) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    float* x = resid + (size_t)src * h;
+    const TD* d = delta ? delta + (size_t)src * h : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        float v = x[i];
+        if (d) {
+            v += ld_f(d + i);
+            if (!rows) x[i] = v;
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) red[wid] = ss;
+    __syncthreads();
+    if (wid == 0) {
+        float v = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) red[0] = v;
+    }
+    __syncthreads();
+    float mean_square = red[0] / (float)h;
+    float inv = 1.0f / sqrtf(mean_square + eps);
+    TO* o = out + (size_t)r * h;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) st_f(o + i, weight[i] * (row[i] * inv));
+}
+
+VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, const float* weight,
+                               const int* rows, void* out, int out_code, int R, int h, float eps,
+                               cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (h <= 0) return VOB_ERR_BAD_ARG;
+    size_t smem = (size_t)h * sizeof(float);
+    if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
+#define LAUNCH(TD, TO) add_rmsnorm_kernel<TD, TO><<<R, 256, smem, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
+    if (out_code == VOB_F32) {
+        if (delta_code == VOB_F32) LAUNCH(float, float); else if (delta_code == VOB_BF16) LAUNCH(__nv_bfloat16, float); else return VOB_ERR_BAD_ARG;
+    } else if (out_code == VOB_BF16) {
+        if (delta_code == VOB_F32) LAUNCH(float, __nv_bfloat16); else if (delta_code == VOB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else return VOB_ERR_BAD_ARG;
+    } else return VOB_ERR_BAD_ARG;
+#undef LAUNCH
+    return vob_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add alone: resid[t, :] += delta[t, :]  (float32 sum). Used where no norm follows.
+// ---------------------------------------------------------------------------------------------
+template <typename TD>
+__global__ void add_residual_kernel(float* __restrict__ resid, const TD* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += ld_f(delta + i);
+}
+
+VOB_EXPORT int vob_add_residual(float* resid, const void* delta, int delta_code, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    VOB_DISPATCH_ELEM(delta_code, add_residual_kernel<ElemT><<<blocks, 256, 0, stream>>>(resid, (const ElemT*)delta, (size_t)n));
+    return vob_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rotary positions on q and k, and the cache write of k and v, in one pass over a token's
+// q/k/v rows:
+//   theta_i = float(pos) * inv_freq[i]         (float32 product; cosf/sinf precise versions)
+//   x1' = x1*cos - x2*sin ; x2' = x2*cos + x1*sin   with x1 = x[:hd/2], x2 = x[hd/2:] per head
+//   K[page, kvh, off, :] = k'[kvh],  V[page, kvh, off, :] = v[kvh],  slot = page*page_size+off
+// Reference ops: rope (crates/engine/src/backend/cpu/rope.rs:64-99) on q and k, then write_kv
+// (crates/engine/src/backend/cpu/mod.rs:257-285), in that order before attention
+// (crates/engine/src/model.rs:307-311). q is rotated in place. A page holds
+// [kv_heads][page_size][head_dim], so one (page, head) is one contiguous tile.
+// `slots` may be null (rotate only); a negative slot skips that token's write.
+// `inv_freq` may be null (no rotation: the part has no position encoding).
+// Launch: one block per token, 128 threads, head_dim floats of shared memory for cos|sin.
+// Bound: memory.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+                                     const T* __restrict__ v, long long v_stride,
+                                     const int* __restrict__ positions, const int* __restrict__ slots,
+                                     const float* __restrict__ inv_freq, T* __restrict__ kcache,
+                                     T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
+    extern __shared__ float cs[];   // cos[half] | sin[half]
+    int t = blockIdx.x;
+    int half = hd >> 1;
+    if (inv_freq) {
+        float p = (float)positions[t];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float theta = p * inv_freq[i];
+            cs[i] = cosf(theta);
+            cs[half + i] = sinf(theta);
+        }
+    }
+    __syncthreads();
+    int slot = slots ? slots[t] : -1;
+    T* qr = q + (size_t)t * q_stride;
+    T* kr = k ? k + (size_t)t * k_stride : nullptr;
+    const T* vr = v ? v + (size_t)t * v_stride : nullptr;
+    // q heads
+    for (int e = threadIdx.x; e < H * half; e += blockDim.x) {
+        int head = e / half, i = e - head * half;
+        T* x = qr + head * hd;
+        if (inv_freq) {
+            float a = ld_f(x + i), b = ld_f(x + half + i);
+            float c = cs[i], s = cs[half + i];
+            st_f(x + i, a * c - b * s);
+            st_f(x + half + i, b * c + a * s);
+        }
+    }
+    if (!kr) return;
+    size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0;
+    int off = slot >= 0 ? slot % page_size : 0;
+    for (int e = threadIdx.x; e < KV * half; e += blockDim.x) {
+        int head = e / half, i = e - head * half;
+        T* x = kr + head * hd;
+        float a = ld_f(x + i), b = ld_f(x + half + i);
+        float ra = a, rb = b;
+        if (inv_freq) {
+            float c = cs[i], s = cs[half + i];
+            ra = a * c - b * s;
+            rb = b * c + a * s;
+            st_f(x + i, ra);
+            st_f(x + half + i, rb);
+        }
+        if (slot >= 0) {
+            size_t base = ((page * KV + head) * page_size + off) * (size_t)hd;
+            st_f(kcache + base + i, ra);
+            st_f(kcache + base + half + i, rb);
+            vcache[base + i] = vr[head * hd + i];
+            vcache[base + half + i] = vr[head * hd + half + i];
+        }
+    }
+}
+
+VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long k_stride, const void* v,
+                                 long long v_stride, const int* positions, const int* slots,
+                                 const float* inv_freq, void* kcache, void* vcache, int code, int T, int H,
+                                 int KV, int hd, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || (hd & 1) || H <= 0 || KV < 0 || page_size <= 0) return VOB_ERR_BAD_ARG;
+    if (k && slots && (!kcache || !vcache || !v)) return VOB_ERR_BAD_ARG;
+    size_t smem = (size_t)hd * sizeof(float);
+    VOB_DISPATCH_ELEM(code, rope_kv_write_kernel<ElemT><<<T, 128, smem, stream>>>(
+        (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
+        (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
+    return vob_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[t, j] = gate / (1 + exp(-gate)) * up, gate = in[t, j], up = in[t, I + j]
+// (divide, then multiply by up, as crates/engine/src/backend/cpu/mod.rs:341-349). The input is
+// the output of one fused [gate; up] matrix product, row stride `in_stride` elements.
+// Launch: grid (T, ceil(I/256)). Bound: memory.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
+    int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= I) return;
+    const T* r = in + (size_t)blockIdx.x * in_stride;
+    float g = ld_f(r + j), u = ld_f(r + I + j);
+    st_f(out + (size_t)blockIdx.x * I + j, g / (1.0f + expf(-g)) * u);
+}
+
+VOB_EXPORT int vob_swiglu(const void* in, long long in_stride, void* out, int code, int T, int I,
+                          cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (I <= 0) return VOB_ERR_BAD_ARG;
+    if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
+    dim3 grid(T, (I + 255) / 256);
+    VOB_DISPATCH_ELEM(code, swiglu_kernel<ElemT><<<grid, 256, 0, stream>>>((const ElemT*)in, in_stride, (ElemT*)out, I));
+    return vob_launch_status();
+}

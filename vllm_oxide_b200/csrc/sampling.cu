@@ -1,0 +1,123 @@
+// Picking the next token from float32 logits [R, V]: greedy, or temperature sampling by the
+// Gumbel-max rule, one pick per row, on the device.
+//
+//   temperature == 0:  first index of the maximum (strictly-greater comparison keeps the first,
+//                      crates/engine/src/backend/cpu/mod.rs:370-388); a NaN anywhere in the row
+//                      raises the row's flag, which the host turns into an error (:377-379).
+//   temperature  > 0:  argmax_i(logit_i / temperature + g_i),  g_i = -log(-log(u_i)),
+//                      u_i in (0,1) from a counter-based hash of (seed, generated index, i):
+//                      a draw from softmax(logits / temperature) that depends on nothing but the
+//                      request's own seed and progress (the reference samples greedily only;
+//                      this rule is this engine's own).
+// Two launches: `pick_partial` gives every (row, slice of the vocabulary) block a best
+// (value, index) pair in scratch memory, `pick_final` reduces a row's pairs. The scratch is
+// [R, splits] pairs supplied by the caller. Bound: memory (R * V * 4 bytes read once).
+#include "common.cuh"
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    return x;
+}
+
+struct Best { float v; int i; };
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+    // larger value wins; equal values: smaller index wins
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ __forceinline__ Best block_best(Best b, Best* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, other);
+    }
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) sh[wid] = b;
+    __syncthreads();
+    if (wid == 0) {
+        Best x = lane < (blockDim.x >> 5) ? sh[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other;
+            other.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+            other.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+            x = better(x, other);
+        }
+        b = x;
+    }
+    return b;   // valid in thread 0
+}
+
+__global__ void __launch_bounds__(256)
+pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
+                    const uint32_t* __restrict__ seeds, const int* __restrict__ steps, int splits,
+                    float* __restrict__ part_val, int* __restrict__ part_idx, int* __restrict__ nan_flags) {
+    __shared__ Best sh[32];
+    int r = blockIdx.y, sp = blockIdx.x;
+    int per = (V + splits - 1) / splits;
+    int lo = sp * per, hi = min(V, lo + per);
+    const float* row = logits + (size_t)r * ld;
+    float tau = temperature ? temperature[r] : 0.f;
+    uint32_t ctr = 0;
+    if (tau > 0.f) {
+        uint32_t key = mix32(seeds[2 * r] ^ mix32(seeds[2 * r + 1] + 0x85EBCA6Bu));
+        ctr = mix32(key ^ mix32((uint32_t)steps[r] + 0x9E3779B9u));
+    }
+    Best b{-INFINITY, 0x7fffffff};
+    bool saw_nan = false;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float x = row[i];
+        if (x != x) saw_nan = true;
+        float v = x;
+        if (tau > 0.f) {
+            uint32_t h = mix32(ctr ^ (uint32_t)i);
+            float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+            v = x / tau + (-logf(-logf(u)));
+        }
+        if (v > b.v) { b.v = v; b.i = i; }      // ascending i per thread: first maximum kept
+    }
+    if (saw_nan) atomicExch(nan_flags + r, 1);
+    b = block_best(b, sh);
+    if (threadIdx.x == 0) {
+        part_val[(size_t)r * splits + sp] = b.v;
+        part_idx[(size_t)r * splits + sp] = b.i;
+    }
+}
+
+__global__ void pick_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                  int splits, int V, int* __restrict__ out) {
+    __shared__ Best sh[32];
+    int r = blockIdx.x;
+    Best b{-INFINITY, 0x7fffffff};
+    for (int s = threadIdx.x; s < splits; s += blockDim.x)
+        b = better(b, Best{part_val[(size_t)r * splits + s], part_idx[(size_t)r * splits + s]});
+    b = block_best(b, sh);
+    // all values -inf or NaN: fall back to index 0, as a scan that never finds a greater value does
+    if (threadIdx.x == 0) out[r] = (b.i >= 0 && b.i < V) ? b.i : 0;
+}
+
+// Scratch needed: R * splits floats and R * splits ints. `splits` is chosen by the caller
+// (vob_pick_splits gives the default for a vocabulary size).
+VOB_EXPORT int vob_pick_splits(int V) {
+    int s = (V + 4095) / 4096;
+    return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+
+VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, const float* temperature,
+                               const uint32_t* seeds, const int* steps, int splits, float* part_val,
+                               int* part_idx, int* nan_flags, int* out, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || splits <= 0 || ld < V || R > 65535) return VOB_ERR_BAD_ARG;
+    if (temperature && (!seeds || !steps)) return VOB_ERR_BAD_ARG;
+    dim3 grid(splits, R);
+    pick_partial_kernel<<<grid, 256, 0, stream>>>(logits, ld, V, temperature, seeds, steps, splits, part_val,
+                                                  part_idx, nan_flags);
+    int e = vob_launch_status();
+    if (e) return e;
+    pick_final_kernel<<<R, 64, 0, stream>>>(part_val, part_idx, splits, V, out);
+    return vob_launch_status();
+}

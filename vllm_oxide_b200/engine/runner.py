@@ -1,0 +1,227 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+The reference has two entry points, prefill and decode, and a step is all one or all the other
+(crates/engine/src/model.rs:221-243); its attention, though, is one function fed the same
+per-row arrays in both (crates/engine/src/backend/cpu/mod.rs:310,337), and a decode row is a
+portion of length one. So here there is ONE `step`: any mix of portions of prompts and single
+decoded tokens runs as one batch, reads older keys from the cache, writes its own, and returns
+the logits at the wanted places together with a token picked from each.
+
+Order inside a layer is the reference's (crates/engine/src/model.rs:302-332): norm, q/k/v,
+rotary, cache write, attention, output projection + residual, norm, gate/up, SwiGLU, down +
+residual; then the final norm and the head on the wanted rows only (:335-344).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..cache.pools import CachePools
+from ..config import EngineConfig, architecture_for, read_config_json
+from ..csrc.build import runtime_module
+from ..errors import CapacityError, KernelError, NaNError, ShapeError
+from ..parts.base import ModelSpec, StepContext, Workspace
+from ..weights import load_safetensors_weights, weights_from_tensors
+
+
+@dataclass
+class StepResult:
+    sampled: torch.Tensor                 # int32 [R] on the device: the token picked at each wanted row
+    logits: Optional[torch.Tensor]        # float32 [R, vocab] where the caller asked for them
+    num_logit_rows: int
+
+    def tokens(self) -> List[int]:
+        """The picked tokens on the host (this is the step's one device-to-host read)."""
+        return self.sampled[:self.num_logit_rows].tolist()
+
+
+def _require_cuda(device: str) -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available; this engine has no CPU path")
+    if not str(device).startswith("cuda"):
+        raise KernelError(f"device {device!r}: this engine runs on a CUDA device only")
+
+
+class ModelRunner:
+    """Owns the model's parts, the cache and the step's device buffers; `step` is the only way
+    tokens go through the model (generation, the scheduler's loop and trace replay all use it)."""
+
+    def __init__(self, config, tensors_or_dir, engine: EngineConfig, arch=None):
+        _require_cuda(engine.device)
+        from ..models import BuildContext      # registers the built-in architecture
+        self.rt = runtime_module()
+        self.engine = engine
+        self.config = config
+        self.device = engine.device
+        self.dtype = engine.dtype
+        torch.cuda.set_device(self.device)
+        arch = arch or architecture_for(config.to_dict())
+        manifest = arch.manifest(config)
+        if isinstance(tensors_or_dir, (str, os.PathLike)):
+            weights = load_safetensors_weights(str(tensors_or_dir), manifest, device=self.device)
+        else:
+            weights = weights_from_tensors(tensors_or_dir, manifest)
+        kernels.preload()
+        self.spec: ModelSpec = arch.build(config, weights, BuildContext(dtype=self.dtype, device=self.device))
+        del weights
+        # As in the reference, the longest sequence is the engine's limit, not config.json's
+        # max_position_embeddings (crates/engine/src/backend/cpu/mod.rs:49-54): rotation angles are
+        # computed from the position itself, so no table length binds them.
+        self.max_model_len = engine.max_model_len
+        self.pools = CachePools(self.spec, engine.block_size, engine.max_seqs, self.dtype, self.device,
+                                num_pages=engine.num_pages, pool_bytes=engine.kv_pool_bytes)
+        self.manager = self.pools.manager
+        self.max_pages = -(-self.max_model_len // engine.block_size)
+        self.rows_cap = engine.max_batch_tokens
+        self.seqs_cap = engine.max_seqs
+        self.logits_cap = engine.max_batch_tokens
+        self.logit_chunk = min(self.logits_cap, max(engine.max_seqs, 64))
+        G = self.pools.num_groups
+        self.layout = self.rt.step_layout(self.rows_cap, self.seqs_cap, self.logits_cap, G, self.max_pages)
+        total = self.layout["total"]
+        self.step_host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.step_host_np = self.step_host.numpy()
+        self.step_dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        # workspace: residual + two pending buffers + the largest block + the head's chunk
+        V = self.spec.vocab_size
+        self.workspace_bytes = self.workspace_formula(self.rows_cap)
+        self.workspace = Workspace(self.workspace_bytes, self.device)
+        splits = kernels.pick_splits(V)
+        self.pick_val = torch.empty(self.logit_chunk * splits, dtype=torch.float32, device=self.device)
+        self.pick_idx = torch.empty(self.logit_chunk * splits, dtype=torch.int32, device=self.device)
+        self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
+        self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ sizes
+    def workspace_formula(self, rows: int) -> int:
+        """Peak bytes of a step of `rows` tokens, read off the scopes of `_forward` (the
+        reference's arena formula, crates/engine/src/model.rs:68-90, for this arrangement)."""
+        es = 2 if self.dtype == torch.bfloat16 else 4
+        h, V = self.spec.hidden_size, self.spec.vocab_size
+        pad = 256
+        resid = rows * h * 4 + pad
+        pending = 2 * (rows * h * es + pad)
+        block = max((b.workspace_bytes(rows, h, es) for b in self.spec.blocks), default=0) + pad
+        head = self.logit_chunk * (h * es + V * 4) + 2 * pad
+        return resid + pending + max(block, head)
+
+    @classmethod
+    def from_dir(cls, model_dir: str, engine: EngineConfig) -> "ModelRunner":
+        from .. import models  # noqa: F401  (registers architectures)
+        d = read_config_json(model_dir)
+        arch = architecture_for(d, os.path.join(model_dir, "config.json"))
+        config = arch.config_cls.from_dict(d, os.path.join(model_dir, "config.json"))
+        return cls(config, model_dir, engine, arch)
+
+    # ------------------------------------------------------------------ the step
+    def context(self, rows: int, seqs: int, arrays=None) -> StepContext:
+        L, d = self.layout, self.step_dev
+        mp = self.max_pages
+
+        def vec(key, n):
+            o = L[key]
+            return d[o:o + n]
+        G = self.pools.num_groups
+        return StepContext(
+            rows=rows, seqs=seqs, dtype=self.dtype,
+            tokens=vec("tokens", rows), positions=vec("positions", rows), row_seq=vec("row_seq", rows),
+            seq_starts=vec("seq_starts", seqs + 1), context_lens=vec("context_lens", seqs),
+            seq_lens=vec("seq_lens", seqs), state_slots=vec("state_slots", seqs),
+            logit_rows=vec("logit_rows", self.logits_cap),
+            slot_mapping=[d[L["slot_mapping"][g]:L["slot_mapping"][g] + rows] for g in range(G)],
+            block_tables=[d[L["block_tables"][g]:L["block_tables"][g] + self.seqs_cap * mp].view(self.seqs_cap, mp)
+                          for g in range(G)],
+            workspace=self.workspace,
+            max_new=arrays.max_new if arrays is not None else 0,
+            max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays)
+
+    def upload(self, arrays) -> None:
+        """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
+        n = arrays.total
+        arrays.copy_into(self.step_host_np)
+        self.step_dev[:n].copy_(self.step_host[:n], non_blocking=True)
+
+    def build_arrays(self, entries):
+        """Lay out a batch given as runtime StepEntry objects (pages must be reserved already)."""
+        return self.rt.build_step(self.manager, entries, self.rows_cap, self.seqs_cap, self.logits_cap,
+                                  self.max_pages, self.spec.vocab_size)
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        """Embedding and every scheduled block; returns (residual, pending): the float32 residual
+        and the last block's output that is still to be added to it."""
+        spec, ws = self.spec, ctx.workspace
+        resid = spec.embedding.forward(ctx)
+        es_shape = (ctx.rows, spec.hidden_size)
+        pend = [ctx.alloc(es_shape), ctx.alloc(es_shape)]
+        pending = None
+        for i, call in enumerate(spec.schedule):
+            block = spec.blocks[call.layer]
+            cache = self.pools.layer_cache(call.cache, call.write)
+            state = self.pools.state.get(i)
+            pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1])
+        return resid, pending
+
+    def _head(self, resid, pending, ctx: StepContext, num_logit_rows: int, logits_out: Optional[torch.Tensor]) -> None:
+        """Final norm and output head on the wanted rows, in chunks; a token is picked from every
+        row; logits are copied out only where the caller gave a place for them."""
+        spec, L = self.spec, self.layout
+        d = self.step_dev
+        V = spec.vocab_size
+        for c0 in range(0, num_logit_rows, self.logit_chunk):
+            n = min(self.logit_chunk, num_logit_rows - c0)
+            with ctx.workspace.scope():
+                rows = d[L["logit_rows"] + c0:L["logit_rows"] + c0 + n]
+                normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n)
+                logits = ctx.workspace.alloc((n, V), torch.float32)
+                spec.lm_head.forward(normed, logits)
+                temp = d[L["temperature"] + c0:L["temperature"] + c0 + n].view(torch.float32)
+                seeds = d[L["seeds"] + 2 * c0:L["seeds"] + 2 * (c0 + n)]
+                steps = d[L["sample_steps"] + c0:L["sample_steps"] + c0 + n]
+                kernels.pick_tokens(logits, self.sampled[c0:c0 + n], self.nan_flags[c0:c0 + n], self.pick_val,
+                                    self.pick_idx, temp, seeds, steps)
+                if logits_out is not None:
+                    logits_out[c0:c0 + n].copy_(logits, non_blocking=logits_out.is_cuda)
+
+    def step(self, arrays, logits_out: Optional[torch.Tensor] = None, check_nan: bool = False) -> StepResult:
+        """Run one batch. `arrays` comes from `build_arrays` or the scheduler. `logits_out`
+        (float32 [>=R, vocab], on the device or the host) receives the logits of the wanted rows."""
+        T, S, R = arrays.rows, arrays.seqs, arrays.logit_count
+        if arrays.max_seq_len > self.max_model_len:
+            raise CapacityError("sequence length", int(arrays.max_seq_len), self.max_model_len)
+        if logits_out is not None and (logits_out.dim() != 2 or logits_out.shape[0] < R
+                                       or logits_out.shape[1] != self.spec.vocab_size or logits_out.dtype != torch.float32):
+            raise ShapeError("step", f"logits_out must be float32 [>={R}, {self.spec.vocab_size}]")
+        self.upload(arrays)
+        self.workspace.reset()
+        ctx = self.context(T, S, arrays)
+        if check_nan:
+            self.nan_flags.zero_()
+        resid, pending = self._forward(ctx)
+        if R:
+            self._head(resid, pending, ctx, R, logits_out)
+        self.steps_run += 1
+        if check_nan and R and bool(self.nan_flags[:R].any().item()):
+            raise NaNError("pick_tokens")
+        if self.spec.embedding.err_flag is not None and check_nan and bool(self.spec.embedding.err_flag.item()):
+            raise ShapeError("embed", "a token id outside the vocabulary reached the device")
+        return StepResult(self.sampled, logits_out, R)
+
+    # ------------------------------------------------------------------ bookkeeping helpers
+    def admit(self, request_id: int) -> int:
+        """Take a state slot for a request and zero its state. -1 when no slot is free."""
+        slot = self.manager.admit(request_id)
+        if slot >= 0:
+            self.pools.reset_slot(slot)
+        return slot
+
+    def decode_read_bytes(self, context_lens) -> int:
+        """Bytes a decode step of these contexts must read: every weight once, plus the cache of
+        the live requests."""
+        return self.spec.weight_bytes + sum(int(c) for c in context_lens) * self.pools.bytes_per_token()

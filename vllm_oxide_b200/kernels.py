@@ -1,0 +1,325 @@
+"""Launch wrappers of the CUDA kernels: every shape, dtype, device and alignment is checked
+here, on the host, before a pointer reaches a kernel (the reference's rule for its launch
+wrappers, CLAUDE.md:79, and the checks of crates/engine/src/arena/ops.rs:30-268).
+
+There is no CPU path and no fallback: a tensor that is not on a CUDA device, or a kernel
+library that cannot be built or loaded, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_cuda_module
+from .errors import KernelError, ShapeError
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_longlong
+_F = ctypes.c_float
+
+_STATUS = {2001: "bad argument", 2002: "size not supported by this kernel"}
+
+
+def _code(t: torch.Tensor, op: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise ShapeError(op, f"dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(op: str, *tensors: Optional[torch.Tensor]) -> None:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError(f"{op}: tensor on {t.device}; the kernels run on a CUDA device only "
+                              "(there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ShapeError(op, f"tensors on different devices: {dev} and {t.device}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return _P(t.data_ptr()) if t is not None else _P(0)
+
+
+def _stream() -> _P:
+    return _P(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, op: str) -> None:
+    if status != 0:
+        what = _STATUS.get(status, f"CUDA error {status}")
+        raise KernelError(f"{op}: launch failed: {what}")
+
+
+def _rows_2d(t: torch.Tensor, op: str, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ShapeError(op, f"{name} must be 2-D with unit inner stride, got shape {list(t.shape)} "
+                             f"strides {list(t.stride())}")
+
+
+def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
+    if t.dtype != torch.int32 or t.dim() != 1 or t.numel() < n or not t.is_contiguous():
+        raise ShapeError(op, f"{name} must be a contiguous int32 vector of at least {n}, got "
+                             f"{t.dtype} {list(t.shape)}")
+
+
+_fn_cache = {}
+
+
+def _fn(module: str, name: str, argtypes):
+    key = (module, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = load_cuda_module(module)
+        try:
+            f = getattr(lib, name)
+        except AttributeError:
+            raise KernelError(f"kernel library '{module}' has no entry point {name}") from None
+        f.argtypes = argtypes
+        f.restype = _I
+        _fn_cache[key] = f
+    return f
+
+
+def preload(modules=("elementwise", "gemm_f32", "attention", "sampling")) -> None:
+    """Build and load kernel modules now (so that compile time is spent at start-up)."""
+    for m in modules:
+        load_cuda_module(m)
+
+
+# ------------------------------------------------------------------------------------ embedding
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] as float32; `tokens` int32 [T], `out` float32 [T, h]."""
+    op = "embed"
+    _cuda(op, table, tokens, out, err_flag)
+    T = out.shape[0]
+    if table.dim() != 2 or not table.is_contiguous():
+        raise ShapeError(op, f"table must be contiguous [vocab, h], got {list(table.shape)}")
+    _int32_vec(tokens, T, op, "tokens")
+    if out.dtype != torch.float32 or out.dim() != 2 or out.shape[1] != table.shape[1] or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous float32 [T, {table.shape[1]}], got {out.dtype} {list(out.shape)}")
+    f = _fn("elementwise", "vob_embed", [_P, _I, _P, _P, _I, _I, _I, _P, _P])
+    _check(f(_ptr(table), _code(table, op), _ptr(tokens), _ptr(out), T, table.shape[1], table.shape[0],
+             _ptr(err_flag), _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ norm
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """resid (+= delta); out = weight * (x / sqrt(mean(x^2) + eps)). With `rows` (int32 [R]) only
+    those rows are normalised into out [R, h] and resid is left as it is."""
+    op = "add_rmsnorm"
+    _cuda(op, resid, delta, weight, out, rows)
+    if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous():
+        raise ShapeError(op, f"the residual must be contiguous float32 [T, h], got {resid.dtype} {list(resid.shape)}")
+    T, h = resid.shape
+    if weight.dtype != torch.float32 or weight.shape != (h,) or not weight.is_contiguous():
+        raise ShapeError(op, f"weight must be float32 [{h}], got {weight.dtype} {list(weight.shape)}")
+    if delta is not None and (delta.shape != resid.shape or not delta.is_contiguous()):
+        raise ShapeError(op, f"delta must be contiguous {list(resid.shape)}, got {list(delta.shape)}")
+    R = T
+    if rows is not None:
+        R = rows.numel()
+        _int32_vec(rows, R, op, "rows")
+    if out.dim() != 2 or out.shape[0] < R or out.shape[1] != h or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous [>={R}, {h}], got {list(out.shape)}")
+    if h * 4 > 48 * 1024:
+        raise ShapeError(op, f"width {h} is beyond this kernel's limit of {48 * 1024 // 4}")
+    f = _fn("elementwise", "vob_add_rmsnorm", [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P])
+    _check(f(_ptr(resid), _ptr(delta), _code(delta, op) if delta is not None else 0, _ptr(weight), _ptr(rows),
+             _ptr(out), _code(out, op), R, h, float(eps), _stream()), op)
+
+
+def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    """resid += delta in float32."""
+    op = "add_residual"
+    _cuda(op, resid, delta)
+    if resid.dtype != torch.float32 or not resid.is_contiguous() or delta.shape != resid.shape or not delta.is_contiguous():
+        raise ShapeError(op, f"need contiguous float32 residual and a delta of the same shape, got "
+                             f"{resid.dtype} {list(resid.shape)} and {list(delta.shape)}")
+    f = _fn("elementwise", "vob_add_residual", [_P, _P, _I, _L, _P])
+    _check(f(_ptr(resid), _ptr(delta), _code(delta, op), resid.numel(), _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ rope + cache write
+def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], positions: torch.Tensor,
+                  slots: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                  kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                  num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Rotate q and k in place (float32 angles position * inv_freq) and write k, v to their cache
+    slots. q [T, H*hd], k and v [T, KV*hd] may be column slices of one wider tensor. kcache and
+    vcache are one layer's pages [num_pages, KV, page_size, hd]."""
+    op = "rope_kv_write"
+    _cuda(op, q, k, v, positions, slots, inv_freq, kcache, vcache)
+    _rows_2d(q, op, "q")
+    T = q.shape[0]
+    if q.shape[1] != num_heads * head_dim:
+        raise ShapeError(op, f"q has {q.shape[1]} columns, expected heads*head_dim = {num_heads * head_dim}")
+    if head_dim % 2 != 0:
+        raise ShapeError(op, f"head_dim {head_dim} must be even")
+    _int32_vec(positions, T, op, "positions")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape != (head_dim // 2,) or not inv_freq.is_contiguous()):
+        raise ShapeError(op, f"inv_freq must be float32 [{head_dim // 2}], got {inv_freq.dtype} {list(inv_freq.shape)}")
+    page_size = 1
+    if k is not None:
+        _rows_2d(k, op, "k")
+        if k.shape != (T, num_kv_heads * head_dim) or k.dtype != q.dtype:
+            raise ShapeError(op, f"k must be {q.dtype} [{T}, {num_kv_heads * head_dim}], got {k.dtype} {list(k.shape)}")
+        if slots is not None:
+            _int32_vec(slots, T, op, "slots")
+            if v is None or kcache is None or vcache is None:
+                raise ShapeError(op, "a cache write needs v, kcache and vcache")
+            _rows_2d(v, op, "v")
+            if v.shape != k.shape or v.dtype != q.dtype:
+                raise ShapeError(op, f"v must match k, got {v.dtype} {list(v.shape)}")
+            for name, c in (("kcache", kcache), ("vcache", vcache)):
+                if c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous() or c.dtype != q.dtype:
+                    raise ShapeError(op, f"{name} must be contiguous {q.dtype} [pages, {num_kv_heads}, page_size, "
+                                         f"{head_dim}], got {c.dtype} {list(c.shape)}")
+            if kcache.shape != vcache.shape:
+                raise ShapeError(op, "kcache and vcache differ in shape")
+            page_size = kcache.shape[2]
+    f = _fn("elementwise", "vob_rope_kv_write", [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
+             v.stride(0) if v is not None else 0, _ptr(positions), _ptr(slots), _ptr(inv_freq), _ptr(kcache),
+             _ptr(vcache), _code(q, op), T, num_heads, num_kv_heads if k is not None else 0, head_dim, page_size,
+             _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ swiglu
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
+    op = "swiglu"
+    _cuda(op, gate_up, out)
+    _rows_2d(gate_up, op, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2 != 0:
+        raise ShapeError(op, f"gate_up has an odd number of columns: {two_i}")
+    if out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous {gate_up.dtype} [{T}, {two_i // 2}], got {out.dtype} {list(out.shape)}")
+    f = _fn("elementwise", "vob_swiglu", [_P, _L, _P, _I, _I, _I, _P])
+    _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out, op), T, two_i // 2, _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ matrix products
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA chains in k order; no tensor cores)."""
+    op = "gemm_f32"
+    _cuda(op, a, w, out)
+    for name, t in (("a", a), ("w", w), ("out", out)):
+        _rows_2d(t, op, name)
+        if t.dtype != torch.float32:
+            raise ShapeError(op, f"{name} must be float32, got {t.dtype}")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ShapeError(op, f"a has {K} columns, w has {w.shape[1]}")
+    if out.shape != (M, N):
+        raise ShapeError(op, f"out must be [{M}, {N}], got {list(out.shape)}")
+    f = _fn("gemm_f32", "vob_gemm_f32", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()), op)
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a @ w^T. float32 operands: the true 32-bit kernel. bfloat16 operands: the library
+    matrix product (cuBLAS through torch, float32 accumulation), as the reference plans for its
+    own matrix products (CLAUDE.md:107); `out` may be bfloat16 or float32."""
+    op = "linear"
+    if a.dtype == torch.float32:
+        gemm_f32(a, w, out)
+        return
+    _cuda(op, a, w, out)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ShapeError(op, f"operands must both be float32 or both bfloat16, got {a.dtype} and {w.dtype}")
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or out.shape != (a.shape[0], w.shape[0]):
+        raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
+    if out.dtype == torch.bfloat16:
+        torch.mm(a, w.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
+
+
+# ------------------------------------------------------------------------------------ attention
+def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                    block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal GQA attention of every row of q [T, H*hd] over its request's pages.
+    block_tables int32 [S, max_pages]; row_seq, positions int32 [T]; window 0 = all keys."""
+    op = "paged_attention"
+    _cuda(op, q, out, kcache, vcache, block_tables, row_seq, positions)
+    _rows_2d(q, op, "q")
+    _rows_2d(out, op, "out")
+    T = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or out.dtype != q.dtype:
+        raise ShapeError(op, f"q and out must be [{T}, {num_heads * head_dim}] of one dtype, got {list(q.shape)} "
+                             f"{q.dtype} and {list(out.shape)} {out.dtype}")
+    if num_kv_heads <= 0 or num_heads % num_kv_heads != 0:
+        raise ShapeError(op, f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+    if head_dim % 8 != 0 or head_dim > 256:
+        raise ShapeError(op, f"head_dim {head_dim} is not supported (multiples of 8 up to 256)")
+    for name, c in (("kcache", kcache), ("vcache", vcache)):
+        if c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous() or c.dtype != q.dtype:
+            raise ShapeError(op, f"{name} must be contiguous {q.dtype} [pages, {num_kv_heads}, page_size, {head_dim}], "
+                                 f"got {c.dtype} {list(c.shape)}")
+    if kcache.shape != vcache.shape:
+        raise ShapeError(op, "kcache and vcache differ in shape")
+    if kcache.numel() // head_dim >= 2 ** 31:
+        raise ShapeError(op, "one layer's cache has 2^31 rows or more")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, f"block_tables must be contiguous int32 [S, max_pages], got {block_tables.dtype} {list(block_tables.shape)}")
+    _int32_vec(row_seq, T, op, "row_seq")
+    _int32_vec(positions, T, op, "positions")
+    f = _fn("attention", "vob_paged_attention",
+            [_P, _L, _P, _L, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _code(q, op),
+             _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), T, num_heads,
+             num_kv_heads, head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ sampling
+def pick_splits(vocab: int) -> int:
+    f = _fn("sampling", "vob_pick_splits", [_I])
+    return int(f(vocab))
+
+
+def pick_tokens(logits: torch.Tensor, out: torch.Tensor, nan_flags: torch.Tensor, scratch_val: torch.Tensor,
+                scratch_idx: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+                seeds: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> None:
+    """One token per row of float32 logits [R, V]: greedy where temperature is 0 or absent,
+    Gumbel-max sampling elsewhere. seeds int32 [R, 2] (low, high word), steps int32 [R]
+    (index of the generated token), nan_flags int32 [R] raised for rows that hold a NaN.
+    scratch_val float32 and scratch_idx int32 need R * pick_splits(V) elements each."""
+    op = "pick_tokens"
+    _cuda(op, logits, out, nan_flags, scratch_val, scratch_idx, temperature, seeds, steps)
+    _rows_2d(logits, op, "logits")
+    if logits.dtype != torch.float32:
+        raise ShapeError(op, f"logits must be float32, got {logits.dtype}")
+    R, V = logits.shape
+    splits = pick_splits(V)
+    _int32_vec(out, R, op, "out")
+    _int32_vec(nan_flags, R, op, "nan_flags")
+    if scratch_val.dtype != torch.float32 or scratch_val.numel() < R * splits or not scratch_val.is_contiguous():
+        raise ShapeError(op, f"scratch_val must hold {R * splits} float32")
+    if scratch_idx.dtype != torch.int32 or scratch_idx.numel() < R * splits or not scratch_idx.is_contiguous():
+        raise ShapeError(op, f"scratch_idx must hold {R * splits} int32")
+    if temperature is not None:
+        if temperature.dtype != torch.float32 or temperature.numel() < R or not temperature.is_contiguous():
+            raise ShapeError(op, f"temperature must be float32 [{R}]")
+        if seeds is None or steps is None:
+            raise ShapeError(op, "temperature sampling needs seeds and steps")
+        if seeds.dtype != torch.int32 or seeds.numel() < 2 * R or not seeds.is_contiguous():
+            raise ShapeError(op, f"seeds must be int32 [{R}, 2]")
+        _int32_vec(steps, R, op, "steps")
+    f = _fn("sampling", "vob_pick_tokens", [_P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(seeds), _ptr(steps), splits,
+             _ptr(scratch_val), _ptr(scratch_idx), _ptr(nan_flags), _ptr(out), _stream()), op)

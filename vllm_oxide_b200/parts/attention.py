@@ -1,0 +1,85 @@
+"""Causal grouped-query attention over the paged cache, as a mixer.
+
+Per step: one fused projection to [q | k | v], rotary positions on q and k, the write of k and
+v to their cache slots, attention of every row over its request's pages, the output projection
+(crates/engine/src/model.rs:302-321: rmsnorm and the residual add belong to the block). The
+write comes before the read, so the step's own keys are read from the cache like the older ones
+(crates/engine/src/model.rs:309-311).
+
+Parameters: head counts, head size, an optional window (the last `window` keys only), an
+optional score scale (default head_dim^-1/2, crates/engine/src/backend/cpu/attention.rs:91),
+and the position encoding (a `Rotary` or None). With `wk`/`wv` None the mixer writes no cache:
+it must be scheduled on a cache that another layer writes.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from .base import CacheSpec, LayerCache, Mixer, StepContext
+from .linear import matmul, to_compute
+
+
+class Attention(Mixer):
+    def __init__(self, wq: torch.Tensor, wk: Optional[torch.Tensor], wv: Optional[torch.Tensor], wo: torch.Tensor,
+                 num_heads: int, num_kv_heads: int, head_dim: int, position=None, window: Optional[int] = None,
+                 scale: Optional[float] = None, dtype=torch.bfloat16, device="cuda"):
+        self.H, self.KV, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
+        if self.H % self.KV != 0:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.KV} kv heads")
+        if self.hd % 16 != 0 or self.hd > 256:
+            raise ValueError(f"head_dim {self.hd} is not supported: multiples of 16 up to 256")
+        hidden = wq.shape[1]
+        if wq.shape != (self.H * self.hd, hidden) or wo.shape != (hidden, self.H * self.hd):
+            raise ValueError(f"q/o projection shapes {list(wq.shape)} / {list(wo.shape)} do not fit "
+                             f"{self.H} heads of {self.hd}")
+        self.owns_cache = wk is not None
+        if self.owns_cache:
+            if wv is None or wk.shape != (self.KV * self.hd, hidden) or wv.shape != wk.shape:
+                raise ValueError("k/v projection shapes do not fit the kv heads")
+            # One matrix [Wq; Wk; Wv]: a single product gives q, k and v side by side. Row o of
+            # the fused matrix is row o of its source, so every output element is unchanged.
+            self.w_qkv = to_compute(torch.cat([wq, wk, wv], dim=0), dtype, device)
+        else:
+            self.w_qkv = to_compute(wq, dtype, device)
+        self.w_o = to_compute(wo, dtype, device)
+        self.position = position
+        self.window = int(window) if window else 0
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
+        self.hidden = hidden
+        self.dtype = dtype
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return CacheSpec(self.KV, self.hd, "window" if self.window else "full", self.window)
+
+    def weight_bytes(self) -> int:
+        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
+
+    def workspace_bytes(self, rows: int) -> int:
+        es = 2 if self.dtype == torch.bfloat16 else 4
+        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + 2 * 256
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
+        if cache is None:
+            raise ValueError("attention needs a cache")
+        T = x.shape[0]
+        qd, kd = self.H * self.hd, self.KV * self.hd
+        qkv = matmul(x, self.w_qkv, ctx.alloc((T, self.w_qkv.shape[0])))
+        q = qkv[:, :qd]
+        inv_freq = self.position.inv_freq if self.position is not None else None
+        if self.owns_cache and cache.write:
+            k, v = qkv[:, qd:qd + kd], qkv[:, qd + kd:]
+            kernels.rope_kv_write(q, k, v, ctx.positions, ctx.slot_mapping[cache.group], inv_freq,
+                                  cache.k, cache.v, self.H, self.KV, self.hd)
+        else:
+            kernels.rope_kv_write(q, None, None, ctx.positions, None, inv_freq, None, None, self.H, self.KV, self.hd)
+        attn = ctx.alloc((T, qd))
+        self.attend(q, attn, ctx, cache)
+        return matmul(attn, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
+
+    def attend(self, q, out, ctx: StepContext, cache: LayerCache) -> None:
+        kernels.paged_attention(q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_seq,
+                                ctx.positions, self.H, self.KV, self.hd, self.scale, self.window)

@@ -1,0 +1,188 @@
+"""Interfaces of the parts a decoder is put together from, and of what a step hands them.
+
+A model is data: a list of blocks, and a list that says in which order they run and which
+cache each call uses (`ModelSpec.schedule`). A block arranges a mixer and a feed-forward
+around two norms; which mixer, feed-forward, norm and position encoding a block gets is the
+architecture builder's choice per layer, taken from the configuration. No part knows which
+model it is in: sizes and constants arrive as constructor parameters, per-step facts arrive
+in a `StepContext`.
+
+What each kind of part must offer:
+
+* Mixer        - `cache_spec()` (pages it needs: all keys, a window, or None),
+                 `state_spec()` (fixed-size per-request state, or None),
+                 `forward(x, ctx, cache, state, out=None) -> [T, hidden]` in the compute dtype.
+* FeedForward  - `forward(x, ctx, out=None) -> [T, hidden]`.
+* Norm         - `forward(resid, delta, ctx, rows=None) -> normed`; adds `delta` into the
+                 float32 residual first (the residual sum is kept in 32-bit).
+* PositionEncoding - whatever its mixer asks of it; the rotary part offers `inv_freq`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+
+# ------------------------------------------------------------------------------ cache / state needs
+@dataclass(frozen=True)
+class CacheSpec:
+    """Pages a mixer needs: keys and values of `num_kv_heads` x `head_dim` per token."""
+    num_kv_heads: int
+    head_dim: int
+    kind: str = "full"          # "full": every key is kept; "window": the last `window` keys
+    window: int = 0
+
+    def group_key(self) -> Tuple:
+        return (self.kind, self.window, self.num_kv_heads, self.head_dim)
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Fixed-size state per request: one tensor of `shape` per state slot, zeroed at admission."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """One cache of one call in the schedule: this layer's pages and which group's block tables
+    address them."""
+    k: torch.Tensor             # [num_pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    group: int
+    write: bool = True          # False: the call reads a cache that another call wrote
+
+
+# ------------------------------------------------------------------------------ per-step facts
+class Workspace:
+    """A bump allocator over one device buffer: a step's activations live here, so that a step
+    allocates nothing and its tensors sit at the same addresses every time. The reference's
+    per-step arena (crates/engine/src/arena.rs:92-158) with scopes that rewind on close."""
+
+    def __init__(self, nbytes: int, device):
+        self.buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        self.top = 0
+        self.high_water = 0
+
+    def alloc(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.top + 255) & ~255
+        if start + nbytes > self.buf.numel():
+            from ..errors import CapacityError
+            raise CapacityError("step workspace", start + nbytes, self.buf.numel())
+        self.top = start + nbytes
+        self.high_water = max(self.high_water, self.top)
+        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+
+    def reset(self) -> None:
+        self.top = 0
+
+    class _Scope:
+        def __init__(self, ws):
+            self.ws = ws
+
+        def __enter__(self):
+            self.mark = self.ws.top
+            return self.ws
+
+        def __exit__(self, *exc):
+            self.ws.top = self.mark
+            return False
+
+    def scope(self) -> "_Scope":
+        return Workspace._Scope(self)
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the current step. Device tensors are views into the
+    step's packed int32 buffer; they hold `rows_cap` / `seqs_cap` entries of which the first
+    `rows` / `seqs` are real (the rest is padding that attends to nothing and writes nothing)."""
+    rows: int                       # rows the kernels run over (real rows, or the padded count)
+    seqs: int
+    dtype: torch.dtype              # compute dtype of activations and cache
+    tokens: torch.Tensor            # int32 [rows]
+    positions: torch.Tensor         # int32 [rows]   position of each row in its request
+    row_seq: torch.Tensor           # int32 [rows]   which request of the batch a row belongs to
+    seq_starts: torch.Tensor        # int32 [seqs+1] first row of each request
+    context_lens: torch.Tensor      # int32 [seqs]   keys cached before this step
+    seq_lens: torch.Tensor          # int32 [seqs]   keys after this step
+    state_slots: torch.Tensor       # int32 [seqs]   state slot of each request
+    logit_rows: torch.Tensor        # int32 [R]
+    slot_mapping: List[torch.Tensor]   # per group: int32 [rows] cache slot of each row (-1: none)
+    block_tables: List[torch.Tensor]   # per group: int32 [seqs, max_pages]
+    workspace: Workspace
+    max_new: int = 0                # longest portion in the batch (host fact)
+    max_seq_len: int = 0            # longest context after the step (host fact)
+    host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them
+
+    def alloc(self, shape, dtype=None) -> torch.Tensor:
+        return self.workspace.alloc(shape, dtype or self.dtype)
+
+
+# ------------------------------------------------------------------------------ part interfaces
+class Mixer:
+    """Mixes information between the tokens of a request (attention here)."""
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def workspace_bytes(self, rows: int) -> int:
+        return 0
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [T, hidden] in the compute dtype -> [T, hidden]. `out`, if given, is where the
+        result should go (a part may ignore it and return a tensor of its own)."""
+        raise NotImplementedError
+
+
+class FeedForward:
+    def workspace_bytes(self, rows: int) -> int:
+        return 0
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm:
+    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
+                rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding:
+    pass
+
+
+# ------------------------------------------------------------------------------ a model as data
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of the run order: run `layer` with cache number `cache` (None: the mixer keeps
+    no pages). Naming a layer twice runs it twice (with two caches, or sharing one); `write`
+    False lets a call read a cache that an earlier call of the same step wrote."""
+    layer: int
+    cache: Optional[int] = None
+    write: bool = True
+
+
+@dataclass
+class ModelSpec:
+    embedding: object                   # .forward(ctx) -> float32 residual [rows, hidden]
+    blocks: List[object]                # Block parts
+    schedule: List[LayerCall]
+    final_norm: Norm
+    lm_head: object                     # .forward(normed, ctx, out) -> float32 logits
+    hidden_size: int
+    vocab_size: int
+    max_position: Optional[int] = None  # longest position the position encodings allow
+    eos_token_ids: Tuple[int, ...] = ()
+    weight_bytes: int = 0               # bytes a decode step must read of the weights

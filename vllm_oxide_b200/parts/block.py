@@ -1,0 +1,47 @@
+"""The arrangement of parts in one layer: pre-norm residual block.
+
+    residual += mixer(norm1(residual));  residual += feed_forward(norm2(residual))
+(crates/engine/src/model.rs:302-332). The residual is float32. Each part's output is not added
+at once: it is handed on as `pending` and the next norm's kernel adds it while it normalises
+(one pass over the row instead of two). The model's final norm takes the last `pending`.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import FeedForward, LayerCache, Mixer, Norm, StepContext
+
+
+class Block:
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+
+    def weight_bytes(self) -> int:
+        return sum(getattr(p, "weight_bytes", lambda: 0)() for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+
+    def workspace_bytes(self, rows: int, hidden: int, act_bytes: int) -> int:
+        """Peak scratch of one run of the block: the mixer's output, then the larger of
+        (normed input + mixer scratch) and (normed input + feed-forward scratch)."""
+        row = rows * hidden * act_bytes + 256
+        return 2 * row + max(self.mixer.workspace_bytes(rows), self.feed_forward.workspace_bytes(rows))
+
+    def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+        """Runs the block. `pending` is the previous block's output that is still to be added to
+        the residual; the feed-forward's output (again not yet added) is written to `out`,
+        which outlives the block's own scratch."""
+        ws = ctx.workspace
+        with ws.scope():
+            mixed = ctx.alloc(out.shape, out.dtype)
+            with ws.scope():
+                normed = self.norm1.forward(resid, pending, ctx)
+                m = self.mixer.forward(normed, ctx, cache, state, out=mixed)
+                if m.data_ptr() != mixed.data_ptr():
+                    mixed.copy_(m)
+            normed2 = self.norm2.forward(resid, mixed, ctx)
+            ff = self.feed_forward.forward(normed2, ctx, out=out)
+            if ff.data_ptr() != out.data_ptr():
+                out.copy_(ff)
+        return out

@@ -1,0 +1,40 @@
+"""Token embedding (row gather into the float32 residual, crates/engine/src/backend/cpu/mod.rs:172-180)
+and the output head (logits = normed x E^T in float32; E is the embedding table when the
+configuration ties them, crates/engine/src/model.rs:344)."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import StepContext
+from .linear import to_compute
+
+
+class Embedding:
+    def __init__(self, table: torch.Tensor, dtype=torch.bfloat16, device="cuda"):
+        self.table = to_compute(table, dtype, device)
+        self.vocab, self.hidden = self.table.shape
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def weight_bytes_per_row(self) -> int:
+        return self.hidden * self.table.element_size()
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        resid = ctx.alloc((ctx.rows, self.hidden), torch.float32)
+        kernels.embed(self.table, ctx.tokens, resid, self.err_flag)
+        return resid
+
+
+class LMHead:
+    """`weight` may be the Embedding's own table (tied): no copy is made then."""
+
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        self.vocab, self.hidden = weight.shape
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, normed: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        kernels.linear(normed, self.weight, out)
+        return out

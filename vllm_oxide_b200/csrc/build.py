@@ -59,7 +59,7 @@ def _nvcc() -> str:
 def _digest(paths: List[str], flags: List[str]) -> str:
     h = hashlib.sha256()
     for p in paths:
-        h.update(p.encode())
+        h.update(os.path.basename(p).encode())
         with open(p, "rb") as f:
             h.update(f.read())
     h.update(" ".join(flags).encode())

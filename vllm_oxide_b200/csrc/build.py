@@ -34,19 +34,26 @@ _lock = threading.Lock()
 _loaded: Dict[str, object] = {}
 
 
+_bdir = None
+_bdir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
-    d = os.path.join(_HERE, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"vllm_oxide_b200-build-{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """`_build/` beside the sources; a per-user folder under the temp dir if that is read-only."""
+    global _bdir
+    with _bdir_lock:
+        if _bdir is None:
+            d = os.path.join(_HERE, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(dir=d)
+                os.close(fd)
+                os.remove(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"vllm_oxide_b200-build-{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _bdir = d
+        return _bdir
 
 
 def _nvcc() -> str:

@@ -3,7 +3,7 @@
 //
 //   temperature == 0:  first index of the maximum (strictly-greater comparison keeps the first,
 //                      crates/engine/src/backend/cpu/mod.rs:370-388); a NaN anywhere in the row
-//                      raises the row's flag, which the host turns into an error (:377-379).
+//                      makes the row's pick -1, which the host turns into an error (:377-379).
 //   temperature  > 0:  argmax_i(logit_i / temperature + g_i),  g_i = -log(-log(u_i)),
 //                      u_i in (0,1) from a counter-based hash of (seed, generated index, i):
 //                      a draw from softmax(logits / temperature) that depends on nothing but the
@@ -89,7 +89,7 @@ pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const
 }
 
 __global__ void pick_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
-                                  int splits, int V, int* __restrict__ out) {
+                                  int splits, int V, int* __restrict__ nan_flags, int* __restrict__ out) {
     __shared__ Best sh[32];
     int r = blockIdx.x;
     Best b{-INFINITY, 0x7fffffff};
@@ -97,7 +97,12 @@ __global__ void pick_final_kernel(const float* __restrict__ part_val, const int*
         b = better(b, Best{part_val[(size_t)r * splits + s], part_idx[(size_t)r * splits + s]});
     b = block_best(b, sh);
     // all values -inf or NaN: fall back to index 0, as a scan that never finds a greater value does
-    if (threadIdx.x == 0) out[r] = (b.i >= 0 && b.i < V) ? b.i : 0;
+    // A row that held a NaN yields -1 (the host turns it into an error) and its flag is cleared.
+    if (threadIdx.x == 0) {
+        int tok = (b.i >= 0 && b.i < V) ? b.i : 0;
+        if (nan_flags[r]) { tok = -1; nan_flags[r] = 0; }
+        out[r] = tok;
+    }
 }
 
 // Scratch needed: R * splits floats and R * splits ints. `splits` is chosen by the caller
@@ -118,6 +123,6 @@ VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, 
                                                   part_idx, nan_flags);
     int e = vob_launch_status();
     if (e) return e;
-    pick_final_kernel<<<R, 64, 0, stream>>>(part_val, part_idx, splits, V, out);
+    pick_final_kernel<<<R, 64, 0, stream>>>(part_val, part_idx, splits, V, nan_flags, out);
     return vob_launch_status();
 }

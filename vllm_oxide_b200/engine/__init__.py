@@ -1,3 +1,4 @@
 from .runner import ModelRunner, StepResult
+from .llm import LLM, Generator, RequestOutput, GenerateOutput
 
-__all__ = ["ModelRunner", "StepResult"]
+__all__ = ["ModelRunner", "StepResult", "LLM", "Generator", "RequestOutput", "GenerateOutput"]

@@ -1,0 +1,241 @@
+"""The Python entry point: load a model folder, generate.
+
+`Generator.greedy(prompt, max_new, stop, capture)` is the reference's library call with its names
+and meanings (crates/engine/src/generate.rs:33-54): token ids in, `GenerateOutput{tokens, captured,
+prefill_time, decode_time}` out, the stop token kept, an empty prompt or max_new = 0 refused.
+`LLM.generate` is the batched form over the scheduler: many prompts, continuous batching,
+chunked prefill, preemption when pages run out. Both run every token through
+`ModelRunner.step`. The loop is the one the reference plans for its engine thread
+(CLAUDE.md:68): schedule, prepare inputs, forward, sample, emit.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..config import EngineConfig
+from ..errors import CapacityError, NaNError, ShapeError
+from ..sampling import SamplingParams
+from .runner import ModelRunner
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finish_reason: str                      # "stop", "length", "capacity", "abort"
+    text: Optional[str] = None
+    logits: Dict[int, torch.Tensor] = field(default_factory=dict)   # generated position -> float32 [vocab]
+    preemptions: int = 0
+
+
+@dataclass
+class GenerateOutput:
+    """crates/engine/src/generate.rs:22-30."""
+    tokens: List[int]
+    captured: List[tuple]                   # (generated index, float32 [vocab])
+    prefill_time: float
+    decode_time: float
+
+
+class LLM:
+    def __init__(self, model: Union[str, ModelRunner], dtype="bfloat16", **engine_kwargs):
+        if isinstance(model, ModelRunner):
+            self.runner = model
+        else:
+            self.runner = ModelRunner.from_dir(model, EngineConfig(dtype=dtype, **engine_kwargs))
+        r = self.runner
+        e = r.engine
+        self.scheduler = r.rt.Scheduler(r.manager, e.max_batch_tokens, e.max_seqs, r.max_model_len,
+                                        e.prefill_chunk or 0)
+        self._next_id = 0
+        self._params: Dict[int, SamplingParams] = {}
+        self._prompts: Dict[int, List[int]] = {}
+        self._captured: Dict[int, Dict[int, torch.Tensor]] = {}
+        self._generated: Dict[int, int] = {}
+        self._preempt: Dict[int, int] = {}
+        self._tokenizer = None
+        self._logit_buf = None
+        self.stats = {"steps": 0, "preemptions": 0, "decode_steps": 0, "graph_steps": 0}
+        tok = os.path.join(model, "tokenizer.json") if isinstance(model, str) else None
+        if tok and os.path.exists(tok):
+            try:
+                from tokenizers import Tokenizer
+                self._tokenizer = Tokenizer.from_file(tok)
+            except ImportError:
+                self._tokenizer = None
+
+    # ------------------------------------------------------------------ requests
+    def encode(self, text: str) -> List[int]:
+        if self._tokenizer is None:
+            raise ShapeError("generate", "text prompts need a tokenizer.json in the model folder; pass token ids")
+        return self._tokenizer.encode(text).ids
+
+    def decode(self, ids: Sequence[int]) -> Optional[str]:
+        return self._tokenizer.decode(list(ids)) if self._tokenizer is not None else None
+
+    def add_request(self, prompt: Union[str, Sequence[int]], params: SamplingParams) -> int:
+        ids = self.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        vocab = self.runner.spec.vocab_size
+        for t in ids:
+            if not 0 <= t < vocab:
+                raise ShapeError("generate", f"token {t} is outside the vocabulary of {vocab}")
+        stops = list(self.runner.spec.eos_token_ids) if params.stop_token_ids is None else [int(s) for s in params.stop_token_ids]
+        rid = self._next_id
+        self._next_id += 1
+        rt = self.runner.rt
+        try:
+            self.scheduler.add_request(rid, ids, rt.SamplingParams(int(params.max_new_tokens), float(params.temperature),
+                                                                   int(params.seed), stops))
+        except rt.RuntimeFault as e:
+            msg = str(e)
+            if msg.startswith("capacity"):
+                need = len(ids) + params.max_new_tokens - 1
+                raise CapacityError("sequence length", need, self.runner.max_model_len) from e
+            raise ShapeError("generate", msg) from e
+        self._params[rid] = params
+        self._prompts[rid] = ids
+        self._captured[rid] = {}
+        self._generated[rid] = 0
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ------------------------------------------------------------------ one engine step
+    def step(self) -> List[RequestOutput]:
+        """schedule -> arrays -> forward -> pick -> update. Returns the requests that finished."""
+        r, sched = self.runner, self.scheduler
+        plan = sched.schedule()
+        self.stats["preemptions"] += len(plan.preempted)
+        for rid in plan.preempted:
+            self._preempt[rid] = self._preempt.get(rid, 0) + 1
+        for rid in plan.admitted:
+            r.pools.reset_slot(r.manager.state_slot(rid))
+        done = []
+        if plan.entries:
+            decode_only = all(e.count == 1 and e.sample for e in plan.entries)
+            want_logits = any(e.sample and self._params[e.id].capture_logits for e in plan.entries)
+            if decode_only and r.graphs_enabled and not want_logits:
+                sampled = r.decode_step_graph(sched, plan)
+                self.stats["graph_steps"] += 1
+            else:
+                arrays = sched.arrays(plan, r.rows_cap, r.seqs_cap, r.logits_cap, r.max_pages, r.spec.vocab_size)
+                buf = None
+                if want_logits:
+                    if self._logit_buf is None:
+                        self._logit_buf = torch.empty((r.seqs_cap, r.spec.vocab_size), dtype=torch.float32, device=r.device)
+                    buf = self._logit_buf
+                sampled = r.step(arrays, logits_out=buf).tokens()
+                if want_logits:
+                    row = 0
+                    for e in plan.entries:
+                        if not e.sample:
+                            continue
+                        g = self._generated[e.id]
+                        if g in self._params[e.id].capture_logits:
+                            self._captured[e.id][g] = buf[row].cpu()
+                        row += 1
+            if any(t < 0 for t in sampled):
+                raise NaNError("pick_tokens")        # crates/engine/src/backend/cpu/mod.rs:377-379
+            self.stats["steps"] += 1
+            self.stats["decode_steps"] += int(decode_only)
+            for e in plan.entries:
+                if e.sample:
+                    self._generated[e.id] += 1
+            done = sched.update(plan, sampled)
+        else:
+            done = sched.take_done()
+            if not done and not plan.preempted and sched.has_unfinished():
+                raise CapacityError("scheduler made no progress: pages", 1, 0)
+        outs = []
+        for f in done:
+            rid = f.id
+            outs.append(RequestOutput(rid, self._prompts.pop(rid), list(f.output), f.reason,
+                                      self.decode(f.output), self._captured.pop(rid), self._preempt.pop(rid, 0)))
+            self._params.pop(rid)
+            self._generated.pop(rid)
+        return outs
+
+    def step_async(self) -> None:
+        """A decode step whose picked tokens stay on the device: the next step reads them there and
+        the host does not wait. For throughput measurement of requests that never stop early; the
+        host-side token lists receive placeholders."""
+        r, sched = self.runner, self.scheduler
+        plan = sched.schedule()
+        if not plan.entries or plan.preempted or plan.admitted or not all(e.count == 1 and e.sample for e in plan.entries):
+            raise ShapeError("step_async", "only steady decode steps can run without reading tokens back")
+        r.decode_step_graph(sched, plan, feed_from_device=True, read=False)
+        for e in plan.entries:
+            self._generated[e.id] += 1
+        self.stats["steps"] += 1
+        for f in sched.update(plan, [0] * len(plan.entries)):
+            self._forget(f.id)
+
+    def drain_async(self) -> None:
+        torch.cuda.synchronize()
+
+    def abort(self, request_id: int) -> None:
+        if self.scheduler.abort(request_id):
+            self.scheduler.take_done()
+        self._forget(request_id)
+
+    def _forget(self, rid: int) -> None:
+        for d in (self._params, self._prompts, self._captured, self._generated, self._preempt):
+            d.pop(rid, None)
+
+    # ------------------------------------------------------------------ whole jobs
+    def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:
+        """Run every prompt to its end; outputs come back in the order of `prompts`."""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        plist = [sampling_params] * len(prompts) if isinstance(sampling_params, SamplingParams) else list(sampling_params)
+        if len(plist) != len(prompts):
+            raise ShapeError("generate", f"{len(prompts)} prompts but {len(plist)} sampling parameter sets")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        results: Dict[int, RequestOutput] = {}
+        while self.has_unfinished():
+            for out in self.step():
+                results[out.request_id] = out
+        return [results[i] for i in ids]
+
+
+class Generator:
+    """The reference's single-sequence driver (crates/engine/src/generate.rs:16-54) over this
+    engine: one request, greedy, timed. The same engine and pool serve call after call."""
+
+    def __init__(self, model: Union[str, ModelRunner, LLM], **kwargs):
+        self.llm = model if isinstance(model, LLM) else LLM(model, **kwargs)
+
+    def model(self) -> ModelRunner:
+        return self.llm.runner
+
+    def greedy(self, prompt: Sequence[int], max_new: int, stop: Optional[int] = None,
+               capture: Sequence[int] = ()) -> GenerateOutput:
+        if len(prompt) == 0 or max_new == 0:
+            raise ShapeError("generate", "empty prompt or max_new = 0")       # generate.rs:55-60
+        sp = SamplingParams(max_new_tokens=max_new, temperature=0.0, stop_token_ids=() if stop is None else (stop,),
+                            capture_logits=tuple(capture))
+        llm = self.llm
+        rid = llm.add_request(prompt, sp)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = None
+        prefill_time = None
+        while out is None:
+            for o in llm.step():
+                if o.request_id == rid:
+                    out = o
+            if prefill_time is None and (out is not None or llm._generated.get(rid, 0) >= 1):
+                torch.cuda.synchronize()
+                prefill_time = time.perf_counter() - t0       # up to and including the first token
+        torch.cuda.synchronize()
+        total = time.perf_counter() - t0
+        return GenerateOutput(list(out.token_ids), sorted(out.logits.items()), prefill_time, total - prefill_time)

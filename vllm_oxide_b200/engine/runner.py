@@ -24,7 +24,7 @@ from .. import kernels
 from ..cache.pools import CachePools
 from ..config import EngineConfig, architecture_for, read_config_json
 from ..csrc.build import runtime_module
-from ..errors import CapacityError, KernelError, NaNError, ShapeError
+from ..errors import CapacityError, KernelError, ShapeError
 from ..parts.base import ModelSpec, StepContext, Workspace
 from ..weights import load_safetensors_weights, weights_from_tensors
 
@@ -97,7 +97,11 @@ class ModelRunner:
         self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.steps_run = 0
-        self.kernel_launches = 0
+        self.graphs_enabled = bool(engine.cuda_graphs)
+        self.decode_layout = self.rt.step_layout(self.seqs_cap, self.seqs_cap, self.seqs_cap, G, self.max_pages)
+        self._graphs = {}
+        self._graph_launches = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ sizes
     def workspace_formula(self, rows: int) -> int:
@@ -121,9 +125,10 @@ class ModelRunner:
         return cls(config, model_dir, engine, arch)
 
     # ------------------------------------------------------------------ the step
-    def context(self, rows: int, seqs: int, arrays=None) -> StepContext:
-        L, d = self.layout, self.step_dev
+    def context(self, rows: int, seqs: int, arrays=None, layout=None) -> StepContext:
+        L, d = layout or self.layout, self.step_dev
         mp = self.max_pages
+        seqs_cap = L["seqs_cap"]
 
         def vec(key, n):
             o = L[key]
@@ -134,9 +139,9 @@ class ModelRunner:
             tokens=vec("tokens", rows), positions=vec("positions", rows), row_seq=vec("row_seq", rows),
             seq_starts=vec("seq_starts", seqs + 1), context_lens=vec("context_lens", seqs),
             seq_lens=vec("seq_lens", seqs), state_slots=vec("state_slots", seqs),
-            logit_rows=vec("logit_rows", self.logits_cap),
+            logit_rows=vec("logit_rows", L["logits_cap"]),
             slot_mapping=[d[L["slot_mapping"][g]:L["slot_mapping"][g] + rows] for g in range(G)],
-            block_tables=[d[L["block_tables"][g]:L["block_tables"][g] + self.seqs_cap * mp].view(self.seqs_cap, mp)
+            block_tables=[d[L["block_tables"][g]:L["block_tables"][g] + seqs_cap * mp].view(seqs_cap, mp)
                           for g in range(G)],
             workspace=self.workspace,
             max_new=arrays.max_new if arrays is not None else 0,
@@ -168,10 +173,11 @@ class ModelRunner:
             pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1])
         return resid, pending
 
-    def _head(self, resid, pending, ctx: StepContext, num_logit_rows: int, logits_out: Optional[torch.Tensor]) -> None:
+    def _head(self, resid, pending, ctx: StepContext, num_logit_rows: int, logits_out: Optional[torch.Tensor],
+              layout=None) -> None:
         """Final norm and output head on the wanted rows, in chunks; a token is picked from every
         row; logits are copied out only where the caller gave a place for them."""
-        spec, L = self.spec, self.layout
+        spec, L = self.spec, layout or self.layout
         d = self.step_dev
         V = spec.vocab_size
         for c0 in range(0, num_logit_rows, self.logit_chunk):
@@ -189,9 +195,10 @@ class ModelRunner:
                 if logits_out is not None:
                     logits_out[c0:c0 + n].copy_(logits, non_blocking=logits_out.is_cuda)
 
-    def step(self, arrays, logits_out: Optional[torch.Tensor] = None, check_nan: bool = False) -> StepResult:
+    def step(self, arrays, logits_out: Optional[torch.Tensor] = None) -> StepResult:
         """Run one batch. `arrays` comes from `build_arrays` or the scheduler. `logits_out`
-        (float32 [>=R, vocab], on the device or the host) receives the logits of the wanted rows."""
+        (float32 [>=R, vocab], on the device or the host) receives the logits of the wanted rows.
+        A picked token of -1 marks a row whose logits held a NaN."""
         T, S, R = arrays.rows, arrays.seqs, arrays.logit_count
         if arrays.max_seq_len > self.max_model_len:
             raise CapacityError("sequence length", int(arrays.max_seq_len), self.max_model_len)
@@ -201,17 +208,62 @@ class ModelRunner:
         self.upload(arrays)
         self.workspace.reset()
         ctx = self.context(T, S, arrays)
-        if check_nan:
-            self.nan_flags.zero_()
         resid, pending = self._forward(ctx)
         if R:
             self._head(resid, pending, ctx, R, logits_out)
         self.steps_run += 1
-        if check_nan and R and bool(self.nan_flags[:R].any().item()):
-            raise NaNError("pick_tokens")
-        if self.spec.embedding.err_flag is not None and check_nan and bool(self.spec.embedding.err_flag.item()):
-            raise ShapeError("embed", "a token id outside the vocabulary reached the device")
         return StepResult(self.sampled, logits_out, R)
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.seqs_cap)
+
+    def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True) -> List[int]:
+        """A step in which every request brings exactly one token. Its kernels are the same as any
+        step's, but their launches are replayed from a CUDA graph captured once per batch-size
+        class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing), because
+        at small batches launching ~10 kernels per layer costs more than running them
+        (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51)."""
+        S = len(plan.entries)
+        L = self.decode_layout
+        arrays = scheduler.arrays(plan, L["rows_cap"], L["seqs_cap"], L["logits_cap"], self.max_pages, self.spec.vocab_size)
+        if arrays.max_seq_len > self.max_model_len:
+            raise CapacityError("sequence length", int(arrays.max_seq_len), self.max_model_len)
+        self.upload(arrays)
+        if feed_from_device:
+            # the tokens of this step are the previous step's picks, taken on the device (the host
+            # runs ahead without reading them back; request order must not have changed)
+            self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
+        b = self._bucket(S)
+        graph = self._graphs.get(b)
+        if graph is None:
+            # first step of this class: run it eagerly (that is this step's result), then record
+            # the same launches for the steps to come
+            self._decode_eager(b)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = kernels.launch_count()
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                self._decode_eager(b)
+            self._graph_launches[b] = kernels.launch_count() - n0
+            kernels.count_launches(-self._graph_launches[b])      # recorded, not run
+            self._graphs[b] = g
+            self._graph_pool = self._graph_pool or g.pool()
+        else:
+            graph.replay()
+            kernels.count_launches(self._graph_launches[b])
+        self.steps_run += 1
+        return self.sampled[:S].tolist() if read else []
+
+    def _decode_eager(self, b: int) -> None:
+        L = self.decode_layout
+        self.workspace.reset()
+        ctx = self.context(b, b, None, L)
+        resid, pending = self._forward(ctx)
+        self._head(resid, pending, ctx, b, None, L)
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def admit(self, request_id: int) -> int:

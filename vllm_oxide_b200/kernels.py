@@ -53,10 +53,25 @@ def _stream() -> _P:
     return _P(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(status: int, op: str) -> None:
+_launches = 0      # kernels of this package launched (or replayed from a graph) so far
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for launches that did not pass through a wrapper (a CUDA graph replay)."""
+    global _launches
+    _launches += n
+
+
+def _check(status: int, op: str, launches: int = 1) -> None:
+    global _launches
     if status != 0:
         what = _STATUS.get(status, f"CUDA error {status}")
         raise KernelError(f"{op}: launch failed: {what}")
+    _launches += launches
 
 
 def _rows_2d(t: torch.Tensor, op: str, name: str) -> None:
@@ -72,6 +87,53 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 
 _fn_cache = {}
+
+# Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
+# (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
+# events and add no synchronisation, crates/engine/src/arena.rs:66-68,243-255).
+_profile = None
+
+
+class OpProfile:
+    """with OpProfile() as p: ...steps...; p.totals() -> [(op, calls, total_ms)] by time."""
+
+    def __init__(self):
+        self.events = []
+
+    def __enter__(self):
+        global _profile
+        _profile = self
+        return self
+
+    def __exit__(self, *exc):
+        global _profile
+        _profile = None
+        return False
+
+    def totals(self):
+        torch.cuda.synchronize()
+        agg = {}
+        for name, a, b in self.events:
+            c, t = agg.get(name, (0, 0.0))
+            agg[name] = (c + 1, t + a.elapsed_time(b))
+        return sorted(((n, c, t) for n, (c, t) in agg.items()), key=lambda x: -x[2])
+
+
+def _timed(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if _profile is None:
+            return fn(*args, **kwargs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        try:
+            return fn(*args, **kwargs)
+        finally:
+            b.record()
+            _profile.events.append((fn.__name__, a, b))
+    return wrapper
 
 
 def _fn(module: str, name: str, argtypes):
@@ -96,6 +158,7 @@ def preload(modules=("elementwise", "gemm_f32", "attention", "sampling")) -> Non
 
 
 # ------------------------------------------------------------------------------------ embedding
+@_timed
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None) -> None:
     """out[t] = table[tokens[t]] as float32; `tokens` int32 [T], `out` float32 [T, h]."""
     op = "embed"
@@ -112,6 +175,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag
 
 
 # ------------------------------------------------------------------------------------ norm
+@_timed
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
     """resid (+= delta); out = weight * (x / sqrt(mean(x^2) + eps)). With `rows` (int32 [R]) only
@@ -138,6 +202,7 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
              _ptr(out), _code(out, op), R, h, float(eps), _stream()), op)
 
 
+@_timed
 def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
     """resid += delta in float32."""
     op = "add_residual"
@@ -150,6 +215,7 @@ def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------------ rope + cache write
+@_timed
 def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], positions: torch.Tensor,
                   slots: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                   kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
@@ -195,6 +261,7 @@ def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.
 
 
 # ------------------------------------------------------------------------------------ swiglu
+@_timed
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
     op = "swiglu"
@@ -210,6 +277,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------------ matrix products
+@_timed
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA chains in k order; no tensor cores)."""
     op = "gemm_f32"
@@ -241,15 +309,21 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise ShapeError(op, f"operands must both be float32 or both bfloat16, got {a.dtype} and {w.dtype}")
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or out.shape != (a.shape[0], w.shape[0]):
         raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
+    _library_gemm_bf16(a, w, out)
+
+
+@_timed
+def _library_gemm_bf16(a, w, out):
     if out.dtype == torch.bfloat16:
         torch.mm(a, w.t(), out=out)
-    elif out.dtype == torch.float32:
-        torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
     else:
-        raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
+        torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
 
 
 # ------------------------------------------------------------------------------------ attention
+@_timed
 def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                     block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
@@ -292,6 +366,7 @@ def pick_splits(vocab: int) -> int:
     return int(f(vocab))
 
 
+@_timed
 def pick_tokens(logits: torch.Tensor, out: torch.Tensor, nan_flags: torch.Tensor, scratch_val: torch.Tensor,
                 scratch_idx: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                 seeds: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> None:
@@ -322,4 +397,4 @@ def pick_tokens(logits: torch.Tensor, out: torch.Tensor, nan_flags: torch.Tensor
         _int32_vec(steps, R, op, "steps")
     f = _fn("sampling", "vob_pick_tokens", [_P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P])
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(seeds), _ptr(steps), splits,
-             _ptr(scratch_val), _ptr(scratch_idx), _ptr(nan_flags), _ptr(out), _stream()), op)
+             _ptr(scratch_val), _ptr(scratch_idx), _ptr(nan_flags), _ptr(out), _stream()), op, launches=2)

@@ -1,0 +1,161 @@
+"""Generation through the entry point: greedy against the plain implementation, batching and
+preemption that leave a request's tokens unchanged, temperature sampling, long decoding, the first
+tokens of a sequence, CUDA graphs on and off, and the errors of the reference's driver."""
+import pytest
+import torch
+
+from tests.plain import llama_plain as plain
+from tests.util import TINY, TOL, make_model_dir, max_rel_diff, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def llm_for(model_dir, dtype, page, **kw):
+    from vllm_oxide_b200.engine import LLM
+    args = dict(max_batch_tokens=64, max_seqs=8, max_model_len=256, block_size=page, num_pages=256 // page * 4)
+    args.update(kw)
+    return LLM(model_dir, dtype=dtype, **args)
+
+
+def sp(**kw):
+    from vllm_oxide_b200.sampling import SamplingParams
+    return SamplingParams(**kw)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_equals_plain_in_f32(tmp_path_factory, name):
+    cfg, _, page = TINY[name]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), name)
+    pc, pt = plain.load_model(d)
+    llm = llm_for(d, "float32", page)
+    from vllm_oxide_b200.engine import Generator
+    gen = Generator(llm)
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 40]}[name]
+    for i, L in enumerate(lengths):
+        prompt = random_tokens(L, cfg.vocab_size, 10 + i)
+        out = gen.greedy(prompt, 8, None, capture=(0, 1, 7))
+        want = plain.greedy_generate(pc, pt, prompt, 8)
+        assert out.tokens == want
+        seq = prompt + want
+        for gi, logits in out.captured:
+            ref = plain.forward(pc, pt, seq[:L + gi])[-1]
+            assert max_rel_diff(logits, ref) <= TOL[torch.float32]
+        assert out.prefill_time > 0 and out.decode_time > 0
+    # the same engine and pool serve call after call (crates/engine/src/generate.rs:165-173)
+    assert llm.runner.manager.num_free_pages(0) == llm.runner.manager.num_pages(0)
+
+
+def test_stop_token_is_kept_and_ends_the_output(tmp_path_factory):
+    cfg, _, page = TINY["A"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "A")
+    from vllm_oxide_b200.engine import Generator
+    gen = Generator(llm_for(d, "float32", page))
+    prompt = random_tokens(12, cfg.vocab_size, 77)
+    full = gen.greedy(prompt, 10).tokens
+    stop = full[3]
+    cut = gen.greedy(prompt, 10, stop).tokens
+    assert cut == full[:full.index(stop) + 1]           # crates/engine/src/generate.rs:176-184
+
+
+def test_driver_errors(tmp_path_factory):
+    from vllm_oxide_b200.engine import Generator
+    from vllm_oxide_b200.errors import CapacityError, ShapeError
+    cfg, _, page = TINY["A"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "A")
+    gen = Generator(llm_for(d, "float32", page, max_model_len=32))
+    with pytest.raises(ShapeError):                      # crates/engine/src/generate.rs:55-60
+        gen.greedy([], 4)
+    with pytest.raises(ShapeError):
+        gen.greedy([1, 2], 0)
+    with pytest.raises(CapacityError):                   # crates/engine/src/generate.rs:187-193
+        gen.greedy(list(range(30)), 4)
+    gen.greedy(list(range(30)), 3)                       # 30 + 3 - 1 = 32 fits exactly
+    with pytest.raises(ShapeError, match="vocabulary"):
+        gen.greedy([cfg.vocab_size], 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batched_equals_alone_and_graphs_change_nothing(tmp_path_factory, dtype):
+    """Tokens of a request do not depend on what is scheduled beside it (CLAUDE.md:72), nor on
+    whether its decode steps are replayed from CUDA graphs, in either dtype."""
+    cfg, _, page = TINY["B"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "B")
+    prompts = [random_tokens(L, cfg.vocab_size, 200 + i) for i, L in enumerate([1, 9, 40, 70, 23, 3])]
+    params = [sp(max_new_tokens=12, temperature=0.0 if i % 2 == 0 else 0.7, seed=40 + i, stop_token_ids=()) for i in range(6)]
+    alone = []
+    solo = llm_for(d, dtype, page, cuda_graphs=False)
+    for p, s in zip(prompts, params):
+        alone.append(solo.generate([p], s)[0].token_ids)
+    for graphs in (False, True):
+        llm = llm_for(d, dtype, page, cuda_graphs=graphs, prefill_chunk=16, max_batch_tokens=40)
+        outs = llm.generate(prompts, params)
+        assert [o.token_ids for o in outs] == alone, f"graphs={graphs}"
+        assert all(o.finish_reason == "length" for o in outs)
+        assert llm.stats["graph_steps"] > 0 if graphs else llm.stats["graph_steps"] == 0
+        assert llm.runner.manager.check_invariants() == ""
+
+
+def test_temperature_sampling_equals_plain_rule(tmp_path_factory):
+    """Seeded temperature sampling (BASELINE tiny B: 0.7) picks what the plain Gumbel-max rule
+    picks from the plain logits, as long as the pick is not a near-tie."""
+    cfg, _, page = TINY["B"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "B")
+    pc, pt = plain.load_model(d)
+    llm = llm_for(d, "float32", page)
+    prompt = random_tokens(9, cfg.vocab_size, 5)
+    out = llm.generate([prompt], sp(max_new_tokens=6, temperature=0.7, seed=(3 << 32) | 12345, stop_token_ids=()))[0]
+    seq = list(prompt)
+    for i, tok in enumerate(out.token_ids):
+        logits = plain.forward(pc, pt, seq)[-1]
+        assert tok == plain.temperature_pick(logits.float(), 0.7, (3 << 32) | 12345, i)
+        seq.append(tok)
+    other = llm.generate([prompt], sp(max_new_tokens=6, temperature=0.7, seed=999, stop_token_ids=()))[0]
+    assert other.token_ids != out.token_ids
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_recomputes_and_changes_no_token(tmp_path_factory, dtype):
+    cfg, _, page = TINY["A"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "A")
+    prompts = [random_tokens(L, cfg.vocab_size, 300 + i) for i, L in enumerate([30, 28, 25, 31])]
+    params = sp(max_new_tokens=40, stop_token_ids=())
+    roomy = llm_for(d, dtype, page, cuda_graphs=False).generate(prompts, params)
+    # 12 pages of 16 = 192 tokens for four requests that grow to ~70 each: someone must give way
+    tight = llm_for(d, dtype, page, num_pages=12, cuda_graphs=False)
+    outs = tight.generate(prompts, params)
+    assert tight.stats["preemptions"] > 0 and sum(o.preemptions for o in outs) == tight.stats["preemptions"]
+    if dtype == "float32":
+        assert [o.token_ids for o in outs] == [o.token_ids for o in roomy]
+    else:
+        # bfloat16: recomputing a generated token as part of a prompt portion may round differently;
+        # near-ties can flip, so compare by how many requests agree exactly
+        same = sum(a.token_ids == b.token_ids for a, b in zip(outs, roomy))
+        assert same >= 2
+    assert tight.runner.manager.num_free_pages(0) == 12 and tight.runner.manager.check_invariants() == ""
+
+
+def test_request_too_large_for_the_pool_fails_cleanly(tmp_path_factory):
+    from vllm_oxide_b200.errors import CapacityError
+    cfg, _, page = TINY["A"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "A")
+    llm = llm_for(d, "float32", page, num_pages=2)
+    with pytest.raises(CapacityError):
+        llm.generate([list(range(40))], sp(max_new_tokens=4))
+    out = llm.generate([list(range(20))], sp(max_new_tokens=4, stop_token_ids=()))[0]
+    assert out.finish_reason == "length" and len(out.token_ids) == 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_long_decoding_and_first_tokens(tmp_path_factory, dtype):
+    """220 single-token steps from an empty cache (the first tokens of a sequence are steps like
+    any other), each position compared with the plain implementation."""
+    from tests.test_gpu_replay import _session, run_trace, check
+    cfg, _, page = TINY["A"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "A")
+    toks = random_tokens(220, cfg.vocab_size, 8)
+    s = _session(d, dtype, 256, page)
+    steps = [{"step": i, "entries": [{"id": "x", "tokens": [toks[i]], "want": [0]}], "end": ["x"] if i == 219 else []}
+             for i in range(220)]
+    got = run_trace(s, steps)
+    assert len(got) == 220
+    check(got, d, {"x": toks}, dtype, "token by token")

@@ -1,0 +1,326 @@
+"""Each kernel alone against the plain implementation's function for the same op, at sizes other
+than the engine's tiny models: odd widths, head sizes in steps of 16, odd head and group counts."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import llama_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+# elementwise results: float32 to rounding; bfloat16 outputs are rounded once to 8 bits (2^-9 relative)
+ETOL = {torch.float32: 2e-6, torch.bfloat16: 2 ** -8}
+
+
+def rel(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+
+def K():
+    from vllm_oxide_b200 import kernels
+    return kernels
+
+
+def test_embed():
+    g = torch.Generator().manual_seed(0)
+    for dt in DT:
+        table = torch.randn(301, 72, generator=g).to(dt).to(DEV)
+        toks = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+        out = torch.empty(5, 72, dtype=torch.float32, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        K().embed(table, toks, out, flag)
+        want = plain.embedding(table.double().cpu(), toks.tolist())
+        assert torch.equal(out.double().cpu(), want) and int(flag) == 0
+        bad = torch.tensor([1, 301, 2, 3, 4], dtype=torch.int32, device=DEV)
+        K().embed(table, bad, out, flag)
+        assert int(flag) == 1 and float(out[1].abs().max()) == 0.0      # out of range: zeros and a raised flag
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("h", [19, 100, 2048, 4100])
+def test_add_rmsnorm(dt, h):
+    g = torch.Generator().manual_seed(h)
+    T = 7
+    resid = torch.randn(T, h, generator=g).to(DEV)
+    delta = (torch.randn(T, h, generator=g) * 0.5).to(dt).to(DEV)
+    w = (1 + 0.3 * torch.randn(h, generator=g)).to(DEV)
+    eps = 3e-5
+    r0 = resid.clone()
+    out = torch.empty(T, h, dtype=dt, device=DEV)
+    K().add_rmsnorm(resid, delta, w, eps, out)
+    x = r0.double().cpu() + delta.double().cpu()
+    assert rel(resid, x) <= 2e-7                                       # the residual sum stays float32
+    assert rel(out, plain.rms_norm(x, w.double().cpu(), eps)) <= ETOL[dt]
+    # without delta, and with a row list: the residual is left alone
+    r1 = resid.clone()
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, h, dtype=dt, device=DEV)
+    K().add_rmsnorm(resid, delta, w, eps, out2, rows)
+    assert torch.equal(resid, r1)
+    x2 = (r1.double().cpu() + delta.double().cpu())[[6, 0, 3]]
+    assert rel(out2, plain.rms_norm(x2, w.double().cpu(), eps)) <= ETOL[dt]
+    out3 = torch.empty(T, h, dtype=dt, device=DEV)
+    K().add_rmsnorm(resid, None, w, eps, out3)
+    assert rel(out3, plain.rms_norm(r1.double().cpu(), w.double().cpu(), eps)) <= ETOL[dt]
+
+
+def test_rmsnorm_refuses_too_wide_rows():
+    from vllm_oxide_b200.errors import ShapeError
+    with pytest.raises(ShapeError, match="limit"):
+        K().add_rmsnorm(torch.zeros(1, 20000, device=DEV), None, torch.ones(20000, device=DEV), 1e-5,
+                        torch.zeros(1, 20000, device=DEV))
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("I", [5, 224, 1000])
+def test_swiglu(dt, I):
+    g = torch.Generator().manual_seed(I)
+    gu = (torch.randn(6, 2 * I, generator=g) * 3).to(dt).to(DEV)
+    out = torch.empty(6, I, dtype=dt, device=DEV)
+    K().swiglu(gu, out)
+    want = plain.swiglu(gu[:, :I].double().cpu(), gu[:, I:].double().cpu())
+    assert rel(out, want) <= ETOL[dt]
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 1, 1), (7, 37, 21), (64, 64, 16), (65, 130, 257), (3, 1000, 96), (200, 50, 2048)])
+def test_gemm_f32(M, N, K_):
+    # odd sizes against the 64x64x16 tiling (the reference tests 7x21 -> 37: crates/engine/src/backend/cpu/tests.rs:37-59)
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    a = torch.randn(M, K_, generator=g).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(DEV)
+    out = torch.empty(M, N, device=DEV)
+    K().gemm_f32(a, w, out)
+    # one chain of K float32 FMAs per element: rounding errors of 2^-24 each add up like a random
+    # walk, sqrt(K) * 2^-24 of the running sum; twice that as the bound (1e-6 at the reference's K = 21)
+    tol = max(1e-6, 2.0 ** -23 * math.sqrt(K_))
+    assert rel(out, plain.linear(a.double().cpu(), w.double().cpu())) <= tol
+    # a row's value does not depend on the rows around it: bitwise
+    out1 = torch.empty(1, N, device=DEV)
+    K().gemm_f32(a[M - 1:M], w, out1)
+    assert torch.equal(out1[0], out[M - 1])
+    # strided views (a column slice of a wider buffer)
+    wide = torch.randn(M, K_ + 8, generator=g).to(DEV)
+    outw = torch.zeros(M, N + 4, device=DEV)
+    K().gemm_f32(wide[:, 4:4 + K_], w, outw[:, 2:2 + N])
+    assert rel(outw[:, 2:2 + N], plain.linear(wide[:, 4:4 + K_].double().cpu(), w.double().cpu())) <= tol
+    assert float(outw[:, :2].abs().max()) == 0.0 and float(outw[:, 2 + N:].abs().max()) == 0.0
+
+
+def test_gemm_f32_shape_errors():
+    from vllm_oxide_b200.errors import ShapeError
+    with pytest.raises(ShapeError):
+        K().gemm_f32(torch.zeros(2, 3, device=DEV), torch.zeros(4, 5, device=DEV), torch.zeros(2, 4, device=DEV))
+    with pytest.raises(ShapeError):
+        K().gemm_f32(torch.zeros(2, 3, device=DEV), torch.zeros(4, 3, device=DEV), torch.zeros(2, 5, device=DEV))
+
+
+def test_linear_bf16_library_product():
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(9, 200, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(77, 200, generator=g).to(torch.bfloat16).to(DEV)
+    want = plain.linear(a.double().cpu(), w.double().cpu())
+    o32 = torch.empty(9, 77, dtype=torch.float32, device=DEV)
+    K().linear(a, w, o32)
+    assert rel(o32, want) <= 1e-5                                      # bf16 inputs are exact; float32 accumulation
+    o16 = torch.empty(9, 77, dtype=torch.bfloat16, device=DEV)
+    K().linear(a, w, o16)
+    assert rel(o16, want) <= 2 ** -8
+
+
+def _paged_case(dt, H, KV, hd, page, seqs, seed, scale_key=None):
+    """seqs: list of (context_len, num_new). Returns tensors for the kernel and per-sequence q/k/v."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-(c + n) // page) for c, n in seqs) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()          # shuffled, non-identity tables
+    kc = torch.randn(total_pages, KV, page, hd, generator=g).to(dt)   # stale values everywhere
+    vc = torch.randn(total_pages, KV, page, hd, generator=g).to(dt)
+    max_pages = max(-(-(c + n) // page) for c, n in seqs) + 1
+    bt = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)
+    qs, ks, vs, row_seq, positions = [], [], [], [], []
+    for s, (c, n) in enumerate(seqs):
+        L = c + n
+        k = torch.randn(L, KV * hd, generator=g).to(dt)
+        v = torch.randn(L, KV * hd, generator=g).to(dt)
+        q = torch.randn(L, H * hd, generator=g).to(dt)
+        if scale_key is not None:
+            j = scale_key(L)
+            k[j] *= 6.0                       # one key stands out: a wrong or missing key shows
+        np_ = -(-L // page)
+        for i in range(np_):
+            bt[s, i] = perm.pop()
+        for p in range(L):
+            pg, off = int(bt[s, p // page]), p % page
+            kc[pg, :, off, :] = k[p].view(KV, hd)
+            vc[pg, :, off, :] = v[p].view(KV, hd)
+        qs.append(q), ks.append(k), vs.append(v)
+        row_seq += [s] * n
+        positions += list(range(c, L))
+    qrows = torch.cat([q[c:] for q, (c, n) in zip(qs, seqs)])
+    return (qrows, kc, vc, bt, torch.tensor(row_seq, dtype=torch.int32), torch.tensor(positions, dtype=torch.int32),
+            qs, ks, vs)
+
+
+ATOL = {torch.float32: 1e-5, torch.bfloat16: 2 ** -7}      # reference: 1e-5 relative for paged attention (cpu/tests.rs:161-334)
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("H,KV,hd,page", [(6, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (8, 2, 64, 16), (4, 2, 128, 16),
+                                          (2, 1, 256, 32), (7, 7, 80, 8)])
+def test_paged_attention_prefill_and_decode_shapes(dt, H, KV, hd, page):
+    # (context, new): mid-page, zero context, page edge, a decode row, a long one
+    seqs = [(5, 6), (0, 3), (2 * page, page), (37, 1), (0, 1), (3 * page - 1, 2)]
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=hd + H)
+    out = torch.empty_like(qrows).to(DEV)
+    K().paged_attention(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), row_seq.to(DEV), pos.to(DEV),
+                        H, KV, hd, 1.0 / math.sqrt(hd))
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd)[c:]
+        got = out[r:r + n]
+        assert rel(got, want) <= ATOL[dt], (s, c, n)
+        r += n
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_paged_attention_far_key_among_hundreds(dt):
+    """One key far back dominates the softmax; it must be found at any distance, across pages."""
+    H, KV, hd, page = 4, 2, 64, 16
+    seqs = [(700, 1), (0, 333), (511, 2)]
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=1, scale_key=lambda L: 3)
+    out = torch.empty_like(qrows).to(DEV)
+    K().paged_attention(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), row_seq.to(DEV), pos.to(DEV),
+                        H, KV, hd, 1.0 / math.sqrt(hd))
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd)[c:]
+        assert rel(out[r:r + n], want) <= ATOL[dt]
+        r += n
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 40])
+def test_paged_attention_window_edge(dt, window):
+    H, KV, hd, page = 4, 2, 32, 8
+    seqs = [(0, 50), (44, 3), (window, 1), (max(window - 1, 0), 1)]
+    # the key just outside the window stands out: reading it would change everything
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=window,
+                                                             scale_key=lambda L: max(L - 1 - window, 0))
+    out = torch.empty_like(qrows).to(DEV)
+    K().paged_attention(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), row_seq.to(DEV), pos.to(DEV),
+                        H, KV, hd, 0.3, window)
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd, window=window, scale=0.3)[c:]
+        assert rel(out[r:r + n], want) <= ATOL[dt]
+        r += n
+
+
+def test_paged_attention_refuses_bad_sizes():
+    from vllm_oxide_b200.errors import ShapeError
+    q = torch.zeros(1, 4 * 20, device=DEV)
+    kc = torch.zeros(2, 2, 8, 20, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ShapeError, match="head_dim 20"):
+        K().paged_attention(q, q.clone(), kc, kc, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 4, 2, 20, 1.0)
+    q = torch.zeros(1, 3 * 16, device=DEV)
+    kc = torch.zeros(2, 2, 8, 16, device=DEV)
+    with pytest.raises(ShapeError, match="multiple"):
+        K().paged_attention(q, q.clone(), kc, kc, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 3, 2, 16, 1.0)
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("H,KV,hd,page", [(6, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (32, 8, 64, 16)])
+def test_rope_kv_write(dt, H, KV, hd, page):
+    g = torch.Generator().manual_seed(hd)
+    T = 11
+    cfg = {"head_dim": hd, "hidden_size": H * hd, "num_attention_heads": H, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 64}}
+    inv = plain.rope_inv_freq(cfg)
+    qkv = torch.randn(T, (H + 2 * KV) * hd, generator=g).to(dt)
+    positions = [0, 1, 2, 63, 64, 65, 1000, 4095, 7, 7, 300]
+    pages = 9
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    slots[4] = -1                                                       # this token writes nothing
+    kc = torch.full((pages, KV, page, hd), 7.0).to(dt)
+    vc = torch.full((pages, KV, page, hd), 7.0).to(dt)
+    d_qkv, d_kc, d_vc = qkv.to(DEV), kc.to(DEV), vc.to(DEV)
+    q, k, v = d_qkv[:, :H * hd], d_qkv[:, H * hd:(H + KV) * hd], d_qkv[:, (H + KV) * hd:]
+    K().rope_kv_write(q, k, v, torch.tensor(positions, dtype=torch.int32, device=DEV), slots.to(DEV), inv.to(DEV),
+                      d_kc, d_vc, H, KV, hd)
+    wq = plain.rope(qkv[:, :H * hd].double(), positions, inv, hd)
+    wk = plain.rope(qkv[:, H * hd:(H + KV) * hd].double(), positions, inv, hd)
+    tol = 3e-6 if dt == torch.float32 else 2 ** -8
+    assert rel(q, wq) <= tol and rel(k, wk) <= tol
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        pg, off = s // page, s % page
+        assert rel(d_kc[pg, :, off, :].reshape(-1), wk[t]) <= tol
+        assert torch.equal(d_vc[pg, :, off, :].reshape(-1).cpu(), qkv[t, (H + KV) * hd:])
+    written = {int(s) for s in slots if s >= 0}
+    for s in range(pages * page):
+        if s not in written:
+            assert float((d_kc[s // page, :, s % page, :].float() - 7.0).abs().max()) == 0.0     # nothing else is touched
+
+
+def test_pick_tokens_greedy_cases():
+    # crates/engine/src/backend/cpu/tests.rs:129-144: ties -> first, all equal -> 0, NaN -> error
+    V = 10007
+    logits = torch.full((5, V), -1.0, device=DEV)
+    logits[0, 5000] = 5.0
+    logits[0, 9000] = 5.0
+    logits[1] = 0.0
+    logits[2, V - 1] = 3.0
+    logits[3, 0] = 2.0
+    logits[4, 77] = float("nan")
+    k = K()
+    sp = k.pick_splits(V)
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(5, dtype=torch.int32, device=DEV)
+    k.pick_tokens(logits, out, flags, torch.empty(5 * sp, device=DEV), torch.empty(5 * sp, dtype=torch.int32, device=DEV))
+    assert out.tolist() == [5000, 0, V - 1, 0, -1]
+    assert flags.tolist() == [0, 0, 0, 0, 0]          # the flag is cleared once it has been turned into -1
+    want = [plain.argmax_first(r) for r in logits[:4].double().cpu()]
+    assert out.tolist()[:4] == want
+
+
+def test_pick_tokens_temperature_matches_plain_and_law():
+    V = 997
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(6, V, generator=g) * 2).to(DEV)
+    temps = torch.tensor([0.7, 0.0, 1.3, 0.7, 0.7, 0.2], device=DEV)
+    seeds = torch.tensor([[1, 0], [2, 0], [3, 7], [1, 0], [9, 1], [4, 4]], dtype=torch.int32, device=DEV)
+    steps = torch.tensor([0, 5, 2, 1, 0, 3], dtype=torch.int32, device=DEV)
+    k = K()
+    sp = k.pick_splits(V)
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    k.pick_tokens(logits, out, torch.zeros(6, dtype=torch.int32, device=DEV), torch.empty(6 * sp, device=DEV),
+                  torch.empty(6 * sp, dtype=torch.int32, device=DEV), temps, seeds, steps)
+    for r in range(6):
+        seed = (int(seeds[r, 1]) << 32) | int(seeds[r, 0])
+        assert int(out[r]) == plain.temperature_pick(logits[r].double().cpu(), float(temps[r]), seed, int(steps[r]))
+    # the law: many steps of one request over small logits follow softmax(logits / t)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, -30.0]], device=DEV).repeat(64, 1)
+    n, counts = 0, torch.zeros(5)
+    for it in range(40):
+        st = torch.arange(it * 64, it * 64 + 64, dtype=torch.int32, device=DEV)
+        o = torch.zeros(64, dtype=torch.int32, device=DEV)
+        k.pick_tokens(small, o, torch.zeros(64, dtype=torch.int32, device=DEV), torch.empty(64, device=DEV),
+                      torch.empty(64, dtype=torch.int32, device=DEV), torch.full((64,), 0.7, device=DEV),
+                      torch.tensor([[11, 3]] * 64, dtype=torch.int32, device=DEV), st)
+        counts += torch.bincount(o.cpu(), minlength=5).float()
+        n += 64
+    p = torch.softmax(small[0].cpu().double() / 0.7, 0)
+    for i in range(5):
+        assert abs(float(counts[i]) / n - float(p[i])) < 4 * math.sqrt(float(p[i]) * (1 - float(p[i])) / n) + 2e-3
+
+
+def test_cpu_tensors_are_refused():
+    from vllm_oxide_b200.errors import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        K().gemm_f32(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))

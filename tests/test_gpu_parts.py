@@ -1,0 +1,292 @@
+"""Each part alone against the plain implementation's function, driven through the same
+StepContext the engine builds; and models that use the generality of the parts: a window, a
+layer run twice, a layer that reads another layer's cache."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import llama_plain as plain
+from tests.util import TOL, max_rel_diff
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+class Harness:
+    """A cache manager, device pools and step contexts for parts under test."""
+
+    def __init__(self, dtype, page=8, pages=64, max_rows=256, max_seqs=4, groups=(("full", 0),), kv=(2, 16), caches=1):
+        from vllm_oxide_b200.csrc.build import runtime_module
+        from vllm_oxide_b200.parts import Workspace
+        self.rt = rt = runtime_module()
+        self.dtype, self.page, self.max_rows, self.max_seqs = dtype, page, max_rows, max_seqs
+        self.mgr = rt.CacheManager(page, [rt.GroupSpec(rt.WINDOW if k == "window" else rt.FULL, w, pages) for k, w in groups], max_seqs)
+        self.max_pages = 64
+        self.layout = rt.step_layout(max_rows, max_seqs, max_rows, len(groups), self.max_pages)
+        self.dev = torch.zeros(self.layout["total"], dtype=torch.int32, device=DEV)
+        self.ws = Workspace(64 << 20, DEV)
+        self.kv = [torch.randn(2, pages, kv[0], page, kv[1], device=DEV).to(dtype) for _ in range(caches)]   # stale contents
+
+    def ctx(self, entries):
+        """entries: [(request id, tokens)] -> StepContext (pages reserved; commit with done())."""
+        from vllm_oxide_b200.parts import StepContext
+        es = []
+        for rid, toks in entries:
+            if not self.mgr.has(rid):
+                self.mgr.admit(rid)
+            assert self.mgr.reserve(rid, len(toks))
+            es.append(self.rt.StepEntry(rid, list(toks), [len(toks) - 1]))
+        a = self.rt.build_step(self.mgr, es, self.max_rows, self.max_seqs, self.max_rows, self.max_pages, 1 << 30)
+        self.dev.copy_(torch.from_numpy(a.data()))
+        self.last = a
+        L, d, T, S = self.layout, self.dev, a.rows, a.seqs
+        G = len(L["slot_mapping"])
+        self.ws.reset()
+        v = lambda k, n: d[L[k]:L[k] + n]
+        return StepContext(rows=T, seqs=S, dtype=self.dtype, tokens=v("tokens", T), positions=v("positions", T),
+                           row_seq=v("row_seq", T), seq_starts=v("seq_starts", S + 1), context_lens=v("context_lens", S),
+                           seq_lens=v("seq_lens", S), state_slots=v("state_slots", S), logit_rows=v("logit_rows", self.max_rows),
+                           slot_mapping=[d[L["slot_mapping"][g]:L["slot_mapping"][g] + T] for g in range(G)],
+                           block_tables=[d[L["block_tables"][g]:L["block_tables"][g] + self.max_seqs * self.max_pages]
+                                         .view(self.max_seqs, self.max_pages) for g in range(G)],
+                           workspace=self.ws, max_new=a.max_new, max_seq_len=a.max_seq_len, host=a)
+
+    def done(self):
+        for rid, n in zip(self.last.ids, self.last.new_counts):
+            self.mgr.commit(rid, n)
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_rmsnorm_part(dt):
+    from vllm_oxide_b200.parts import RMSNorm
+    h = Harness(dt)
+    g = torch.Generator().manual_seed(1)
+    w = 1 + 0.2 * torch.randn(50, generator=g)
+    part = RMSNorm(w.to(torch.bfloat16), 2e-6, DEV)                 # stored bf16, read as float32
+    ctx = h.ctx([(1, [0] * 9)])
+    resid = torch.randn(9, 50, generator=g).to(DEV)
+    delta = torch.randn(9, 50, generator=g).to(dt).to(DEV)
+    want_sum = resid.double().cpu() + delta.double().cpu()
+    out = part.forward(resid, delta, ctx)
+    assert max_rel_diff(resid.cpu(), want_sum) < 1e-6
+    assert max_rel_diff(out.cpu(), plain.rms_norm(want_sum, w.to(torch.bfloat16).double(), 2e-6)) <= (2e-6 if dt == torch.float32 else 2 ** -8)
+
+
+def test_rotary_part_tables():
+    from vllm_oxide_b200.config import RopeScaling
+    from vllm_oxide_b200.parts import Rotary
+    for hd, theta, sc in [(64, 500000.0, RopeScaling(32.0, 1.0, 4.0, 8192)), (32, 10000.0, None), (48, 20000.0, RopeScaling(4.0, 1.0, 2.0, 32))]:
+        r = Rotary(hd, theta, sc, DEV)
+        cfg = {"head_dim": hd, "rope_theta": theta, "hidden_size": hd, "num_attention_heads": 1,
+               "rope_scaling": None if sc is None else sc.to_json()}
+        assert torch.equal(r.inv_freq.cpu(), plain.rope_inv_freq(cfg))
+    with pytest.raises(ValueError):
+        Rotary(33, 1e4, None, DEV)
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_swiglu_part(dt):
+    from vllm_oxide_b200.parts import SwiGLU
+    h = Harness(dt)
+    g = torch.Generator().manual_seed(2)
+    wg, wu, wd = (torch.randn(s, generator=g).mul(0.2).to(torch.bfloat16) for s in ((37, 24), (37, 24), (24, 37)))
+    part = SwiGLU(wg, wu, wd, dt, DEV)
+    ctx = h.ctx([(1, [0] * 5)])
+    x = torch.randn(5, 24, generator=g).to(dt).to(DEV)
+    out = part.forward(x, ctx)
+    want = plain.feed_forward(x.double().cpu(), wg.double(), wu.double(), wd.double())
+    assert max_rel_diff(out.cpu(), want) <= (1e-5 if dt == torch.float32 else 3e-2)
+    with pytest.raises(ValueError):
+        SwiGLU(wg, wu[:5], wd, dt, DEV)
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_embedding_and_head_parts(dt):
+    from vllm_oxide_b200.parts import Embedding, LMHead
+    h = Harness(dt)
+    g = torch.Generator().manual_seed(3)
+    table = torch.randn(61, 40, generator=g).to(torch.bfloat16)
+    emb = Embedding(table, dt, DEV)
+    toks = [60, 0, 7, 7]
+    ctx = h.ctx([(1, toks)])
+    resid = emb.forward(ctx)
+    assert torch.equal(resid.cpu().double(), plain.embedding(table.double(), toks))
+    head = LMHead(emb.table)                                           # tied: the same tensor
+    assert head.weight.data_ptr() == emb.table.data_ptr()
+    x = torch.randn(4, 40, generator=g).to(dt).to(DEV)
+    logits = head.forward(x, torch.empty(4, 61, dtype=torch.float32, device=DEV))
+    assert max_rel_diff(logits.cpu(), plain.linear(x.double().cpu(), table.double())) <= 1e-5
+
+
+def _attn_weights(g, hidden, H, KV, hd, std=0.3):
+    mk = lambda *s: torch.randn(*s, generator=g).mul(std).to(torch.bfloat16)
+    return mk(H * hd, hidden), mk(KV * hd, hidden), mk(KV * hd, hidden), mk(hidden, H * hd)
+
+
+def _plain_attention_block(x, wq, wk, wv, wo, H, KV, hd, inv, window=None, scale=None, positions=None):
+    positions = list(range(x.shape[0])) if positions is None else positions
+    q = plain.linear(x, wq.double())
+    k = plain.linear(x, wk.double())
+    if inv is not None:
+        q, k = plain.rope(q, positions, inv, hd), plain.rope(k, positions, inv, hd)
+    v = plain.linear(x, wv.double())
+    return plain.linear(plain.causal_attention(q, k, v, H, KV, hd, window=window, scale=scale), wo.double())
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("window,rope,scale", [(None, True, None), (11, True, 0.2), (None, False, None)])
+def test_attention_part_in_portions(dt, window, rope, scale):
+    """The mixer alone: a sequence fed in portions (cache continuation, page edges) equals the
+    plain whole-sequence block; with a window, without positions, with its own scale."""
+    from vllm_oxide_b200.config import RopeScaling
+    from vllm_oxide_b200.parts import Attention, LayerCache, Rotary
+    hidden, H, KV, hd, page = 40, 6, 2, 16, 8
+    g = torch.Generator().manual_seed(4)
+    wq, wk, wv, wo = _attn_weights(g, hidden, H, KV, hd)
+    rot = Rotary(hd, 500000.0, RopeScaling(8.0, 1.0, 4.0, 16), DEV) if rope else None
+    part = Attention(wq, wk, wv, wo, H, KV, hd, position=rot, window=window, scale=scale, dtype=dt, device=DEV)
+    spec = part.cache_spec()
+    assert (spec.kind, spec.window) == (("window", window) if window else ("full", 0))
+    h = Harness(dt, page=page, groups=((spec.kind, spec.window),), kv=(KV, hd))
+    cache = LayerCache(h.kv[0][0], h.kv[0][1], 0, True)
+    T = 45
+    x = torch.randn(T, hidden, generator=g).to(dt)
+    inv = plain.rope_inv_freq({"head_dim": hd, "hidden_size": hidden, "num_attention_heads": H, "rope_theta": 500000.0,
+                               "rope_scaling": RopeScaling(8.0, 1.0, 4.0, 16).to_json()}) if rope else None
+    want = _plain_attention_block(x.double(), wq, wk, wv, wo, H, KV, hd, inv, window, scale)
+    got, p = [], 0
+    for n in [8, 1, 7, 2, 16, 3, 1, 1, 6]:
+        ctx = h.ctx([(1, [0] * n)])
+        got.append(part.forward(x[p:p + n].to(DEV), ctx, cache).clone())
+        h.done()
+        p += n
+    assert p == T
+    tol = 2e-5 if dt == torch.float32 else 3e-2
+    assert max_rel_diff(torch.cat(got).cpu(), want) <= tol
+    if window:
+        table = h.mgr.block_table(1, 0)
+        assert table[0] == -1 and table[-1] >= 0            # pages the window has passed were given back
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_block_part_and_bad_sizes(dt):
+    from vllm_oxide_b200.parts import Attention, Block, LayerCache, RMSNorm, Rotary, SwiGLU
+    hidden, H, KV, hd, inter = 48, 3, 3, 16, 56
+    g = torch.Generator().manual_seed(5)
+    wq, wk, wv, wo = _attn_weights(g, hidden, H, KV, hd, 0.2)
+    wg, wu, wd = (torch.randn(s, generator=g).mul(0.2).to(torch.bfloat16) for s in ((inter, hidden), (inter, hidden), (hidden, inter)))
+    n1, n2 = (1 + 0.2 * torch.randn(hidden, generator=g) for _ in range(2))
+    rot = Rotary(hd, 10000.0, None, DEV)
+    block = Block(RMSNorm(n1, 1e-5, DEV), Attention(wq, wk, wv, wo, H, KV, hd, rot, dtype=dt, device=DEV),
+                  RMSNorm(n2, 1e-5, DEV), SwiGLU(wg, wu, wd, dt, DEV))
+    h = Harness(dt, kv=(KV, hd))
+    T = 13
+    ctx = h.ctx([(1, [0] * T)])
+    resid = torch.randn(T, hidden, generator=g).to(DEV)
+    pending = torch.randn(T, hidden, generator=g).to(dt).to(DEV)
+    x0 = resid.double().cpu() + pending.double().cpu()
+    out = ctx.alloc((T, hidden))
+    block.forward(resid, pending, ctx, LayerCache(h.kv[0][0], h.kv[0][1], 0, True), None, out)
+    inv = plain.rope_inv_freq({"head_dim": hd, "hidden_size": hidden, "num_attention_heads": H, "rope_theta": 10000.0})
+    x1 = x0 + _plain_attention_block(plain.rms_norm(x0, n1.double(), 1e-5), wq, wk, wv, wo, H, KV, hd, inv)
+    ff = plain.feed_forward(plain.rms_norm(x1, n2.double(), 1e-5), wg.double(), wu.double(), wd.double())
+    tol = 2e-5 if dt == torch.float32 else 3e-2
+    assert max_rel_diff(resid.cpu(), x1) <= tol           # the residual holds x + attention; ff is still pending
+    assert max_rel_diff(out.cpu(), ff) <= tol
+    with pytest.raises(ValueError, match="head_dim"):
+        Attention(wq, wk, wv, wo, H, KV, 24, rot, dtype=dt, device=DEV)
+    with pytest.raises(ValueError, match="multiple"):
+        Attention(wq, wk[:32], wv[:32], wo, 3, 2, 16, rot, dtype=dt, device=DEV)
+
+
+# ----------------------------------------------------------------------------- run order as data
+def _toy_model(dtype, schedule_kind):
+    """Two blocks of the framework's own parts, arranged by a schedule the Llama builder never
+    produces: 'twice' runs block 0, block 1, block 0 again (three caches); 'shared' lets block 1
+    (which has no k/v projections) read the cache block 0 wrote; 'window' gives block 1 a window."""
+    from vllm_oxide_b200.parts import (Attention, Block, Embedding, LayerCall, LMHead, ModelSpec, RMSNorm, Rotary, SwiGLU)
+    hidden, H, KV, hd, inter, V = 32, 4, 2, 16, 48, 50
+    g = torch.Generator().manual_seed(9)
+    mk = lambda *s: torch.randn(*s, generator=g).mul(0.25).to(torch.bfloat16)
+    W = {"emb": mk(V, hidden)}
+    blocks = []
+    rot = Rotary(hd, 10000.0, None, DEV)
+    for i in range(2):
+        shared = schedule_kind == "shared" and i == 1
+        W[f"q{i}"], W[f"o{i}"] = mk(H * hd, hidden), mk(hidden, H * hd)
+        W[f"k{i}"], W[f"v{i}"] = (None, None) if shared else (mk(KV * hd, hidden), mk(KV * hd, hidden))
+        W[f"g{i}"], W[f"u{i}"], W[f"d{i}"] = mk(inter, hidden), mk(inter, hidden), mk(hidden, inter)
+        W[f"n{i}a"], W[f"n{i}b"] = 1 + mk(hidden).float(), 1 + mk(hidden).float()
+        win = 9 if (schedule_kind == "window" and i == 1) else None
+        blocks.append(Block(RMSNorm(W[f"n{i}a"], 1e-5, DEV),
+                            Attention(W[f"q{i}"], W[f"k{i}"], W[f"v{i}"], W[f"o{i}"], H, KV, hd, rot, window=win, dtype=dtype, device=DEV),
+                            RMSNorm(W[f"n{i}b"], 1e-5, DEV), SwiGLU(W[f"g{i}"], W[f"u{i}"], W[f"d{i}"], dtype, DEV)))
+    W["nf"] = 1 + mk(hidden).float()
+    emb = Embedding(W["emb"], dtype, DEV)
+    schedule = {"twice": [LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2)],
+                "shared": [LayerCall(0, 0), LayerCall(1, 0, write=False)],
+                "window": [LayerCall(0, 0), LayerCall(1, 1)]}[schedule_kind]
+    spec = ModelSpec(embedding=emb, blocks=blocks, schedule=schedule, final_norm=RMSNorm(W["nf"], 1e-5, DEV),
+                     lm_head=LMHead(emb.table), hidden_size=hidden, vocab_size=V)
+    return spec, W, (hidden, H, KV, hd)
+
+
+def _toy_plain(W, dims, schedule_kind, tokens):
+    hidden, H, KV, hd = dims
+    inv = plain.rope_inv_freq({"head_dim": hd, "hidden_size": hidden, "num_attention_heads": H, "rope_theta": 10000.0})
+    x = plain.embedding(W["emb"].double(), tokens)
+    order = {"twice": [0, 1, 0], "shared": [0, 1], "window": [0, 1]}[schedule_kind]
+    for i in order:
+        wk, wv = (W["k0"], W["v0"]) if (schedule_kind == "shared" and i == 1) else (W[f"k{i}"], W[f"v{i}"])
+        normed = plain.rms_norm(x, W[f"n{i}a"].double(), 1e-5)
+        if schedule_kind == "shared" and i == 1:
+            # keys and values are the ones block 0 computed from ITS normed input
+            n0 = plain.rms_norm(plain.embedding(W["emb"].double(), tokens), W["n0a"].double(), 1e-5)
+            pos = list(range(len(tokens)))
+            q = plain.rope(plain.linear(normed, W["q1"].double()), pos, inv, hd)
+            k = plain.rope(plain.linear(n0, W["k0"].double()), pos, inv, hd)
+            v = plain.linear(n0, W["v0"].double())
+            att = plain.linear(plain.causal_attention(q, k, v, H, KV, hd), W["o1"].double())
+        else:
+            att = _plain_attention_block(normed, W[f"q{i}"], wk, wv, W[f"o{i}"], H, KV, hd, inv,
+                                         window=9 if (schedule_kind == "window" and i == 1) else None)
+        x = x + att
+        x = x + plain.feed_forward(plain.rms_norm(x, W[f"n{i}b"].double(), 1e-5), W[f"g{i}"].double(), W[f"u{i}"].double(), W[f"d{i}"].double())
+    return plain.linear(plain.rms_norm(x, W["nf"].double(), 1e-5), W["emb"].double())
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
+@pytest.mark.parametrize("kind", ["twice", "shared", "window"])
+def test_run_order_is_data(dt, kind):
+    """A layer named twice, a layer reading another layer's cache, and a window group beside a
+    full group run through the unchanged engine (runner, cache pools, step) and equal the plain
+    composition, whole and in portions."""
+    from vllm_oxide_b200.config import Architecture, EngineConfig
+    from vllm_oxide_b200.engine import ModelRunner
+    from vllm_oxide_b200.replay.trace import TraceSession
+    spec, W, dims = _toy_model(dt, kind)
+
+    class Cfg:
+        def to_dict(self):
+            return {"architectures": ["ToyOrder"]}
+    arch = Architecture("ToyOrder", Cfg, manifest=lambda c: {}, build=lambda c, w, ctx: spec)
+    eng = EngineConfig(max_batch_tokens=64, max_seqs=4, max_model_len=64, block_size=8, num_pages=16, dtype=dt, cuda_graphs=False)
+    runner = ModelRunner(Cfg(), {}, eng, arch)
+    assert runner.pools.num_groups == (2 if kind == "window" else 1)
+    assert len(runner.pools.kv) == {"twice": 3, "shared": 1, "window": 2}[kind]
+    s = TraceSession(runner)
+    toks = [(7 * i + 3) % 50 for i in range(41)]
+    want = _toy_plain(W, dims, kind, toks)
+    whole = s.run_step({"step": 0, "entries": [{"id": "a", "tokens": toks, "want": list(range(41))}], "end": ["a"]})
+    tol = TOL[dt]
+    assert max_rel_diff(whole, want) <= tol
+    got, p = [], 0
+    for i, n in enumerate([5, 11, 2, 1, 16, 6]):
+        got.append(s.run_step({"step": i, "entries": [{"id": "b", "tokens": toks[p:p + n], "want": list(range(n))}], "end": []}))
+        p += n
+    assert max_rel_diff(torch.cat(got), want) <= tol
+    if kind == "window":
+        assert runner.manager.block_table(s.ids["b"], 1)[0] == -1 and runner.manager.block_table(s.ids["b"], 0)[0] >= 0

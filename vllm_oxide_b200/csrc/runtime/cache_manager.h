@@ -148,7 +148,7 @@ public:
             int64_t room = (int64_t)r.tables[g].size() * page_size_ - r.len + (int64_t)pools_[g].num_free() * page_size_;
             best = std::min(best, room);
         }
-        return best == INT64_MAX ? 0 : best;
+        return best == INT64_MAX ? (int64_t)1 << 40 : best;    // no paged group: nothing limits it
     }
 
     // Hold pages for tokens [len, len + n_new) in every group; all groups or none.

@@ -74,12 +74,13 @@ def test_driver_errors(tmp_path_factory):
         gen.greedy([cfg.vocab_size], 2)
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_batched_equals_alone_and_graphs_change_nothing(tmp_path_factory, dtype):
+def test_batched_equals_alone_and_graphs_change_nothing(tmp_path_factory, dtype, name):
     """Tokens of a request do not depend on what is scheduled beside it (CLAUDE.md:72), nor on
     whether its decode steps are replayed from CUDA graphs, in either dtype."""
-    cfg, _, page = TINY["B"]
-    d = make_model_dir(tmp_path_factory.getbasetemp(), "B")
+    cfg, _, page = TINY[name]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), name)
     prompts = [random_tokens(L, cfg.vocab_size, 200 + i) for i, L in enumerate([1, 9, 40, 70, 23, 3])]
     params = [sp(max_new_tokens=12, temperature=0.0 if i % 2 == 0 else 0.7, seed=40 + i, stop_token_ids=()) for i in range(6)]
     alone = []

@@ -324,3 +324,70 @@ def test_cpu_tensors_are_refused():
     from vllm_oxide_b200.errors import KernelError
     with pytest.raises(KernelError, match="no CPU path"):
         K().gemm_f32(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))
+
+
+# ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
+def _starts_ctx(seqs):
+    starts, ctxs, r = [0], [], 0
+    for c, n in seqs:
+        r += n
+        starts.append(r)
+        ctxs.append(c)
+    return torch.tensor(starts, dtype=torch.int32, device=DEV), torch.tensor(ctxs, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("H,KV,hd,page", [(8, 2, 64, 16), (3, 1, 64, 8), (4, 4, 128, 32), (6, 2, 128, 16), (32, 8, 64, 64)])
+def test_attn_prefill_mma(H, KV, hd, page, window):
+    dt = torch.bfloat16
+    # portions that start mid-page, at a page edge, at zero; single tokens beside them; > one row tile
+    seqs = [(5, 6), (0, 3), (2 * page, page), (137, 1), (0, 1), (3 * page - 1, 2), (0, 150), (201, 77)]
+    sk = (lambda L: max(L - 1 - window, 0)) if window else (lambda L: min(3, L - 1))
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=hd + H + page, scale_key=sk)
+    starts, ctxs = _starts_ctx(seqs)
+    out = torch.empty_like(qrows).to(DEV)
+    K().attn_prefill_mma(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), starts, ctxs, len(seqs),
+                         max(n for _, n in seqs), H, KV, hd, 1.0 / math.sqrt(hd), window)
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd, window=window or None)[c:]
+        assert rel(out[r:r + n], want) <= 2 ** -6, (s, c, n)     # P is rounded to bfloat16 before P V: one more 2^-9 rounding per key
+        r += n
+
+
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("H,KV,hd,page", [(8, 2, 64, 16), (3, 1, 64, 8), (4, 4, 128, 32), (32, 2, 128, 16)])
+def test_attn_decode_mma(H, KV, hd, page, window, splits):
+    dt = torch.bfloat16
+    seqs = [(700, 1), (0, 1), (63, 1), (64, 1), (65, 1), (333, 1), (5, 1)]
+    sk = (lambda L: max(L - 1 - window, 0)) if window else (lambda L: min(3, L - 1))
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=hd + H + page + splits, scale_key=sk)
+    # a padding row: position -1, attends to nothing, must come out as zeros
+    qrows = torch.cat([qrows, torch.randn(1, H * hd).to(dt)])
+    pos = torch.cat([pos, torch.tensor([-1], dtype=torch.int32)])
+    bt = torch.cat([bt, bt[:1]])
+    out = torch.full_like(qrows, 7.0).to(DEV)
+    k = K()
+    scratch = torch.empty(max(1, k.attn_decode_scratch_floats(len(seqs) + 1, H, hd, splits)), device=DEV)
+    k.attn_decode_mma(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), pos.to(DEV), H, KV, hd,
+                      1.0 / math.sqrt(hd), window, splits, scratch)
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd, window=window or None)[c:]
+        assert rel(out[s:s + 1], want) <= 2 ** -6, (s, c)
+    assert float(out[len(seqs)].float().abs().max()) == 0.0
+
+
+def test_attn_mma_refusals():
+    from vllm_oxide_b200.errors import ShapeError
+    k = K()
+    assert k.attn_mma_supported(32, 8, 64, 16, True) and k.attn_mma_supported(24, 8, 128, 16, False)
+    assert not k.attn_mma_supported(4, 2, 48, 16, False) and not k.attn_mma_supported(4, 2, 64, 24, False)
+    assert not k.attn_mma_supported(34, 2, 64, 16, True) and k.attn_mma_supported(34, 2, 64, 16, False)
+    q = torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(2, 2, 16, 48, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ShapeError, match="not supported"):
+        k.attn_prefill_mma(q, q.clone(), kc, kc, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 4, 2, 48, 1.0)
+    with pytest.raises(ShapeError, match="bfloat16 only"):
+        k.attn_prefill_mma(q.float(), q.float(), kc.float(), kc.float(), torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 4, 2, 48, 1.0)

@@ -141,11 +141,11 @@ def _requests(vocab, lengths, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_four_ways_of_cutting(tmp_path_factory, name, dtype):
     cfg, _, page = TINY[name]
     model_dir = make_model_dir(tmp_path_factory.getbasetemp(), name)
-    lengths = {"A": [5, 17, 33, 100], "B": [1, 9, 40, 70], "C": [3, 64, 65, 90]}[name]
+    lengths = {"A": [5, 17, 33, 100], "B": [1, 9, 40, 70], "C": [3, 64, 65, 90], "D": [2, 63, 64, 127]}[name]
     reqs = _requests(cfg.vocab_size, lengths, 100)
     s = _session(model_dir, dtype, 128, page)
     w1 = check(run_trace(s, whole_steps(reqs)), model_dir, reqs, dtype, "whole")
@@ -157,7 +157,7 @@ def test_four_ways_of_cutting(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_mixed_batches_reuse_pages(tmp_path_factory, name, dtype):
     cfg, _, page = TINY[name]
     model_dir = make_model_dir(tmp_path_factory.getbasetemp(), name)

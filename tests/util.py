@@ -25,7 +25,13 @@ TINY_C = LlamaConfig(
     head_dim=48, vocab_size=301, max_position_embeddings=512, rms_norm_eps=3e-5, rope_theta=20000.0,
     rope_scaling=RopeScaling(4.0, 1.0, 2.0, 32), tie_word_embeddings=True)
 
-TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16)}   # config, std, page size
+# head_dim 64: the size the bfloat16 engine's tensor-core attention kernels take (Llama 3.2 1B's)
+TINY_D = LlamaConfig(
+    hidden_size=96, intermediate_size=160, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+    head_dim=64, vocab_size=200, max_position_embeddings=1024, rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=RopeScaling(32.0, 1.0, 4.0, 128), tie_word_embeddings=True)
+
+TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16)}   # config, std, page size
 
 
 def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:

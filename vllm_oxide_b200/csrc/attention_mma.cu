@@ -1,0 +1,509 @@
+// Tensor-core attention over the paged cache for the bfloat16 engine: one kernel for portions of
+// prompts (and mixed batches), one for steps of single decoded tokens.
+//
+// Math (as csrc/attention.cu; reference crates/engine/src/backend/cpu/attention.rs:76-128):
+//   s_j = (q . K_j) * scale over keys first..p, softmax in float32 with a running maximum,
+//   out = sum_j softmax_j V_j. Q K^T and P V run on the tensor cores (mma.sync m16n8k16, bf16 in,
+//   float32 accumulate); P is rounded to bfloat16 for the second product; everything between is
+//   float32 (exp2 of scores pre-multiplied by scale * log2 e).
+//
+// Grouped-query packing: the G = H / KV query heads that share a kv head are stacked as rows, so a
+// K/V tile is read once per kv head instead of once per head. Row rr of a request's row space is
+// token rr / G (position context_len + rr / G) and head kvh * G + rr % G.
+//
+// K/V tiles of 64 keys are gathered page by page with 16-byte cp.async copies into padded shared
+// memory (row stride head_dim + 8 elements keeps ldmatrix free of bank conflicts), double buffered.
+// Keys outside [first, p] are never read from global memory (their pages may have been given
+// back): their shared-memory rows are zero-filled and their scores masked to -inf.
+//
+// Kernels take head_dim 64 or 128, page sizes that divide 64, G <= 16 for the decode kernel;
+// the launcher refuses anything else (the caller then uses the general kernel).
+#include "common.cuh"
+
+namespace {
+
+constexpr int BN = 64;        // keys per tile
+constexpr int NTHREADS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather one tile of 64 keys (K and V of one kv head) into shared memory. Keys outside
+// [lo, hi) are zero-filled and never touched in global memory.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* __restrict__ kc,
+                                             const __nv_bfloat16* __restrict__ vc, const int* __restrict__ bt, int kvh,
+                                             int KV, int page_size, int tile_start, int lo, int hi) {
+    constexpr int LD = HD + 8;
+    constexpr int CH = HD / 8;                 // 16-byte pieces per key
+    for (int c = threadIdx.x; c < BN * CH; c += NTHREADS) {
+        int key = c / CH, ch = c - key * CH;
+        int j = tile_start + key;
+        __nv_bfloat16* dk = sK + key * LD + ch * 8;
+        __nv_bfloat16* dv = sV + key * LD + ch * 8;
+        if (j >= lo && j < hi) {
+            int page = bt[j / page_size];
+            size_t off = (((size_t)page * KV + kvh) * page_size + (j % page_size)) * HD + ch * 8;
+            cp_async16(dk, kc + off);
+            cp_async16(dv, vc + off);
+        } else {
+            *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// S (16 rows x 8*NB keys) += Q K^T for the n-blocks [nb0, nb0+NB) of the tile in sK.
+template <int HD, int NB>
+__device__ __forceinline__ void qk_tile(float (&s)[NB][4], const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* sK, int nb0) {
+    constexpr int LD = HD + 8;
+    int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[nb][i] = 0.f;
+#pragma unroll
+        for (int k2 = 0; k2 < HD / 32; ++k2) {
+            uint32_t r[4];
+            ldmatrix_x4(r, sK + ((nb0 + nb) * 8 + (lane & 7)) * LD + k2 * 32 + (lane >> 3) * 8);
+            mma_bf16(s[nb], qf[2 * k2], r[0], r[1]);
+            mma_bf16(s[nb], qf[2 * k2 + 1], r[2], r[3]);
+        }
+    }
+}
+
+// O (16 x HD) += P V for NK slices of 16 keys starting at key slice ks0 of the tile in sV.
+template <int HD, int NK>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&pa)[NK][4], const __nv_bfloat16* sV, int ks0) {
+    constexpr int LD = HD + 8;
+    int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kk = 0; kk < NK; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < HD / 16; ++n2) {
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, sV + ((ks0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + n2 * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * n2], pa[kk], r[0], r[1]);
+            mma_bf16(o[2 * n2 + 1], pa[kk], r[2], r[3]);
+        }
+    }
+}
+
+// Mask, running maximum, exponentials; returns P as A-fragments. s holds NB n-blocks of 8 keys
+// starting at key index key0; this thread's rows are r and r+8 with limits [lo, pos].
+template <int NB, int HDN>
+__device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[NB / 2][4], float (&o)[HDN][4],
+                                             float (&m)[2], float (&l)[2], int key0, const int (&lo)[2],
+                                             const int (&pos)[2], float scale_log2) {
+    int lane = threadIdx.x & 31;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int j = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
+            int h = i >> 1;
+            bool ok = j >= lo[h] && j <= pos[h];
+            float v = ok ? s[nb][i] * scale_log2 : -INFINITY;
+            s[nb][i] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    }
+    float alpha[2], msafe[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        float mn = fmaxf(m[h], mx[h]);
+        msafe[h] = mn == -INFINITY ? 0.f : mn;
+        alpha[h] = exp2f(m[h] - msafe[h]);            // m = -inf: 0
+        m[h] = mn;
+        l[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float p = exp2f(s[nb][i] - msafe[i >> 1]);
+            s[nb][i] = p;
+            l[i >> 1] += p;                           // this thread's share; the quad is summed at the end
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < HDN; ++n) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < NB / 2; ++kk) {
+        pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Portions of prompts and mixed batches. Grid (row tiles, requests, kv heads); a block of 4 warps
+// owns 64 rows of one request's row space (16 rows per warp) and walks the key tiles that any of
+// its rows can see. Blocks beyond a request's rows leave at once.
+// Bound: tensor-core and exp throughput for long portions; for short ones the K/V reads.
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
+                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
+                        const int* __restrict__ context_lens, int H, int KV, int page_size, int window, float scale_log2) {
+    constexpr int LD = HD + 8;
+    constexpr int BM = 64;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sK0 = sQ + BM * LD;
+    __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
+
+    const int G = H / KV;
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int row0 = seq_starts[seq];
+    const int n_new = seq_starts[seq + 1] - row0;
+    const int total_rows = n_new * G;
+    const int tile_row0 = blockIdx.x * BM;
+    if (tile_row0 >= total_rows) return;
+    const int ctx = context_lens[seq];
+    const int* bt = block_tables + (size_t)seq * max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // rows of this block -> shared memory (zero for rows beyond the request)
+    for (int c = threadIdx.x; c < BM * (HD / 8); c += NTHREADS) {
+        int r = c / (HD / 8), ch = c - r * (HD / 8);
+        int rr = tile_row0 + r;
+        __nv_bfloat16* dst = sQ + r * LD + ch * 8;
+        if (rr < total_rows) {
+            int tok = rr / G, head = kvh * G + rr % G;
+            cp_async16(dst, q + (size_t)(row0 + tok) * q_stride + (size_t)head * HD + ch * 8);
+        } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    // key range any row of the block reads
+    const int last_rr = min(tile_row0 + BM, total_rows) - 1;
+    const int hi = ctx + last_rr / G + 1;
+    const int first_tok_pos = ctx + tile_row0 / G;
+    const int lo_blk = window > 0 ? max(0, first_tok_pos + 1 - window) : 0;
+    const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
+
+    load_kv_tile<HD>(sK0, sV0, kc, vc, bt, kvh, KV, page_size, t_begin * BN, lo_blk, hi);
+    cp_async_commit();
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
+        pos[h] = rr < total_rows ? ctx + rr / G : -1;
+        lo[h] = window > 0 ? max(0, pos[h] + 1 - window) : 0;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    uint32_t qf[HD / 16][4];
+
+    for (int t = t_begin; t < t_end; ++t) {
+        int buf = (t - t_begin) & 1;
+        __nv_bfloat16* sK = sK0 + buf * BN * LD;
+        __nv_bfloat16* sV = sV0 + buf * BN * LD;
+        cp_async_wait<0>();
+        __syncthreads();                       // tile t (and Q) visible; everyone is done with tile t-1
+        if (t + 1 < t_end) {
+            load_kv_tile<HD>(sK0 + (buf ^ 1) * BN * LD, sV0 + (buf ^ 1) * BN * LD, kc, vc, bt, kvh, KV, page_size,
+                             (t + 1) * BN, lo_blk, hi);
+            cp_async_commit();
+        }
+        if (t == t_begin) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+                ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
+        }
+        // a warp whose rows all lie before this tile's first key has nothing to do here
+        int warp_last_pos = max(pos[0], pos[1]);
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
+        if (t * BN <= warp_last_pos) {
+            float s[8][4];
+            qk_tile<HD, 8>(s, qf, sK, 0);
+            uint32_t pa[4][4];
+            softmax_step<8, HD / 8>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+            pv_tile<HD, 4>(o, pa, sV, 0);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
+        if (rr >= total_rows) continue;
+        int tok = rr / G, head = kvh * G + rr % G;
+        float inv = 1.0f / l[h];
+        __nv_bfloat16* op = out + (size_t)(row0 + tok) * out_stride + (size_t)head * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<uint32_t*>(op + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Steps of single decoded tokens. Grid (requests, kv heads, splits): a block reads its share of
+// the request's key tiles once for all G heads of the group; its 4 warps split every tile's 64
+// keys (16 each) and combine through shared memory; with more than one split the block writes an
+// unnormalised partial (running maximum, sum, weighted values) to scratch and a second kernel
+// merges the splits in a fixed order. Bound: the K/V reads (memory).
+// Scratch layout: part_ml [requests][H][splits][2], part_o [requests][H][splits][HD], float32.
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
+                       long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                       const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
+                       int H, int KV, int page_size, int window, float scale_log2, int splits,
+                       float* __restrict__ part_ml, float* __restrict__ part_o) {
+    constexpr int LD = HD + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
+    __nv_bfloat16* sK0 = sQ + 16 * LD;
+    __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
+
+    const int G = H / KV;
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int p = positions[seq];                 // one row per request: row index == request index
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* bt = block_tables + (size_t)seq * max_pages;
+    const int hi = p + 1;
+    const int lo_key = (p >= 0 && window > 0) ? max(0, p + 1 - window) : 0;
+    const int t_first = lo_key / BN;
+    const int n_tiles = p >= 0 ? (hi + BN - 1) / BN - t_first : 0;
+    const int per = (n_tiles + splits - 1) / splits;
+    const int t_begin = t_first + split * per;
+    const int t_end = min(t_first + n_tiles, t_begin + per);
+
+    for (int c = threadIdx.x; c < 16 * (HD / 8); c += NTHREADS) {
+        int r = c / (HD / 8), ch = c - r * (HD / 8);
+        __nv_bfloat16* dst = sQ + r * LD + ch * 8;
+        if (r < G && p >= 0) cp_async16(dst, q + (size_t)seq * q_stride + (size_t)(kvh * G + r) * HD + ch * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    if (t_begin < t_end) load_kv_tile<HD>(sK0, sV0, kc, vc, bt, kvh, KV, page_size, t_begin * BN, lo_key, hi);
+    cp_async_commit();
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int r = (lane >> 2) + h * 8;
+        pos[h] = r < G ? p : -1;
+        lo[h] = lo_key;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    uint32_t qf[HD / 16][4];
+
+    for (int t = t_begin; t < t_end; ++t) {
+        int buf = (t - t_begin) & 1;
+        __nv_bfloat16* sK = sK0 + buf * BN * LD;
+        __nv_bfloat16* sV = sV0 + buf * BN * LD;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (t + 1 < t_end) {
+            load_kv_tile<HD>(sK0 + (buf ^ 1) * BN * LD, sV0 + (buf ^ 1) * BN * LD, kc, vc, bt, kvh, KV, page_size,
+                             (t + 1) * BN, lo_key, hi);
+            cp_async_commit();
+        }
+        if (t == t_begin) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+                ldmatrix_x4(qf[kk], sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
+        }
+        float s[2][4];
+        qk_tile<HD, 2>(s, qf, sK, warp * 2);                    // this warp's 16 keys of the tile
+        uint32_t pa[1][4];
+        softmax_step<2, HD / 8>(s, pa, o, m, l, t * BN + warp * 16, lo, pos, scale_log2);
+        pv_tile<HD, 1>(o, pa, sV, warp);
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                            // K/V buffers are free: reuse them for the combine
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    float* cm = reinterpret_cast<float*>(sK0);                  // [4 warps][16 rows] max
+    float* cl = cm + 64;                                        // [4][16] sum
+    float* co = cl + 64;                                        // [4][16][HD]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int r = (lane >> 2) + h * 8;
+        if ((lane & 3) == 0) { cm[warp * 16 + r] = m[h]; cl[warp * 16 + r] = l[h]; }
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            co[(warp * 16 + r) * HD + n * 8 + (lane & 3) * 2] = o[n][2 * h];
+            co[(warp * 16 + r) * HD + n * 8 + (lane & 3) * 2 + 1] = o[n][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * HD; e += NTHREADS) {
+        int r = e / HD, d = e - r * HD;
+        float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
+        float Ms = M == -INFINITY ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float f = exp2f(cm[w * 16 + r] - Ms);
+            acc += f * co[(w * 16 + r) * HD + d];
+            L += f * cl[w * 16 + r];
+        }
+        int head = kvh * G + r;
+        if (splits == 1) {
+            if (p >= 0) out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+            else out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(0.f);
+        } else {
+            size_t idx = ((size_t)seq * H + head) * splits + split;
+            part_o[idx * HD + d] = acc;
+            if (d == 0) { part_ml[idx * 2] = M; part_ml[idx * 2 + 1] = L; }
+        }
+    }
+}
+
+// Merge the splits of every (request, head): a fixed order, so the result does not depend on
+// which block finished first. Grid (requests, H), HD threads.
+template <int HD>
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_o, int splits,
+                                         int H, __nv_bfloat16* __restrict__ out, long long out_stride) {
+    int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    size_t base = ((size_t)seq * H + head) * splits;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float Ms = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        float f = exp2f(part_ml[(base + s) * 2] - Ms);
+        acc += f * part_o[(base + s) * HD + d];
+        L += f * part_ml[(base + s) * 2 + 1];
+    }
+    out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+template <int HD> constexpr size_t prefill_smem() { return (size_t)(64 + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16); }
+template <int HD> constexpr size_t decode_smem() { return (size_t)(16 + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16); }
+
+template <int HD>
+int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
+                   const int* bt, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new,
+                   int H, int KV, int page_size, int window, float scale, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)prefill_smem<HD>());
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int G = H / KV;
+    dim3 grid(((long long)max_new * G + 63) / 64, S, KV);
+    attn_prefill_mma_kernel<HD><<<grid, NTHREADS, prefill_smem<HD>(), stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, page_size, window,
+        scale * 1.4426950408889634f);
+    return vob_launch_status();
+}
+
+template <int HD>
+int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
+                  const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
+                  float scale, int splits, float* part_ml, float* part_o, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)decode_smem<HD>());
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(S, KV, splits);
+    attn_decode_mma_kernel<HD><<<grid, NTHREADS, decode_smem<HD>(), stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, bt, max_pages, positions, H, KV, page_size, window, scale * 1.4426950408889634f,
+        splits, part_ml, part_o);
+    int e = vob_launch_status();
+    if (e || splits == 1) return e;
+    attn_decode_merge_kernel<HD><<<dim3(S, H), HD, 0, stream>>>(part_ml, part_o, splits, H, (__nv_bfloat16*)out, out_stride);
+    return vob_launch_status();
+}
+
+bool sizes_ok(int H, int KV, int hd, int page_size) {
+    return (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && page_size > 0 && BN % page_size == 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take these sizes (decode additionally needs H / KV <= 16).
+VOB_EXPORT int vob_attn_mma_supported(int H, int KV, int hd, int page_size, int decode) {
+    if (!sizes_ok(H, KV, hd, page_size)) return 0;
+    if (decode && H / KV > 16) return 0;
+    return 1;
+}
+
+VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
+                                    const void* vcache, const int* block_tables, int max_pages, const int* seq_starts,
+                                    const int* context_lens, int S, int max_new, int H, int KV, int hd, int page_size,
+                                    int window, float scale, cudaStream_t stream) {
+    if (S <= 0 || max_new <= 0) return 0;
+    if (!sizes_ok(H, KV, hd, page_size)) return VOB_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || out_stride % 2 != 0 || S > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
+    if (hd == 64) return launch_prefill<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,
+                                           context_lens, S, max_new, H, KV, page_size, window, scale, stream);
+    return launch_prefill<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,
+                               context_lens, S, max_new, H, KV, page_size, window, scale, stream);
+}
+
+// Scratch: part_ml needs S * H * splits * 2 floats, part_o S * H * splits * hd floats (unused when splits == 1).
+VOB_EXPORT int vob_attn_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
+                                   const void* vcache, const int* block_tables, int max_pages, const int* positions, int S,
+                                   int H, int KV, int hd, int page_size, int window, float scale, int splits,
+                                   float* part_ml, float* part_o, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || splits < 1 || splits > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
+    if (splits > 1 && (!part_ml || !part_o)) return VOB_ERR_BAD_ARG;
+    if (hd == 64) return launch_decode<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
+                                          H, KV, page_size, window, scale, splits, part_ml, part_o, stream);
+    return launch_decode<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
+                              page_size, window, scale, splits, part_ml, part_o, stream);
+}

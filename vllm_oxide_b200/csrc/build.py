@@ -29,7 +29,7 @@ _NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
                "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 _CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
-CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "sampling", "gemm_sm100")
+CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "attention_mma", "sampling", "gemm_sm100")
 _lock = threading.Lock()
 _loaded: Dict[str, object] = {}
 

@@ -145,7 +145,8 @@ class ModelRunner:
                           for g in range(G)],
             workspace=self.workspace,
             max_new=arrays.max_new if arrays is not None else 0,
-            max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays)
+            max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays,
+            decode_only=bool(arrays is not None and arrays.max_new == 1 and arrays.rows == arrays.seqs))
 
     def upload(self, arrays) -> None:
         """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
@@ -262,6 +263,7 @@ class ModelRunner:
         L = self.decode_layout
         self.workspace.reset()
         ctx = self.context(b, b, None, L)
+        ctx.decode_only, ctx.max_new = True, 1
         resid, pending = self._forward(ctx)
         self._head(resid, pending, ctx, b, None, L)
 

@@ -151,7 +151,7 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
-def preload(modules=("elementwise", "gemm_f32", "attention", "sampling")) -> None:
+def preload(modules=("elementwise", "gemm_f32", "attention", "attention_mma", "sampling")) -> None:
     """Build and load kernel modules now (so that compile time is spent at start-up)."""
     for m in modules:
         load_cuda_module(m)
@@ -358,6 +358,89 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _code(q, op),
              _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), T, num_heads,
              num_kv_heads, head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
+
+
+def attn_mma_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, decode: bool) -> bool:
+    """Whether the tensor-core attention kernels take these sizes (bfloat16 only)."""
+    f = _fn("attention_mma", "vob_attn_mma_supported", [_I, _I, _I, _I, _I])
+    return bool(f(num_heads, num_kv_heads, head_dim, page_size, int(decode)))
+
+
+def _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim):
+    _cuda(op, q, out, kcache, vcache, block_tables)
+    _rows_2d(q, op, "q")
+    _rows_2d(out, op, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or vcache.dtype != torch.bfloat16:
+        raise ShapeError(op, "the tensor-core attention kernels are bfloat16 only")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise ShapeError(op, f"q and out must be [T, {num_heads * head_dim}], got {list(q.shape)} and {list(out.shape)}")
+    for name, c in (("kcache", kcache), ("vcache", vcache)):
+        if c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous():
+            raise ShapeError(op, f"{name} must be contiguous [pages, {num_kv_heads}, page_size, {head_dim}], got {list(c.shape)}")
+    if kcache.shape != vcache.shape:
+        raise ShapeError(op, "kcache and vcache differ in shape")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, "block_tables must be contiguous int32 [S, max_pages]")
+    if q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0 or out.stride(0) % 2 != 0 or out.data_ptr() % 4 != 0:
+        raise ShapeError(op, "q rows must be 16-byte aligned and out rows 4-byte aligned")
+    if not attn_mma_supported(num_heads, num_kv_heads, head_dim, kcache.shape[2], False):
+        raise ShapeError(op, f"sizes not supported by the tensor-core kernels: heads {num_heads}/{num_kv_heads}, "
+                             f"head_dim {head_dim}, page {kcache.shape[2]} (head_dim 64 or 128, page size dividing 64)")
+
+
+@_timed
+def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
+                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Tensor-core attention for portions of prompts and mixed batches (bfloat16). q/out [T, H*hd];
+    seq_starts int32 [S+1] (first row of each request), context_lens int32 [S] (keys cached before
+    the step), max_new = the longest portion."""
+    op = "attn_prefill_mma"
+    _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
+    _cuda(op, seq_starts, context_lens)
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(context_lens, num_seqs, op, "context_lens")
+    if block_tables.shape[0] < num_seqs:
+        raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {num_seqs} requests")
+    f = _fn("attention_mma", "vob_attn_prefill_mma",
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+             block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
+             head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
+
+
+def attn_decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, splits: int) -> int:
+    return num_seqs * num_heads * splits * (head_dim + 2) if splits > 1 else 0
+
+
+@_timed
+def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, window: int = 0, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
+    With splits > 1 each request's keys are shared out over `splits` blocks and merged by a second
+    kernel; `scratch` (float32) needs attn_decode_scratch_floats(...) elements."""
+    op = "attn_decode_mma"
+    _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
+    _cuda(op, positions, scratch)
+    S = q.shape[0]
+    _int32_vec(positions, S, op, "positions")
+    if block_tables.shape[0] < S:
+        raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {S} requests")
+    if num_heads // num_kv_heads > 16:
+        raise ShapeError(op, f"{num_heads // num_kv_heads} heads per kv head: the decode kernel takes at most 16")
+    ml = po = None
+    launches = 1
+    if splits > 1:
+        need = attn_decode_scratch_floats(S, num_heads, head_dim, splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_contiguous():
+            raise ShapeError(op, f"scratch must be contiguous float32 with at least {need} elements")
+        n_ml = S * num_heads * splits * 2
+        ml, po = scratch[:n_ml], scratch[n_ml:need]
+        launches = 2
+    f = _fn("attention_mma", "vob_attn_decode_mma",
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+             block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
+             float(scale), int(splits), _ptr(ml), _ptr(po), _stream()), op, launches=launches)
 
 
 # ------------------------------------------------------------------------------------ sampling

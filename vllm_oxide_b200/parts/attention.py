@@ -51,6 +51,8 @@ class Attention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         self.hidden = hidden
         self.dtype = dtype
+        self.impl = "auto"            # "general" forces the general attention kernel (tests)
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return CacheSpec(self.KV, self.hd, "window" if self.window else "full", self.window)
@@ -60,7 +62,7 @@ class Attention(Mixer):
 
     def workspace_bytes(self, rows: int) -> int:
         es = 2 if self.dtype == torch.bfloat16 else 4
-        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + 2 * 256
+        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + rows * self.H * 16 * (self.hd + 2) * 4 + 3 * 256
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
         if cache is None:
@@ -81,5 +83,29 @@ class Attention(Mixer):
         return matmul(attn, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
 
     def attend(self, q, out, ctx: StepContext, cache: LayerCache) -> None:
-        kernels.paged_attention(q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_seq,
-                                ctx.positions, self.H, self.KV, self.hd, self.scale, self.window)
+        """bfloat16 with sizes the tensor-core kernels take: the decode kernel for steps of single
+        tokens, the portion kernel for everything else. Otherwise (float32, other head sizes) the
+        general kernel."""
+        page = cache.k.shape[2]
+        bt = ctx.block_tables[cache.group]
+        if self.dtype == torch.bfloat16 and self.impl != "general":
+            if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
+                splits = self.decode_splits(ctx.rows)
+                scratch = None
+                if splits > 1:
+                    scratch = ctx.alloc((kernels.attn_decode_scratch_floats(ctx.rows, self.H, self.hd, splits),), torch.float32)
+                kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd,
+                                        self.scale, self.window, splits, scratch)
+                return
+            if not ctx.decode_only and ctx.max_new > 0 and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, False):
+                kernels.attn_prefill_mma(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,
+                                         ctx.max_new, self.H, self.KV, self.hd, self.scale, self.window)
+                return
+        kernels.paged_attention(q, out, cache.k, cache.v, bt, ctx.row_seq, ctx.positions, self.H, self.KV, self.hd,
+                                self.scale, self.window)
+
+    def decode_splits(self, num_seqs: int) -> int:
+        """How many blocks share one request's keys in a decode step: enough that the grid fills
+        the GPU twice over, at most 16."""
+        blocks = max(1, num_seqs * self.KV)
+        return max(1, min(16, -(-2 * self.num_sms // blocks)))

@@ -119,6 +119,7 @@ class StepContext:
     workspace: Workspace
     max_new: int = 0                # longest portion in the batch (host fact)
     max_seq_len: int = 0            # longest context after the step (host fact)
+    decode_only: bool = False       # every request brings exactly one token and row i is request i
     host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them
 
     def alloc(self, shape, dtype=None) -> torch.Tensor:

@@ -81,21 +81,118 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     for (int i = threadIdx.x; i < h; i += blockDim.x) st_f(o + i, weight[i] * (row[i] * inv));
 }
 
+// Fast path for rows whose width is a multiple of 4 and fits NV float4 per thread: every load of
+// the row is issued before anything depends on one (a row of a small batch is latency-bound, not
+// bandwidth-bound), the row stays in registers, and the sums take the same fixed order for every
+// row. Same arithmetic as the kernel above.
+template <typename TD> struct Load4;
+template <> struct Load4<float> {
+    __device__ static inline float4 ld(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct Load4<__nv_bfloat16> {
+    __device__ static inline float4 ld(const __nv_bfloat16* p) {
+        uint2 u = *reinterpret_cast<const uint2*>(p);
+        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+template <typename TO> struct Store4;
+template <> struct Store4<float> {
+    __device__ static inline void st(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Store4<__nv_bfloat16> {
+    __device__ static inline void st(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
+                       const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
+    __shared__ float red[32];
+    int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    float* x = resid + (size_t)src * h;
+    const TD* d = delta ? delta + (size_t)src * h : nullptr;
+    int nvec = h >> 2;
+    float4 v[NV], dv[NV], w[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        int i = threadIdx.x + k * 256;
+        if (i < nvec) {
+            v[k] = *reinterpret_cast<const float4*>(x + 4 * i);
+            dv[k] = d ? Load4<TD>::ld(d + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[k] = *reinterpret_cast<const float4*>(weight + 4 * i);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        int i = threadIdx.x + k * 256;
+        if (i < nvec) {
+            v[k].x += dv[k].x; v[k].y += dv[k].y; v[k].z += dv[k].z; v[k].w += dv[k].w;
+            if (d && !rows) *reinterpret_cast<float4*>(x + 4 * i) = v[k];
+            ss += v[k].x * v[k].x; ss += v[k].y * v[k].y; ss += v[k].z * v[k].z; ss += v[k].w * v[k].w;
+        }
+    }
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) red[wid] = ss;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < 8 ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[0] = t;
+    }
+    __syncthreads();
+    float inv = 1.0f / sqrtf(red[0] / (float)h + eps);
+    TO* o = out + (size_t)r * h;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        int i = threadIdx.x + k * 256;
+        if (i < nvec)
+            Store4<TO>::st(o + 4 * i, make_float4(w[k].x * (v[k].x * inv), w[k].y * (v[k].y * inv),
+                                                  w[k].z * (v[k].z * inv), w[k].w * (v[k].w * inv)));
+    }
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* resid, const void* delta, const float* weight, const int* rows, void* out, int R,
+                              int h, float eps, cudaStream_t stream) {
+    bool aligned = (h % 4 == 0) && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) % 16 == 0);
+    int nv = (h / 4 + 255) / 256;
+    if (aligned && nv <= 8) {
+#define VEC(NV) add_rmsnorm_vec_kernel<TD, TO, NV><<<R, 256, 0, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
+        if (nv <= 1) VEC(1); else if (nv <= 2) VEC(2); else if (nv <= 4) VEC(4); else VEC(8);
+#undef VEC
+        return vob_launch_status();
+    }
+    size_t smem = (size_t)h * sizeof(float);
+    if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
+    add_rmsnorm_kernel<TD, TO><<<R, 256, smem, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps);
+    return vob_launch_status();
+}
+
 VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, const float* weight,
                                const int* rows, void* out, int out_code, int R, int h, float eps,
                                cudaStream_t stream) {
     if (R <= 0) return 0;
     if (h <= 0) return VOB_ERR_BAD_ARG;
-    size_t smem = (size_t)h * sizeof(float);
-    if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
-#define LAUNCH(TD, TO) add_rmsnorm_kernel<TD, TO><<<R, 256, smem, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
+    if (!delta) delta_code = VOB_F32;
     if (out_code == VOB_F32) {
-        if (delta_code == VOB_F32) LAUNCH(float, float); else if (delta_code == VOB_BF16) LAUNCH(__nv_bfloat16, float); else return VOB_ERR_BAD_ARG;
+        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, float>(resid, delta, weight, rows, out, R, h, eps, stream);
+        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, weight, rows, out, R, h, eps, stream);
     } else if (out_code == VOB_BF16) {
-        if (delta_code == VOB_F32) LAUNCH(float, __nv_bfloat16); else if (delta_code == VOB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else return VOB_ERR_BAD_ARG;
-    } else return VOB_ERR_BAD_ARG;
-#undef LAUNCH
-    return vob_launch_status();
+        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, stream);
+        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, stream);
+    }
+    return VOB_ERR_BAD_ARG;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -126,64 +223,57 @@ VOB_EXPORT int vob_add_residual(float* resid, const void* delta, int delta_code,
 // [kv_heads][page_size][head_dim], so one (page, head) is one contiguous tile.
 // `slots` may be null (rotate only); a negative slot skips that token's write.
 // `inv_freq` may be null (no rotation: the part has no position encoding).
-// Launch: one block per token, 128 threads, head_dim floats of shared memory for cos|sin.
-// Bound: memory.
+// Launch: grid (tokens, ceil((H+KV)*hd/2 / 128)), one thread per (head, pair); each thread takes
+// the sine and cosine of its own angle. Bound: memory.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
-                                     const T* __restrict__ v, long long v_stride,
-                                     const int* __restrict__ positions, const int* __restrict__ slots,
-                                     const float* __restrict__ inv_freq, T* __restrict__ kcache,
-                                     T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
-    extern __shared__ float cs[];   // cos[half] | sin[half]
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+                     const T* __restrict__ v, long long v_stride, const int* __restrict__ positions,
+                     const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
+                     T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
+    // one thread per (head, pair i): heads 0..H-1 are q heads, H..H+KV-1 are k heads (with their v)
     int t = blockIdx.x;
     int half = hd >> 1;
+    int e = blockIdx.y * blockDim.x + threadIdx.x;
+    int nheads = H + (k ? KV : 0);
+    if (e >= nheads * half) return;
+    int head = e / half, i = e - head * half;
+    float c = 1.f, s = 0.f;
     if (inv_freq) {
-        float p = (float)positions[t];
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            float theta = p * inv_freq[i];
-            cs[i] = cosf(theta);
-            cs[half + i] = sinf(theta);
-        }
+        float theta = (float)positions[t] * inv_freq[i];
+        c = cosf(theta);
+        s = sinf(theta);
     }
-    __syncthreads();
-    int slot = slots ? slots[t] : -1;
-    T* qr = q + (size_t)t * q_stride;
-    T* kr = k ? k + (size_t)t * k_stride : nullptr;
-    const T* vr = v ? v + (size_t)t * v_stride : nullptr;
-    // q heads
-    for (int e = threadIdx.x; e < H * half; e += blockDim.x) {
-        int head = e / half, i = e - head * half;
-        T* x = qr + head * hd;
+    if (head < H) {
+        T* x = q + (size_t)t * q_stride + (size_t)head * hd;
         if (inv_freq) {
             float a = ld_f(x + i), b = ld_f(x + half + i);
-            float c = cs[i], s = cs[half + i];
             st_f(x + i, a * c - b * s);
             st_f(x + half + i, b * c + a * s);
         }
+        return;
     }
-    if (!kr) return;
-    size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0;
-    int off = slot >= 0 ? slot % page_size : 0;
-    for (int e = threadIdx.x; e < KV * half; e += blockDim.x) {
-        int head = e / half, i = e - head * half;
-        T* x = kr + head * hd;
-        float a = ld_f(x + i), b = ld_f(x + half + i);
-        float ra = a, rb = b;
-        if (inv_freq) {
-            float c = cs[i], s = cs[half + i];
-            ra = a * c - b * s;
-            rb = b * c + a * s;
-            st_f(x + i, ra);
-            st_f(x + half + i, rb);
-        }
-        if (slot >= 0) {
-            size_t base = ((page * KV + head) * page_size + off) * (size_t)hd;
-            st_f(kcache + base + i, ra);
-            st_f(kcache + base + half + i, rb);
-            vcache[base + i] = vr[head * hd + i];
-            vcache[base + half + i] = vr[head * hd + half + i];
-        }
+    int kh = head - H;
+    T* x = k + (size_t)t * k_stride + (size_t)kh * hd;
+    float a = ld_f(x + i), b = ld_f(x + half + i);
+    float ra = a, rb = b;
+    if (inv_freq) {
+        ra = a * c - b * s;
+        rb = b * c + a * s;
+        st_f(x + i, ra);
+        st_f(x + half + i, rb);
+    }
+    int slot = slots ? slots[t] : -1;
+    if (slot >= 0) {
+        size_t page = (size_t)(slot / page_size);
+        int off = slot % page_size;
+        size_t base = ((page * KV + kh) * page_size + off) * (size_t)hd;
+        const T* vr = v + (size_t)t * v_stride + (size_t)kh * hd;
+        st_f(kcache + base + i, ra);
+        st_f(kcache + base + half + i, rb);
+        vcache[base + i] = vr[i];
+        vcache[base + half + i] = vr[half + i];
     }
 }
 
@@ -194,8 +284,10 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
     if (T <= 0) return 0;
     if (hd <= 0 || (hd & 1) || H <= 0 || KV < 0 || page_size <= 0) return VOB_ERR_BAD_ARG;
     if (k && slots && (!kcache || !vcache || !v)) return VOB_ERR_BAD_ARG;
-    size_t smem = (size_t)hd * sizeof(float);
-    VOB_DISPATCH_ELEM(code, rope_kv_write_kernel<ElemT><<<T, 128, smem, stream>>>(
+    int pairs = (H + (k ? KV : 0)) * (hd / 2);
+    dim3 grid(T, (pairs + 127) / 128);
+    if (grid.y > 65535) return VOB_ERR_UNSUPPORTED;
+    VOB_DISPATCH_ELEM(code, rope_kv_write_kernel<ElemT><<<grid, 128, 0, stream>>>(
         (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
         (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
     return vob_launch_status();
@@ -216,12 +308,48 @@ __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* 
     st_f(out + (size_t)blockIdx.x * I + j, g / (1.0f + expf(-g)) * u);
 }
 
+// 16 bytes per load: 8 bfloat16 or 4 float per thread (I a multiple of that, rows 16-byte aligned).
+template <typename T, int N>
+__global__ void swiglu_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
+    int j = (blockIdx.y * blockDim.x + threadIdx.x) * N;
+    if (j >= I) return;
+    const T* r = in + (size_t)blockIdx.x * in_stride;
+    uint4 gu = *reinterpret_cast<const uint4*>(r + j);
+    uint4 uu = *reinterpret_cast<const uint4*>(r + I + j);
+    const T* g = reinterpret_cast<const T*>(&gu);
+    const T* u = reinterpret_cast<const T*>(&uu);
+    uint4 ov;
+    T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+        float gf = ld_f(g + e), uf = ld_f(u + e);
+        st_f(o + e, gf / (1.0f + expf(-gf)) * uf);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * I + j) = ov;
+}
+
+template <typename T>
+static int launch_swiglu(const void* in, long long in_stride, void* out, int T_rows, int I, cudaStream_t stream) {
+    constexpr int N = 16 / sizeof(T);
+    bool vec = (I % N == 0) && (in_stride % N == 0) && (((uintptr_t)in | (uintptr_t)out) % 16 == 0);
+    if (vec) {
+        int per = 256 * N;
+        if ((I + per - 1) / per > 65535) return VOB_ERR_UNSUPPORTED;
+        dim3 grid(T_rows, (I + per - 1) / per);
+        swiglu_vec_kernel<T, N><<<grid, 256, 0, stream>>>((const T*)in, in_stride, (T*)out, I);
+    } else {
+        if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
+        dim3 grid(T_rows, (I + 255) / 256);
+        swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)in, in_stride, (T*)out, I);
+    }
+    return vob_launch_status();
+}
+
 VOB_EXPORT int vob_swiglu(const void* in, long long in_stride, void* out, int code, int T, int I,
                           cudaStream_t stream) {
     if (T <= 0) return 0;
     if (I <= 0) return VOB_ERR_BAD_ARG;
-    if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
-    dim3 grid(T, (I + 255) / 256);
-    VOB_DISPATCH_ELEM(code, swiglu_kernel<ElemT><<<grid, 256, 0, stream>>>((const ElemT*)in, in_stride, (ElemT*)out, I));
-    return vob_launch_status();
+    if (code == VOB_F32) return launch_swiglu<float>(in, in_stride, out, T, I, stream);
+    if (code == VOB_BF16) return launch_swiglu<__nv_bfloat16>(in, in_stride, out, T, I, stream);
+    return VOB_ERR_BAD_ARG;
 }

@@ -391,3 +391,60 @@ def test_attn_mma_refusals():
         k.attn_prefill_mma(q, q.clone(), kc, kc, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 4, 2, 48, 1.0)
     with pytest.raises(ShapeError, match="bfloat16 only"):
         k.attn_prefill_mma(q.float(), q.float(), kc.float(), kc.float(), torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 4, 2, 48, 1.0)
+
+
+# ----------------------------------------------------------------------------- tcgen05 matrix product (bfloat16)
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32], ids=["bf16out", "f32out"])
+@pytest.mark.parametrize("T,N,Kd,splits", [
+    (1, 128, 64, 1), (8, 128, 256, None), (5, 640, 8192, 8), (8, 2048, 2048, 3), (16, 256, 512, 2), (17, 200, 136, None),
+    (33, 200, 136, None), (64, 2048, 2048, None), (100, 300, 520, None), (129, 1000, 1032, None), (300, 520, 264, None),
+    (700, 384, 96, None)])
+def test_gemm_sm100(T, N, Kd, splits, odt):
+    """TMA + tcgen05 product against float64: rows and features that are no multiple of a tile,
+    K that is no multiple of 64, every token-tile width (16 ... 256), K split over a cluster."""
+    g = torch.Generator().manual_seed(T * 7 + N)
+    a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, N), 7.0, dtype=odt, device=DEV)
+    k = K()
+    k.gemm_sm100(a, w, out, splits)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    want = plain.linear(a.double().cpu(), w.double().cpu())
+    # bfloat16 inputs are exact and products accumulate in float32: sqrt(K) * 2^-24 like the float32
+    # kernel; a bfloat16 result adds one rounding of 2^-9
+    tol = (2.0 ** -8) if odt == torch.bfloat16 else max(2e-6, 2.0 ** -22 * math.sqrt(Kd))
+    assert rel(out, want) <= tol
+    # a row's value does not depend on the rows beside it (same tile width): bitwise
+    if T > 1:
+        bt = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+        lo = max(0, T - 2) if (T - 1) // bt == 0 or bt == 16 else T - 1
+        sub = torch.empty((T - lo, N), dtype=odt, device=DEV)
+        if (T - lo <= 16) == (T <= 16) and splits == 1:
+            k.gemm_sm100(a[lo:].contiguous(), w, sub, splits)
+            assert torch.equal(sub, out[lo:])
+    # replay: nothing needs resetting between launches
+    out2 = torch.zeros_like(out)
+    k.gemm_sm100(a, w, out2, splits)
+    assert torch.equal(out2, out)
+
+
+def test_gemm_sm100_strided_and_refusals():
+    from vllm_oxide_b200.errors import ShapeError
+    k = K()
+    g = torch.Generator().manual_seed(1)
+    wide = torch.randn(9, 96, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(50, 64, generator=g).to(torch.bfloat16).to(DEV)
+    outw = torch.zeros(9, 80, dtype=torch.bfloat16, device=DEV)
+    k.gemm_sm100(wide[:, 16:80], w, outw[:, 8:58])             # column slices of wider buffers
+    want = plain.linear(wide[:, 16:80].double().cpu(), w.double().cpu())
+    assert rel(outw[:, 8:58], want) <= 2 ** -8
+    assert float(outw[:, :8].float().abs().max()) == 0.0 and float(outw[:, 58:].float().abs().max()) == 0.0
+    assert not k.gemm_sm100_supported(wide[:, 1:65], w)         # rows not 16-byte aligned
+    assert not k.gemm_sm100_supported(wide[:, :60], w[:, :60])  # K no multiple of 8
+    with pytest.raises(ShapeError):
+        k.gemm_sm100(wide[:, :60], w[:, :60], outw[:, :50])
+    # linear() falls back to the library product for such operands instead of failing
+    o = torch.empty(9, 50, dtype=torch.bfloat16, device=DEV)
+    k.linear(wide[:, :60].contiguous(), w[:, :60].contiguous(), o)
+    assert rel(o, plain.linear(wide[:, :60].double().cpu(), w[:, :60].double().cpu())) <= 2 ** -8

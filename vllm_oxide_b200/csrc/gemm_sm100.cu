@@ -1,0 +1,402 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: C[T, N] = X[T, K] * W[N, K]^T.
+// Reference op: crates/engine/src/backend/cpu/mod.rs:199-229 (x * W^T, W [out, in] row-major).
+//
+// Shape of the kernel. The weight matrix is the M operand of tcgen05.mma (128 weight rows per
+// block), the tokens are the N operand (a tile of BT = 16 ... 256 tokens): D[128 features, BT
+// tokens] accumulates in tensor memory in float32. Both operands are K-major, which is how W
+// [N, K] and X [T, K] already lie in memory, so nothing is transposed. With the tokens on the N
+// side one kernel serves a decode step of a few tokens (a weight-streaming, HBM-bound product:
+// every weight byte is read exactly once, by TMA, through a multi-stage ring) and a prompt
+// portion of thousands (tensor-bound).
+//
+// Roles inside a block of 192 threads: warp 0 (one elected lane) issues the TMA loads
+// (cp.async.bulk.tensor, 128-byte swizzle, one mbarrier per stage), warp 1 allocates tensor
+// memory and (one lane) issues tcgen05.mma, committing each stage back to the producer with
+// tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld (each warp its own 32 lanes) and
+// write C: lane = output feature, so one store instruction of a warp covers 32 consecutive
+// features of one token.
+//
+// Few tokens leave most SMs without a tile, so the K range can be split over blockIdx.z. The
+// blocks of one tile form a thread-block cluster (up to 8): each leaves its float32 partial tile
+// in its own shared memory, the cluster meets at a barrier, and every block then adds up a share
+// of the tile's tokens, reading its peers' partials through distributed shared memory in rank
+// order (a fixed order: the result does not depend on timing) and writes C. Nothing goes through
+// global memory and nothing needs resetting between launches.
+//
+// Every wait on an mbarrier is bounded (two seconds): on expiry the block raises the error flag,
+// stops issuing work, frees its tensor memory and returns; the host turns the flag into an
+// exception. No TMA load uses cluster multicast.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;           // weight rows (output features) per block
+constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait. Returns false (and raises the flags) when the limit passes or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_flag, int code) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (err_flag) atomicExch(err_flag, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
+    uint64_t addr = smem_u32(tile);
+    uint64_t d = (addr & 0x3FFFF) >> 4;          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                      // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset
+    d |= (uint64_t)1 << 46;                      // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+
+template <typename OutT> __device__ __forceinline__ void store_out(OutT* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int BT> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
+template <int BT> __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
+
+template <int BT, int STAGES, typename OutT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ C,
+                  long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * stage_bytes<BT>());
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+    const int total_kb = (K + BK - 1) / BK;
+    const int kb0 = split * kb_per_split;
+    const int kb1 = min(total_kb, kb0 + kb_per_split);
+    const int nkb = kb1 - kb0;                    // >= 1 by the launcher's choice of splits
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(tmem_cols<BT>()) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                int s = i % STAGES;
+                uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, err_flag, 1)) break;
+                unsigned char* a = tiles + s * stage_bytes<BT>();
+                unsigned char* b = a + BM * BK * 2;
+                mbar_expect_tx(full_bar + s, stage_bytes<BT>());
+                tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + s);
+                tma_load_2d(b, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BT);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                int s = i % STAGES;
+                uint32_t ph = (i / STAGES) & 1;
+                ok = mbar_wait(full_bar + s, ph, abort_flag, err_flag, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* a = tiles + s * stage_bytes<BT>();
+                uint64_t adesc = umma_desc_sw128(a);
+                uint64_t bdesc = umma_desc_sw128(a + BM * BK * 2);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 K elements = 32 bytes = 2 units of the descriptor's start address
+                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar + s);       // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_bar);         // the accumulator is complete
+        }
+    } else {
+        // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) ... + 31
+        const int quad = warp & 3;
+        const int f = m_tile * BM + quad * 32 + lane;          // this thread's output feature
+        bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const int t0 = n_tile * BT;
+        if (ok && splits == 1) {
+#pragma unroll
+            for (int c = 0; c < BT; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (f < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        int t = t0 + c + j;
+                        if (t < T) store_out<OutT>(C + (size_t)t * ldc + f, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        } else if (ok) {
+            // partial tile to this block's shared memory: [token][feature] float32, over the operand
+            // stages (every MMA that read them has completed once acc_bar has flipped)
+            float* mine = reinterpret_cast<float*>(tiles) + quad * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < BT; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) mine[(c + j) * BM] = __uint_as_float(r[j]);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    if (splits > 1) {
+        // every thread of every block of the cluster: partials are written, peers may read them
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2 && !*abort_flag) {
+            const int quad = warp & 3;
+            const int col = quad * 32 + lane;
+            const int f = m_tile * BM + col;
+            const int t0 = n_tile * BT;
+            const uint32_t local = smem_u32(reinterpret_cast<float*>(tiles) + col);
+            // this block adds up the tokens j with j % splits == its rank
+            for (int j = split; j < BT && t0 + j < T; j += splits) {
+                float part[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    part[p] = 0.f;
+                    if (p < splits) {
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local + (uint32_t)(j * BM * 4)), "r"(p));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[p]) : "r"(remote) : "memory");
+                    }
+                }
+                float acc = 0.f;
+#pragma unroll
+                for (int p = 0; p < 8; ++p) acc += part[p];           // rank order, zeros beyond the last rank
+                if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
+            }
+        }
+        // nobody leaves (and frees its shared memory) while a peer may still be reading it
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols<BT>()) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h ^= std::hash<long long>()(k.rows * 1000003 + k.cols) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= std::hash<long long>()(k.ld * 131 + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+
+// A 2-D bfloat16 tensor [rows, cols] with row stride ld elements; boxes of [box_rows, 64] elements,
+// 128-byte swizzle; rows and columns outside the tensor read as zero.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return VOB_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return VOB_ERR_BAD_ARG;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+template <int BT, int STAGES> constexpr size_t smem_bytes() { return (size_t)STAGES * stage_bytes<BT>() + 1024 + 256; }
+
+template <int BT, int STAGES, typename OutT>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int splits, int kb_per,
+           int* err_flag, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BT, STAGES, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem_bytes<BT, STAGES>());
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + BM - 1) / BM, (T + BT - 1) / BT, splits);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem_bytes<BT, STAGES>();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;            // the blocks that share one tile
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<BT, STAGES, OutT>, mw, mx, (OutT*)C, ldc, T, N, K, kb_per, err_flag);
+    return e != cudaSuccess ? (int)e : vob_launch_status();
+}
+
+int pick_bt(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
+
+}  // namespace
+
+// How many splits of K fill `num_sms` SMs for a product with few tokens (1 when the tiles alone do).
+VOB_EXPORT int vob_gemm_sm100_pick_splits(int T, int N, int K, int num_sms) {
+    int bt = pick_bt(T);
+    int tiles = ((N + BM - 1) / BM) * ((T + bt - 1) / bt);
+    int total_kb = (K + BK - 1) / BK;
+    if (T > 32 || tiles * 2 > num_sms) return 1;
+    int want = num_sms / tiles;
+    if (want > 8) want = 8;                                           // the portable cluster size
+    int max_splits = total_kb / 4 > 0 ? total_kb / 4 : 1;             // at least 4 k-blocks (256 of K) per split
+    int s = want < max_splits ? want : max_splits;
+    if (s < 1) s = 1;
+    int per = (total_kb + s - 1) / s;
+    return (total_kb + per - 1) / per;                                // every split gets at least one k-block
+}
+
+// C[T, N] (row stride ldc, bfloat16 or float32) = X[T, K] (row stride ldx) * W[N, K]^T (row stride ldw).
+VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int out_code,
+                              int T, int N, int K, int splits, int* err_flag, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || ldx < K || ldw < K || ldc < N) return VOB_ERR_BAD_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0) return VOB_ERR_UNSUPPORTED;
+    if (out_code != VOB_F32 && out_code != VOB_BF16) return VOB_ERR_BAD_ARG;
+    int bt = pick_bt(T);
+    int total_kb = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > 8) splits = 8;
+    if (splits > total_kb) splits = total_kb;
+    int kb_per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per - 1) / kb_per;
+    if ((T + bt - 1) / bt > 65535 || splits > 65535) return VOB_ERR_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int e = make_map(&mw, W, N, K, ldw, BM);
+    if (e) return e;
+    e = make_map(&mx, X, T, K, ldx, bt);
+    if (e) return e;
+#define GO(BT, ST)                                                                                                         \
+    return out_code == VOB_F32                                                                                             \
+               ? launch<BT, ST, float>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)      \
+               : launch<BT, ST, __nv_bfloat16>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)
+    switch (bt) {
+        case 16: GO(16, 4);
+        case 32: GO(32, 4);
+        case 64: GO(64, 4);
+        case 128: GO(128, 4);
+        default: GO(256, 4);
+    }
+#undef GO
+}

@@ -151,7 +151,7 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
-def preload(modules=("elementwise", "gemm_f32", "attention", "attention_mma", "sampling")) -> None:
+def preload(modules=("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "sampling")) -> None:
     """Build and load kernel modules now (so that compile time is spent at start-up)."""
     for m in modules:
         load_cuda_module(m)
@@ -296,10 +296,78 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()), op)
 
 
+class _GemmScratch:
+    """Per device: the error word that a timed-out wait inside the tensor-core product raises."""
+
+    def __init__(self, device):
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+
+
+_gemm_scratch = {}
+
+
+def _scratch_for(device) -> _GemmScratch:
+    s = _gemm_scratch.get(device)
+    if s is None:
+        s = _gemm_scratch[device] = _GemmScratch(device)
+    return s
+
+
+def gemm_sm100_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes these operands: bfloat16, K a multiple of 8, 16-byte
+    aligned rows (what TMA asks for)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+@_timed
+def gemm_sm100(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
+    """out[T, N] = a[T, K] @ w[N, K]^T on the tcgen05 tensor cores: bfloat16 operands fetched by
+    TMA, float32 accumulation in tensor memory, bfloat16 or float32 out. `splits` > 1 (at most 8) splits K over
+    the blocks of a cluster (for few tokens); None picks it from the sizes."""
+    op = "gemm_sm100"
+    _cuda(op, a, w, out)
+    if not gemm_sm100_supported(a, w):
+        raise ShapeError(op, f"operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows, got "
+                             f"{a.dtype} {list(a.shape)} strides {list(a.stride())} and {w.dtype} {list(w.shape)}")
+    T, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N) or out.stride(1) != 1:
+        raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
+    sc = _scratch_for(a.device)
+    if splits is None:
+        f = _fn("gemm_sm100", "vob_gemm_sm100_pick_splits", [_I, _I, _I, _I])
+        splits = int(f(T, N, K, sc.num_sms))
+    f = _fn("gemm_sm100", "vob_gemm_sm100", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out, op), T, N, K, int(splits),
+             _ptr(sc.err), _stream()), op)
+
+
+def gemm_sm100_check() -> None:
+    """Raise if a wait inside the tensor-core product ever timed out (reads one word from the device)."""
+    for dev, sc in _gemm_scratch.items():
+        code = int(sc.err.item())
+        if code:
+            sc.err.zero_()
+            raise KernelError(f"gemm_sm100: a bounded wait expired inside the kernel (role {code}: 1 = TMA producer, "
+                              "2 = MMA issuer, 3 = epilogue); its result is not valid")
+
+
+# Above this many rows the library product is used for bfloat16 (None: the tensor-core kernel of this
+# package always). The hand-written kernel is the faster one for the few rows of a decode step.
+LIBRARY_GEMM_ABOVE_ROWS = 32
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = a @ w^T. float32 operands: the true 32-bit kernel. bfloat16 operands: the library
-    matrix product (cuBLAS through torch, float32 accumulation), as the reference plans for its
-    own matrix products (CLAUDE.md:107); `out` may be bfloat16 or float32."""
+    """out = a @ w^T. float32 operands: the true 32-bit kernel. bfloat16 operands: this package's
+    tcgen05 kernel (TMA operands, float32 accumulation in tensor memory); for many rows, or
+    operands TMA cannot address (K not a multiple of 8, unaligned rows), the library product
+    (cuBLAS through torch, float32 accumulation), as the reference plans for its own matrix
+    products (CLAUDE.md:107). `out` may be bfloat16 or float32."""
     op = "linear"
     if a.dtype == torch.float32:
         gemm_f32(a, w, out)
@@ -311,7 +379,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
-    _library_gemm_bf16(a, w, out)
+    if (LIBRARY_GEMM_ABOVE_ROWS is None or a.shape[0] <= LIBRARY_GEMM_ABOVE_ROWS) and gemm_sm100_supported(a, w):
+        gemm_sm100(a, w, out)
+    else:
+        _library_gemm_bf16(a, w, out)
 
 
 @_timed

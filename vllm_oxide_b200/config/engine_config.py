@@ -43,6 +43,7 @@ class EngineConfig:
     dtype: torch.dtype = torch.bfloat16
     prefill_chunk: Optional[int] = None  # most prompt tokens of one request per step
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
+    pdl: bool = True                   # programmatic dependent launch between the engine's kernels
     device: str = "cuda:0"
 
     def __post_init__(self):

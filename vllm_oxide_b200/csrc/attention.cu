@@ -11,6 +11,7 @@
 // Cache layout per layer: K and V are [num_pages][KV][page_size][hd]; key j of a request lives
 // in page block_table[seq][j / page_size] at offset j % page_size.
 #include "common.cuh"
+VOB_PDL_SWITCH(attention)
 
 // ---------------------------------------------------------------------------------------------
 // General kernel: one warp per (row, head). Keys are visited in chunks of 32: each lane scores
@@ -50,6 +51,8 @@ paged_attention_warp_kernel(const T* __restrict__ q, long long q_stride, T* __re
                             const int* __restrict__ block_tables, int max_pages,
                             const int* __restrict__ row_seq, const int* __restrict__ positions,
                             int T_rows, int H, int KV, int hd, int page_size, int window, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float qs_all[];
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long w = (long long)blockIdx.x * 4 + warp;
@@ -141,8 +144,8 @@ VOB_EXPORT int vob_paged_attention(const void* q, long long q_stride, void* out,
     long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return VOB_ERR_UNSUPPORTED;
     size_t smem = 4 * (size_t)hd * sizeof(float);
-    VOB_DISPATCH_ELEM(code, paged_attention_warp_kernel<ElemT><<<(unsigned)blocks, 128, smem, stream>>>(
+    VOB_DISPATCH_ELEM(code, return vob_launch(paged_attention_warp_kernel<ElemT>, dim3((unsigned)blocks), dim3(128), smem, stream,
         (const ElemT*)q, q_stride, (ElemT*)out, out_stride, (const ElemT*)kcache, (const ElemT*)vcache, block_tables,
         max_pages, row_seq, positions, T_rows, H, KV, hd, page_size, window, scale));
-    return vob_launch_status();
+    return 0;
 }

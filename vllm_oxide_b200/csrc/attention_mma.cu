@@ -19,6 +19,7 @@
 // Kernels take head_dim 64 or 128, page sizes that divide 64, G <= 16 for the decode kernel;
 // the launcher refuses anything else (the caller then uses the general kernel).
 #include "common.cuh"
+VOB_PDL_SWITCH(attention_mma)
 
 namespace {
 
@@ -180,6 +181,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
                         const int* __restrict__ context_lens, int H, int KV, int page_size, int window, float scale_log2) {
     constexpr int LD = HD + 8;
     constexpr int BM = 64;
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK0 = sQ + BM * LD;
@@ -295,6 +298,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
                        int H, int KV, int page_size, int window, float scale_log2, int splits,
                        float* __restrict__ part_ml, float* __restrict__ part_o) {
     constexpr int LD = HD + 8;
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
     __nv_bfloat16* sK0 = sQ + 16 * LD;
@@ -408,6 +413,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
 template <int HD>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_o, int splits,
                                          int H, __nv_bfloat16* __restrict__ out, long long out_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     size_t base = ((size_t)seq * H + head) * splits;
     float M = -INFINITY;
@@ -438,11 +445,10 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     }
     int G = H / KV;
     dim3 grid(((long long)max_new * G + 63) / 64, S, KV);
-    attn_prefill_mma_kernel<HD><<<grid, NTHREADS, prefill_smem<HD>(), stream>>>(
+    return vob_launch(attn_prefill_mma_kernel<HD>, grid, dim3(NTHREADS), prefill_smem<HD>(), stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, page_size, window,
         scale * 1.4426950408889634f);
-    return vob_launch_status();
 }
 
 template <int HD>
@@ -457,14 +463,13 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
         configured = true;
     }
     dim3 grid(S, KV, splits);
-    attn_decode_mma_kernel<HD><<<grid, NTHREADS, decode_smem<HD>(), stream>>>(
+    int e = vob_launch(attn_decode_mma_kernel<HD>, grid, dim3(NTHREADS), decode_smem<HD>(), stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, bt, max_pages, positions, H, KV, page_size, window, scale * 1.4426950408889634f,
         splits, part_ml, part_o);
-    int e = vob_launch_status();
     if (e || splits == 1) return e;
-    attn_decode_merge_kernel<HD><<<dim3(S, H), HD, 0, stream>>>(part_ml, part_o, splits, H, (__nv_bfloat16*)out, out_stride);
-    return vob_launch_status();
+    return vob_launch(attn_decode_merge_kernel<HD>, dim3(S, H), dim3(HD), 0, stream, (const float*)part_ml,
+                      (const float*)part_o, splits, H, (__nv_bfloat16*)out, out_stride);
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {

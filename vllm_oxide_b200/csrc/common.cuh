@@ -24,6 +24,36 @@ static inline int vob_launch_status() {
     return (int)e;
 }
 
+// Programmatic dependent launch. Every kernel of this package calls pdl_launch_dependents() first
+// thing (so the next kernel in the stream may start as soon as all blocks of this one have
+// started) and pdl_wait() before it touches anything an earlier kernel wrote or still reads (the
+// wait returns once every earlier grid has completed and its memory is visible). What a kernel
+// does between the two (barrier set-up, tensor-memory allocation, prefetch of weights, which no
+// kernel writes) overlaps the tail of its predecessors. Launches carry the attribute only while
+// the switch below is on; without it both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static int g_vob_pdl = 0;
+
+template <typename... P, typename... A>
+static inline int vob_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_vob_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+    return e != cudaSuccess ? (int)e : vob_launch_status();
+}
+
+#define VOB_PDL_SWITCH(module) VOB_EXPORT void vob_set_pdl_##module(int on) { g_vob_pdl = on; }
+
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {
     static constexpr int code = VOB_F32;

@@ -6,6 +6,7 @@
 // reductions, rotation angles and the activation are float32. One block works on one row, so a
 // row's result does not depend on what else is in the batch.
 #include "common.cuh"
+VOB_PDL_SWITCH(elementwise)
 
 // ---------------------------------------------------------------------------------------------
 // Embedding gather: out[t, :] = table[tokens[t], :]   (float32 out)
@@ -16,6 +17,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int h, int vocab, int* err_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     int tok = tokens[t];
     bool ok = tok >= 0 && tok < vocab;
@@ -29,8 +32,8 @@ VOB_EXPORT int vob_embed(const void* table, int table_code, const int* tokens, f
                          int vocab, int* err_flag, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (h <= 0 || vocab <= 0) return VOB_ERR_BAD_ARG;
-    VOB_DISPATCH_ELEM(table_code, embed_kernel<ElemT><<<T, 256, 0, stream>>>((const ElemT*)table, tokens, out, h, vocab, err_flag));
-    return vob_launch_status();
+    VOB_DISPATCH_ELEM(table_code, return vob_launch(embed_kernel<ElemT>, dim3(T), dim3(256), 0, stream, (const ElemT*)table, tokens, out, h, vocab, err_flag));
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -49,6 +52,8 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, const int* __restrict__ rows,
                                    TO* __restrict__ out, int h, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float row[];
     __shared__ float red[32];
     int r = blockIdx.x;
@@ -115,6 +120,8 @@ template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
                        const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
@@ -168,15 +175,13 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const float* weig
     bool aligned = (h % 4 == 0) && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) % 16 == 0);
     int nv = (h / 4 + 255) / 256;
     if (aligned && nv <= 8) {
-#define VEC(NV) add_rmsnorm_vec_kernel<TD, TO, NV><<<R, 256, 0, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
+#define VEC(NV) return vob_launch(add_rmsnorm_vec_kernel<TD, TO, NV>, dim3(R), dim3(256), 0, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
         if (nv <= 1) VEC(1); else if (nv <= 2) VEC(2); else if (nv <= 4) VEC(4); else VEC(8);
 #undef VEC
-        return vob_launch_status();
     }
     size_t smem = (size_t)h * sizeof(float);
     if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
-    add_rmsnorm_kernel<TD, TO><<<R, 256, smem, stream>>>(resid, (const TD*)delta, weight, rows, (TO*)out, h, eps);
-    return vob_launch_status();
+    return vob_launch(add_rmsnorm_kernel<TD, TO>, dim3(R), dim3(256), smem, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps);
 }
 
 VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, const float* weight,
@@ -200,6 +205,8 @@ VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, 
 // ---------------------------------------------------------------------------------------------
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ resid, const TD* __restrict__ delta, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += ld_f(delta + i);
 }
@@ -207,8 +214,8 @@ __global__ void add_residual_kernel(float* __restrict__ resid, const TD* __restr
 VOB_EXPORT int vob_add_residual(float* resid, const void* delta, int delta_code, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    VOB_DISPATCH_ELEM(delta_code, add_residual_kernel<ElemT><<<blocks, 256, 0, stream>>>(resid, (const ElemT*)delta, (size_t)n));
-    return vob_launch_status();
+    VOB_DISPATCH_ELEM(delta_code, return vob_launch(add_residual_kernel<ElemT>, dim3(blocks), dim3(256), 0, stream, resid, (const ElemT*)delta, (size_t)n));
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -233,6 +240,8 @@ rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, l
                      const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
                      T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
     // one thread per (head, pair i): heads 0..H-1 are q heads, H..H+KV-1 are k heads (with their v)
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     int half = hd >> 1;
     int e = blockIdx.y * blockDim.x + threadIdx.x;
@@ -287,10 +296,10 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
     int pairs = (H + (k ? KV : 0)) * (hd / 2);
     dim3 grid(T, (pairs + 127) / 128);
     if (grid.y > 65535) return VOB_ERR_UNSUPPORTED;
-    VOB_DISPATCH_ELEM(code, rope_kv_write_kernel<ElemT><<<grid, 128, 0, stream>>>(
+    VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_kernel<ElemT>, grid, dim3(128), 0, stream,
         (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
         (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
-    return vob_launch_status();
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -301,6 +310,8 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
     int j = blockIdx.y * blockDim.x + threadIdx.x;
     if (j >= I) return;
     const T* r = in + (size_t)blockIdx.x * in_stride;
@@ -311,6 +322,8 @@ __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* 
 // 16 bytes per load: 8 bfloat16 or 4 float per thread (I a multiple of that, rows 16-byte aligned).
 template <typename T, int N>
 __global__ void swiglu_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
     int j = (blockIdx.y * blockDim.x + threadIdx.x) * N;
     if (j >= I) return;
     const T* r = in + (size_t)blockIdx.x * in_stride;
@@ -336,13 +349,12 @@ static int launch_swiglu(const void* in, long long in_stride, void* out, int T_r
         int per = 256 * N;
         if ((I + per - 1) / per > 65535) return VOB_ERR_UNSUPPORTED;
         dim3 grid(T_rows, (I + per - 1) / per);
-        swiglu_vec_kernel<T, N><<<grid, 256, 0, stream>>>((const T*)in, in_stride, (T*)out, I);
+        return vob_launch(swiglu_vec_kernel<T, N>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
     } else {
         if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
         dim3 grid(T_rows, (I + 255) / 256);
-        swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)in, in_stride, (T*)out, I);
+        return vob_launch(swiglu_kernel<T>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
     }
-    return vob_launch_status();
 }
 
 VOB_EXPORT int vob_swiglu(const void* in, long long in_stride, void* out, int code, int T, int I,

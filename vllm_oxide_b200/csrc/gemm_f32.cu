@@ -7,6 +7,7 @@
 // Launch: 64x64 output tile per block, 256 threads, 4x4 outputs per thread, K in slabs of 16
 // through shared memory. Bound: CUDA-core FMA throughput. Any M, N, K >= 1; edges are guarded.
 #include "common.cuh"
+VOB_PDL_SWITCH(gemm_f32)
 
 #define TM 64
 #define TN 64
@@ -15,6 +16,8 @@
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
                 float* __restrict__ C, long long ldc, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[TK][TM + 4];
     __shared__ float Ws[TK][TN + 4];
     int tid = threadIdx.x;
@@ -94,6 +97,5 @@ VOB_EXPORT int vob_gemm_f32(const float* A, long long lda, const float* W, long 
     if (K <= 0 || lda < K || ldw < K || ldc < N) return VOB_ERR_BAD_ARG;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return VOB_ERR_UNSUPPORTED;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
-    return vob_launch_status();
+    return vob_launch(gemm_f32_kernel, grid, dim3(256), 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
 }

@@ -27,6 +27,7 @@
 // stops issuing work, frees its tensor memory and returns; the host turns the flag into an
 // exception. No TMA load uses cluster multicast.
 #include "common.cuh"
+VOB_PDL_SWITCH(gemm_sm100)
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -124,6 +125,7 @@ template <int BT, int STAGES, typename OutT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ C,
                   long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag) {
+    pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -157,7 +159,20 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // Weights are written by no kernel, so their loads start at once and overlap whatever
+            // still runs before this kernel; the activations are loaded only after the wait.
+            const int pre = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                unsigned char* a = tiles + i * stage_bytes<BT>();
+                mbar_expect_tx(full_bar + i, stage_bytes<BT>());
+                tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + i);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                unsigned char* b = tiles + i * stage_bytes<BT>() + BM * BK * 2;
+                tma_load_2d(b, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + i);
+            }
+            for (int i = pre; i < nkb; ++i) {
                 int s = i % STAGES;
                 uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, err_flag, 1)) break;
@@ -194,6 +209,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) ... + 31
         const int quad = warp & 3;
         const int f = m_tile * BM + quad * 32 + lane;          // this thread's output feature
+        pdl_wait();
         bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -337,13 +353,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = smem_bytes<BT, STAGES>();
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;            // the blocks that share one tile
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_vob_pdl ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<BT, STAGES, OutT>, mw, mx, (OutT*)C, ldc, T, N, K, kb_per, err_flag);
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }

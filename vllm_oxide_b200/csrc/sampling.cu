@@ -13,6 +13,7 @@
 // (value, index) pair in scratch memory, `pick_final` reduces a row's pairs. The scratch is
 // [R, splits] pairs supplied by the caller. Bound: memory (R * V * 4 bytes read once).
 #include "common.cuh"
+VOB_PDL_SWITCH(sampling)
 
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
@@ -56,6 +57,8 @@ __global__ void __launch_bounds__(256)
 pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
                     const uint32_t* __restrict__ seeds, const int* __restrict__ steps, int splits,
                     float* __restrict__ part_val, int* __restrict__ part_idx, int* __restrict__ nan_flags) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ Best sh[32];
     int r = blockIdx.y, sp = blockIdx.x;
     int per = (V + splits - 1) / splits;
@@ -90,6 +93,8 @@ pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const
 
 __global__ void pick_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                   int splits, int V, int* __restrict__ nan_flags, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ Best sh[32];
     int r = blockIdx.x;
     Best b{-INFINITY, 0x7fffffff};
@@ -119,10 +124,9 @@ VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, 
     if (V <= 0 || splits <= 0 || ld < V || R > 65535) return VOB_ERR_BAD_ARG;
     if (temperature && (!seeds || !steps)) return VOB_ERR_BAD_ARG;
     dim3 grid(splits, R);
-    pick_partial_kernel<<<grid, 256, 0, stream>>>(logits, ld, V, temperature, seeds, steps, splits, part_val,
-                                                  part_idx, nan_flags);
-    int e = vob_launch_status();
+    int e = vob_launch(pick_partial_kernel, grid, dim3(256), 0, stream, logits, ld, V, temperature, seeds, steps, splits,
+                       part_val, part_idx, nan_flags);
     if (e) return e;
-    pick_final_kernel<<<R, 64, 0, stream>>>(part_val, part_idx, splits, V, nan_flags, out);
-    return vob_launch_status();
+    return vob_launch(pick_final_kernel, dim3(R), dim3(64), 0, stream, (const float*)part_val, (const int*)part_idx, splits, V,
+                      nan_flags, out);
 }

@@ -67,6 +67,7 @@ class ModelRunner:
         else:
             weights = weights_from_tensors(tensors_or_dir, manifest)
         kernels.preload()
+        kernels.set_pdl(bool(engine.pdl))
         self.spec: ModelSpec = arch.build(config, weights, BuildContext(dtype=self.dtype, device=self.device))
         del weights
         # As in the reference, the longest sequence is the engine's limit, not config.json's

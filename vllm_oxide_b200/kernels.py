@@ -87,6 +87,7 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 
 _fn_cache = {}
+_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "sampling")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -151,10 +152,23 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
-def preload(modules=("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "sampling")) -> None:
+def preload(modules=_MODULES) -> None:
     """Build and load kernel modules now (so that compile time is spent at start-up)."""
     for m in modules:
         load_cuda_module(m)
+
+
+def set_pdl(on: bool) -> None:
+    """Switch programmatic dependent launch on or off for every kernel of this package: with it, a
+    kernel's set-up (and a matrix product's first weight loads) overlaps the end of the kernel
+    before it; each kernel still waits for its predecessors before it reads or writes anything
+    they touch."""
+    for m in _MODULES:
+        lib = load_cuda_module(m)
+        f = getattr(lib, f"vob_set_pdl_{m}")
+        f.argtypes = [_I]
+        f.restype = None
+        f(1 if on else 0)
 
 
 # ------------------------------------------------------------------------------------ embedding

@@ -285,28 +285,30 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
 // ---------------------------------------------------------------------------------------------
 // Steps of single decoded tokens. Grid (requests, kv heads, splits): a block reads its share of
 // the request's key tiles once for all G heads of the group; its 4 warps split every tile's 64
-// keys (16 each) and combine through shared memory; with more than one split the block writes an
-// unnormalised partial (running maximum, sum, weighted values) to scratch and a second kernel
-// merges the splits in a fixed order. Bound: the K/V reads (memory).
-// Scratch layout: part_ml [requests][H][splits][2], part_o [requests][H][splits][HD], float32.
+// keys (16 each) and combine through shared memory. The `splits` blocks of one (request, kv
+// head) form a thread-block cluster: each leaves its unnormalised partial (running maximum, sum,
+// weighted values) in its own shared memory, the cluster meets at a barrier, and every block
+// then finishes a share of the outputs by reading its peers' partials through distributed shared
+// memory in rank order (a fixed order, so the result does not depend on timing). K/V tiles go
+// through a cp.async ring of three stages (two when the grid is so large that the smaller
+// footprint lets one more block live on an SM). Bound: the K/V reads (memory).
 // ---------------------------------------------------------------------------------------------
-template <int HD>
+template <int HD, int DEC_STAGES>
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
-                       int H, int KV, int page_size, int window, float scale_log2, int splits,
-                       float* __restrict__ part_ml, float* __restrict__ part_o) {
+                       int H, int KV, int page_size, int window, float scale_log2) {
     constexpr int LD = HD + 8;
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
-    __nv_bfloat16* sK0 = sQ + 16 * LD;
-    __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
+    __nv_bfloat16* sK0 = sQ + 16 * LD;                                          // DEC_STAGES x BN x LD
+    __nv_bfloat16* sV0 = sK0 + DEC_STAGES * BN * LD;
 
     const int G = H / KV;
-    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const int p = positions[seq];                 // one row per request: row index == request index
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_tables + (size_t)seq * max_pages;
@@ -324,8 +326,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         if (r < G && p >= 0) cp_async16(dst, q + (size_t)seq * q_stride + (size_t)(kvh * G + r) * HD + ch * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    if (t_begin < t_end) load_kv_tile<HD>(sK0, sV0, kc, vc, bt, kvh, KV, page_size, t_begin * BN, lo_key, hi);
-    cp_async_commit();
+    // prologue: the first DEC_STAGES - 1 tiles, one commit group each (empty groups keep the count)
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (t_begin + s < t_end)
+            load_kv_tile<HD>(sK0 + s * BN * LD, sV0 + s * BN * LD, kc, vc, bt, kvh, KV, page_size, (t_begin + s) * BN, lo_key, hi);
+        cp_async_commit();
+    }
 
     int pos[2], lo[2];
 #pragma unroll
@@ -343,14 +350,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     uint32_t qf[HD / 16][4];
 
     for (int t = t_begin; t < t_end; ++t) {
-        int buf = (t - t_begin) & 1;
+        int buf = (t - t_begin) % DEC_STAGES;
         __nv_bfloat16* sK = sK0 + buf * BN * LD;
         __nv_bfloat16* sV = sV0 + buf * BN * LD;
-        cp_async_wait<0>();
-        __syncthreads();
-        if (t + 1 < t_end) {
-            load_kv_tile<HD>(sK0 + (buf ^ 1) * BN * LD, sV0 + (buf ^ 1) * BN * LD, kc, vc, bt, kvh, KV, page_size,
-                             (t + 1) * BN, lo_key, hi);
+        cp_async_wait<DEC_STAGES - 2>();        // tile t has landed (one newer group may be in flight)
+        __syncthreads();                        // ... for every thread; and everyone is done with tile t-1
+        {
+            int tn = t + DEC_STAGES - 1;        // refill the buffer tile t-1 used
+            int nb = (tn - t_begin) % DEC_STAGES;
+            if (tn < t_end)
+                load_kv_tile<HD>(sK0 + nb * BN * LD, sV0 + nb * BN * LD, kc, vc, bt, kvh, KV, page_size, tn * BN, lo_key, hi);
             cp_async_commit();
         }
         if (t == t_begin) {
@@ -374,6 +383,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     float* cm = reinterpret_cast<float*>(sK0);                  // [4 warps][16 rows] max
     float* cl = cm + 64;                                        // [4][16] sum
     float* co = cl + 64;                                        // [4][16][HD]
+    float* fin = co + 4 * 16 * HD;                              // this block's partial: [16][HD] values, [16] max, [16] sum
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         int r = (lane >> 2) + h * 8;
@@ -396,41 +406,57 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             acc += f * co[(w * 16 + r) * HD + d];
             L += f * cl[w * 16 + r];
         }
-        int head = kvh * G + r;
         if (splits == 1) {
-            if (p >= 0) out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
-            else out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(0.f);
+            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
-            size_t idx = ((size_t)seq * H + head) * splits + split;
-            part_o[idx * HD + d] = acc;
-            if (d == 0) { part_ml[idx * 2] = M; part_ml[idx * 2 + 1] = L; }
+            fin[r * HD + d] = acc;
+            if (d == 0) { fin[16 * HD + r] = M; fin[16 * HD + 16 + r] = L; }
         }
     }
-}
-
-// Merge the splits of every (request, head): a fixed order, so the result does not depend on
-// which block finished first. Grid (requests, H), HD threads.
-template <int HD>
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_o, int splits,
-                                         int H, __nv_bfloat16* __restrict__ out, long long out_stride) {
-    pdl_launch_dependents();
-    pdl_wait();
-    int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-    size_t base = ((size_t)seq * H + head) * splits;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float Ms = M == -INFINITY ? 0.f : M;
-    float acc = 0.f, L = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        float f = exp2f(part_ml[(base + s) * 2] - Ms);
-        acc += f * part_o[(base + s) * HD + d];
-        L += f * part_ml[(base + s) * 2 + 1];
+    if (splits > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t fin_local = smem_u32(fin);
+        const int total = G * HD;
+        const int chunk = (total + splits - 1) / splits;
+        const int e0 = split * chunk, e1 = min(total, e0 + chunk);
+        for (int e = e0 + threadIdx.x; e < e1; e += NTHREADS) {
+            int r = e / HD, d = e - r * HD;
+            float pm[8], pl[8], po[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                pm[k] = -INFINITY; pl[k] = 0.f; po[k] = 0.f;
+                if (k < splits) {
+                    uint32_t base;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base) : "r"(fin_local), "r"(k));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(po[k]) : "r"(base + (uint32_t)((r * HD + d) * 4)) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pm[k]) : "r"(base + (uint32_t)((16 * HD + r) * 4)) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pl[k]) : "r"(base + (uint32_t)((16 * HD + 16 + r) * 4)) : "memory");
+                }
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) M = fmaxf(M, pm[k]);
+            float Ms = M == -INFINITY ? 0.f : M;
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {                       // rank order; ranks beyond the last add zero
+                float f = exp2f(pm[k] - Ms);
+                acc += f * po[k];
+                L += f * pl[k];
+            }
+            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+        // nobody leaves (and frees its shared memory) while a peer may still be reading it
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
-    out[(size_t)seq * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
 template <int HD> constexpr size_t prefill_smem() { return (size_t)(64 + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16); }
-template <int HD> constexpr size_t decode_smem() { return (size_t)(16 + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16); }
+template <int HD, int DEC_STAGES> constexpr size_t decode_smem() {
+    size_t ring = (size_t)(16 + 2 * DEC_STAGES * BN) * (HD + 8) * sizeof(__nv_bfloat16);
+    size_t combine = 16 * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)(128 + 4 * 16 * HD + 16 * HD + 32) * sizeof(float);
+    return ring > combine ? ring : combine;
+}
 
 template <int HD>
 int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
@@ -451,25 +477,56 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
         scale * 1.4426950408889634f);
 }
 
-template <int HD>
-int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
+template <int HD, int ST>
+int launch_decode_st(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                   const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                  float scale, int splits, float* part_ml, float* part_o, cudaStream_t stream) {
+                  float scale, int splits, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)decode_smem<HD>());
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)decode_smem<HD, ST>());
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(S, KV, splits);
-    int e = vob_launch(attn_decode_mma_kernel<HD>, grid, dim3(NTHREADS), decode_smem<HD>(), stream,
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
-        (const __nv_bfloat16*)vc, bt, max_pages, positions, H, KV, page_size, window, scale * 1.4426950408889634f,
-        splits, part_ml, part_o);
-    if (e || splits == 1) return e;
-    return vob_launch(attn_decode_merge_kernel<HD>, dim3(S, H), dim3(HD), 0, stream, (const float*)part_ml,
-                      (const float*)part_o, splits, H, (__nv_bfloat16*)out, out_stride);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(S, KV, splits);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = decode_smem<HD, ST>();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;            // the blocks that share one (request, kv head)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_vob_pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
+                                       out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
+                                       H, KV, page_size, window, scale * 1.4426950408889634f);
+    return e != cudaSuccess ? (int)e : vob_launch_status();
+}
+
+template <int HD>
+int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
+                  const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
+                  float scale, int splits, cudaStream_t stream) {
+    static int num_sms = 0;
+    if (!num_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (num_sms <= 0) num_sms = 148;
+    }
+    // three stages while every block of the grid can be resident at once with them; else two
+    long long blocks = (long long)S * KV * splits;
+    long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>() + 1024));
+    if (blocks <= fit3)
+        return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
+                                       window, scale, splits, stream);
+    return launch_decode_st<HD, 2>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
+                                   window, scale, splits, stream);
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {
@@ -498,17 +555,16 @@ VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out
                                context_lens, S, max_new, H, KV, page_size, window, scale, stream);
 }
 
-// Scratch: part_ml needs S * H * splits * 2 floats, part_o S * H * splits * hd floats (unused when splits == 1).
+// `splits` (1..8) blocks share each (request, kv head) as one cluster.
 VOB_EXPORT int vob_attn_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                                    const void* vcache, const int* block_tables, int max_pages, const int* positions, int S,
                                    int H, int KV, int hd, int page_size, int window, float scale, int splits,
-                                   float* part_ml, float* part_o, cudaStream_t stream) {
+                                   cudaStream_t stream) {
     if (S <= 0) return 0;
     if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
-    if (q_stride % 8 != 0 || splits < 1 || splits > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
-    if (splits > 1 && (!part_ml || !part_o)) return VOB_ERR_BAD_ARG;
+    if (q_stride % 8 != 0 || splits < 1 || splits > 8 || KV > 65535) return VOB_ERR_BAD_ARG;
     if (hd == 64) return launch_decode<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
-                                          H, KV, page_size, window, scale, splits, part_ml, part_o, stream);
+                                          H, KV, page_size, window, scale, splits, stream);
     return launch_decode<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
-                              page_size, window, scale, splits, part_ml, part_o, stream);
+                              page_size, window, scale, splits, stream);
 }

@@ -282,6 +282,133 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Many tokens (prompt portions): a persistent form of the same kernel. One block per SM walks
+// over output tiles (tile id -> weight-row block id / n_tiles, token block id % n_tiles, so the
+// blocks running at one time share weight tiles and keep all of X in L2). The accumulator is
+// double buffered in tensor memory (2 x BT columns): while the four epilogue warps drain one
+// buffer to C, the MMA warp already fills the other, and the TMA ring runs ahead across tile
+// boundaries; so the tensor cores never wait for an epilogue. Bound: tensor-core throughput.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BT, int STAGES, typename OutT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_sm100_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                             OutT* __restrict__ C, long long ldc, int T, int N, int K, int* __restrict__ err_flag) {
+    pdl_launch_dependents();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * stage_bytes<BT>());
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;           // [2]
+    uint64_t* acc_empty = acc_full + 2;                // [2]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_kb = (K + BK - 1) / BK;
+    const int m_tiles = (N + BM - 1) / BM, n_tiles = (T + BT - 1) / BT;
+    const int num_tiles = m_tiles * n_tiles;
+    constexpr int ACC_COLS = 2 * BT;                   // 256 or 512 columns: a power of two
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(ACC_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_holder;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, err_flag, 1)) { ok = false; break; }
+                    unsigned char* a = tiles + s * stage_bytes<BT>();
+                    mbar_expect_tx(full_bar + s, stage_bytes<BT>());
+                    tma_load_2d(a, &map_w, kb * BK, m_tile * BM, full_bar + s);
+                    tma_load_2d(a + BM * BK * 2, &map_x, kb * BK, n_tile * BT, full_bar + s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BT);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1, aph = (local >> 1) & 1;
+                if (!mbar_wait(acc_empty + buf, aph ^ 1, abort_flag, err_flag, 2)) break;     // drained by the epilogue
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * BT;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full_bar + s, ph, abort_flag, err_flag, 2)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned char* a = tiles + s * stage_bytes<BT>();
+                    uint64_t adesc = umma_desc_sw128(a);
+                    uint64_t bdesc = umma_desc_sw128(a + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty_bar + s);
+                }
+                if (ok) umma_commit(acc_full + buf);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        uint32_t local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+            const uint32_t buf = local & 1, aph = (local >> 1) & 1;
+            if (!mbar_wait(acc_full + buf, aph, abort_flag, err_flag, 3)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + buf * BT + ((uint32_t)(quad * 32) << 16);
+            const int f = m_tile * BM + quad * 32 + lane;
+            const int t0 = n_tile * BT;
+#pragma unroll 2
+            for (int c = 0; c < BT; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (f < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        int t = t0 + c + j;
+                        if (t < T) store_out<OutT>(C + (size_t)t * ldc + f, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty + buf);                   // 128 arrivals hand the buffer back to the MMA warp
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -366,6 +493,27 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }
 
+template <int BT, int STAGES, typename OutT>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int* err_flag,
+                      cudaStream_t stream) {
+    static bool configured = false;
+    static int num_sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_persistent_kernel<BT, STAGES, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<BT, STAGES>());
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (num_sms <= 0) num_sms = 148;
+        configured = true;
+    }
+    int tiles = ((N + BM - 1) / BM) * ((T + BT - 1) / BT);
+    int grid = tiles < num_sms ? tiles : num_sms;
+    return vob_launch(gemm_sm100_persistent_kernel<BT, STAGES, OutT>, dim3(grid), dim3(NTHREADS), smem_bytes<BT, STAGES>(), stream,
+                      mw, mx, (OutT*)C, ldc, T, N, K, err_flag);
+}
+
 int pick_bt(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 }  // namespace
@@ -393,6 +541,16 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0) return VOB_ERR_UNSUPPORTED;
     if (out_code != VOB_F32 && out_code != VOB_BF16) return VOB_ERR_BAD_ARG;
     int bt = pick_bt(T);
+    if (bt == 256) {
+        // 256-token tiles unless 128-token tiles fill the SMs in fewer token-columns of work
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        long long mt = (N + BM - 1) / BM;
+        long long w256 = ((mt * ((T + 255) / 256) + sms - 1) / sms) * 256;
+        long long w128 = ((mt * ((T + 127) / 128) + sms - 1) / sms) * 128;
+        if (w128 < w256) bt = 128;
+    }
     int total_kb = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
     if (splits > 8) splits = 8;
@@ -413,8 +571,13 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
         case 16: GO(16, 4);
         case 32: GO(32, 4);
         case 64: GO(64, 4);
-        case 128: GO(128, 4);
-        default: GO(256, 4);
+        default: break;
     }
 #undef GO
+#define GOP(BT, ST)                                                                                                \
+    return out_code == VOB_F32 ? launch_persistent<BT, ST, float>(mw, mx, C, ldc, T, N, K, err_flag, stream)          \
+                               : launch_persistent<BT, ST, __nv_bfloat16>(mw, mx, C, ldc, T, N, K, err_flag, stream)
+    if (bt == 128) { GOP(128, 6); }
+    GOP(256, 4);
+#undef GOP
 }

@@ -493,39 +493,28 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
              head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
 
 
-def attn_decode_scratch_floats(num_seqs: int, num_heads: int, head_dim: int, splits: int) -> int:
-    return num_seqs * num_heads * splits * (head_dim + 2) if splits > 1 else 0
-
-
 @_timed
 def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int = 0, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+                    scale: float, window: int = 0, splits: int = 1) -> None:
     """Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
-    With splits > 1 each request's keys are shared out over `splits` blocks and merged by a second
-    kernel; `scratch` (float32) needs attn_decode_scratch_floats(...) elements."""
+    With splits > 1 (at most 8) each request's keys are shared out over the blocks of a cluster,
+    which merge their partial results through distributed shared memory."""
     op = "attn_decode_mma"
     _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
-    _cuda(op, positions, scratch)
+    _cuda(op, positions)
     S = q.shape[0]
     _int32_vec(positions, S, op, "positions")
     if block_tables.shape[0] < S:
         raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {S} requests")
     if num_heads // num_kv_heads > 16:
         raise ShapeError(op, f"{num_heads // num_kv_heads} heads per kv head: the decode kernel takes at most 16")
-    ml = po = None
-    launches = 1
-    if splits > 1:
-        need = attn_decode_scratch_floats(S, num_heads, head_dim, splits)
-        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_contiguous():
-            raise ShapeError(op, f"scratch must be contiguous float32 with at least {need} elements")
-        n_ml = S * num_heads * splits * 2
-        ml, po = scratch[:n_ml], scratch[n_ml:need]
-        launches = 2
+    if not 1 <= splits <= 8:
+        raise ShapeError(op, f"splits must be 1..8, got {splits}")
     f = _fn("attention_mma", "vob_attn_decode_mma",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P])
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
              block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
-             float(scale), int(splits), _ptr(ml), _ptr(po), _stream()), op, launches=launches)
+             float(scale), int(splits), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ sampling

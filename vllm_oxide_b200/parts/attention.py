@@ -62,7 +62,7 @@ class Attention(Mixer):
 
     def workspace_bytes(self, rows: int) -> int:
         es = 2 if self.dtype == torch.bfloat16 else 4
-        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + rows * self.H * 16 * (self.hd + 2) * 4 + 3 * 256
+        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + 2 * 256
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
         if cache is None:
@@ -90,12 +90,8 @@ class Attention(Mixer):
         bt = ctx.block_tables[cache.group]
         if self.dtype == torch.bfloat16 and self.impl != "general":
             if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
-                splits = self.decode_splits(ctx.rows)
-                scratch = None
-                if splits > 1:
-                    scratch = ctx.alloc((kernels.attn_decode_scratch_floats(ctx.rows, self.H, self.hd, splits),), torch.float32)
                 kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd,
-                                        self.scale, self.window, splits, scratch)
+                                        self.scale, self.window, self.decode_splits(ctx.rows))
                 return
             if not ctx.decode_only and ctx.max_new > 0 and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, False):
                 kernels.attn_prefill_mma(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,
@@ -106,6 +102,6 @@ class Attention(Mixer):
 
     def decode_splits(self, num_seqs: int) -> int:
         """How many blocks share one request's keys in a decode step: enough that the grid fills
-        the GPU twice over, at most 16."""
+        the GPU twice over, at most 8 (the blocks of one request form a cluster)."""
         blocks = max(1, num_seqs * self.KV)
-        return max(1, min(16, -(-2 * self.num_sms // blocks)))
+        return max(1, min(8, -(-2 * self.num_sms // blocks)))

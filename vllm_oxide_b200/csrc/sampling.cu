@@ -130,3 +130,53 @@ VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, 
     return vob_launch(pick_final_kernel, dim3(R), dim3(64), 0, stream, (const float*)part_val, (const int*)part_idx, splits, V,
                       nan_flags, out);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same pick for callers that cannot allocate: scratch in a fixed device array of this
+// library (see no_alloc.h for who needs this and the rules that come with it).
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) unsigned char vob_pick_static_scratch[VOB_PICK_STATIC_BYTES];
+
+// Device address of the array on the current device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use; the address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static int pick_static_scratch_address(unsigned char** ptr) {
+    static std::mutex mu;
+    static unsigned char* known[64] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return VOB_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> g(mu);
+    if (!known[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, vob_pick_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        known[dev] = static_cast<unsigned char*>(p);
+    }
+    *ptr = known[dev];
+    return 0;
+}
+
+int vob_pick_tokens_static(const float* logits, long long ld, int R, int V, const float* temperature,
+                           const uint32_t* seeds, const int* steps, int* out, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (R > VOB_PICK_STATIC_MAX_ROWS) return VOB_ERR_STATIC_TOO_LARGE;
+    if (V <= 0 || ld < V || !logits || !out) return VOB_ERR_BAD_ARG;
+    if (temperature && (!seeds || !steps)) return VOB_ERR_BAD_ARG;
+    int splits = vob_pick_splits(V);
+    if (splits > VOB_PICK_STATIC_MAX_SPLITS) return VOB_ERR_STATIC_TOO_LARGE;
+    unsigned char* base = nullptr;
+    int rc = pick_static_scratch_address(&base);
+    if (rc) return rc;
+    float* part_val = reinterpret_cast<float*>(base);
+    int* part_idx = reinterpret_cast<int*>(base + VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 4);
+    int* nan_flags = reinterpret_cast<int*>(base + VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 8);
+    // the array keeps what the last call left: the NaN marks must start at zero
+    cudaError_t e = cudaMemsetAsync(nan_flags, 0, sizeof(int) * R, stream);
+    if (e != cudaSuccess) return (int)e;
+    return vob_pick_tokens(logits, ld, R, V, temperature, seeds, steps, splits, part_val, part_idx, nan_flags, out, stream);
+}

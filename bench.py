@@ -215,7 +215,7 @@ def main():
         return B * steps / dt
     e2e_steps = min(a.steps, GEN_LEN - a.warmup - 2)
     e2e_val = decode_e2e(a.batch, e2e_steps, a.warmup)
-    e2e = {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": runner.decode_layout["total"] * 4,
+    e2e = {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": runner.last_upload_bytes,
            "d2h_bytes_per_step": 4 * a.batch}
 
     points = {}

@@ -174,6 +174,26 @@ def runtime_module():
         return mod
 
 
+def ensure_built(modules) -> None:
+    """Compile the given CUDA modules (those that are stale) side by side, so that a first call
+    waits for the slowest file rather than for the sum."""
+    errors: List[str] = []
+
+    def one(m):
+        try:
+            cuda_library_path(m)
+        except KernelError as e:
+            errors.append(str(e))
+
+    threads = [threading.Thread(target=one, args=(m,)) for m in modules]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if errors:
+        raise KernelError("\n\n".join(errors))
+
+
 def build_all(verbose: bool = True) -> None:
     """Compile every module (in parallel); used by the build check and before a GPU run."""
     errors: List[str] = []

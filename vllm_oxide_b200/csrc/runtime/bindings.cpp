@@ -76,10 +76,11 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def_readonly("new_counts", &StepArrays::new_counts)
         .def_property_readonly("layout", [](const StepArrays& a) { return layout_dict(a.layout); })
         .def_property_readonly("total", [](const StepArrays& a) { return a.layout.total; })
+        .def_readonly("used", &StepArrays::used)
         // Copy the packed int32 buffer into a caller-owned (pinned) array of at least `total` ints.
         .def("copy_into", [](const StepArrays& a, py::array_t<int32_t, py::array::c_style> dst) {
-            if ((size_t)dst.size() < a.data.size()) throw CacheError("copy_into: destination too small");
-            std::memcpy(dst.mutable_data(), a.data.data(), a.data.size() * sizeof(int32_t));
+            if ((size_t)dst.size() < (size_t)a.used) throw CacheError("copy_into: destination too small");
+            std::memcpy(dst.mutable_data(), a.data.data(), (size_t)a.used * sizeof(int32_t));
         })
         .def("data", [](const StepArrays& a) {
             return py::array_t<int32_t>((py::ssize_t)a.data.size(), a.data.data());
@@ -110,6 +111,9 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
 
     py::class_<StepPlan>(m, "StepPlan")
         .def_readonly("entries", &StepPlan::entries)
+        .def_property_readonly("num_entries", [](const StepPlan& p) { return p.entries.size(); })
+        .def_property_readonly("decode_only", &StepPlan::decode_only)
+        .def("sampling_ids", &StepPlan::sampling_ids)
         .def_readonly("preempted", &StepPlan::preempted)
         .def_readonly("admitted", &StepPlan::admitted)
         .def_readonly("failed", &StepPlan::failed);

@@ -50,6 +50,17 @@ struct PlannedEntry {
 
 struct StepPlan {
     std::vector<PlannedEntry> entries;
+    // every entry is one token that reaches its request's end: a pure decode step
+    bool decode_only() const {
+        if (entries.empty()) return false;
+        for (const auto& e : entries) if (e.count != 1 || !e.sample) return false;
+        return true;
+    }
+    std::vector<int64_t> sampling_ids() const {
+        std::vector<int64_t> v;
+        for (const auto& e : entries) if (e.sample) v.push_back(e.id);
+        return v;
+    }
     std::vector<int64_t> preempted;      // requests preempted while planning this step
     std::vector<int64_t> admitted;       // requests that entered the running set
     std::vector<std::pair<int64_t, std::string>> failed;   // finished without running: (id, reason)

@@ -67,6 +67,7 @@ struct StepArrays {
     bool any_sampling = false;      // some row has temperature > 0
     std::vector<int64_t> ids;       // request of each sequence, in batch order
     std::vector<int32_t> new_counts;
+    int used = 0;                   // ints from the start of `data` that this batch actually fills
 };
 
 // Lay the entries out. Every request must be admitted and must already hold pages for its new
@@ -148,10 +149,9 @@ inline StepArrays build_step(const CacheManager& cache, const std::vector<StepEn
     }
     d[L.seq_starts + S] = row;
     for (int s = S + 1; s <= seqs_cap; ++s) d[L.seq_starts + s] = row;
-    // padding requests read request 0's block table so that padded rows touch valid pages only
-    for (int g = 0; g < G; ++g)
-        for (int s = S; s < seqs_cap; ++s)
-            std::memcpy(d + L.block_tables[g] + (size_t)s * max_pages, d + L.block_tables[g], sizeof(int32_t) * max_pages);
+    // Padding rows carry position -1 and read no block table, so with one group (whose block
+    // tables are the last section) only the first S rows of it need to reach the device.
+    A.used = G == 1 ? L.block_tables[0] + S * max_pages : L.total;
     A.rows = T; A.seqs = S; A.logit_count = R;
     return A;
 }

@@ -118,9 +118,10 @@ class LLM:
         for rid in plan.admitted:
             r.pools.reset_slot(r.manager.state_slot(rid))
         done = []
-        if plan.entries:
-            decode_only = all(e.count == 1 and e.sample for e in plan.entries)
-            want_logits = any(e.sample and self._params[e.id].capture_logits for e in plan.entries)
+        if plan.num_entries:
+            decode_only = plan.decode_only
+            sampling = plan.sampling_ids()
+            want_logits = any(self._params[i].capture_logits for i in sampling)
             if decode_only and r.graphs_enabled and not want_logits:
                 sampled = r.decode_step_graph(sched, plan)
                 self.stats["graph_steps"] += 1
@@ -133,21 +134,17 @@ class LLM:
                     buf = self._logit_buf
                 sampled = r.step(arrays, logits_out=buf).tokens()
                 if want_logits:
-                    row = 0
-                    for e in plan.entries:
-                        if not e.sample:
-                            continue
-                        g = self._generated[e.id]
-                        if g in self._params[e.id].capture_logits:
-                            self._captured[e.id][g] = buf[row].cpu()
-                        row += 1
-            if any(t < 0 for t in sampled):
+                    for row, rid in enumerate(sampling):
+                        g = self._generated[rid]
+                        if g in self._params[rid].capture_logits:
+                            self._captured[rid][g] = buf[row].cpu()
+            if min(sampled, default=0) < 0:
                 raise NaNError("pick_tokens")        # crates/engine/src/backend/cpu/mod.rs:377-379
             self.stats["steps"] += 1
             self.stats["decode_steps"] += int(decode_only)
-            for e in plan.entries:
-                if e.sample:
-                    self._generated[e.id] += 1
+            gen = self._generated
+            for rid in sampling:
+                gen[rid] += 1
             done = sched.update(plan, sampled)
         else:
             done = sched.take_done()
@@ -168,13 +165,14 @@ class LLM:
         host-side token lists receive placeholders."""
         r, sched = self.runner, self.scheduler
         plan = sched.schedule()
-        if not plan.entries or plan.preempted or plan.admitted or not all(e.count == 1 and e.sample for e in plan.entries):
+        if not plan.decode_only or plan.preempted or plan.admitted:
             raise ShapeError("step_async", "only steady decode steps can run without reading tokens back")
         r.decode_step_graph(sched, plan, feed_from_device=True, read=False)
-        for e in plan.entries:
-            self._generated[e.id] += 1
+        ids = plan.sampling_ids()
+        for rid in ids:
+            self._generated[rid] += 1
         self.stats["steps"] += 1
-        for f in sched.update(plan, [0] * len(plan.entries)):
+        for f in sched.update(plan, [0] * len(ids)):
             self._forget(f.id)
 
     def drain_async(self) -> None:

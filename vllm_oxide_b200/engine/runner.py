@@ -66,8 +66,8 @@ class ModelRunner:
             weights = load_safetensors_weights(str(tensors_or_dir), manifest, device=self.device)
         else:
             weights = weights_from_tensors(tensors_or_dir, manifest)
-        kernels.preload()
         kernels.set_pdl(bool(engine.pdl))
+        kernels.preload(kernels.modules_for(self.dtype))
         self.spec: ModelSpec = arch.build(config, weights, BuildContext(dtype=self.dtype, device=self.device))
         del weights
         # As in the reference, the longest sequence is the engine's limit, not config.json's
@@ -97,7 +97,10 @@ class ModelRunner:
         self.pick_idx = torch.empty(self.logit_chunk * splits, dtype=torch.int32, device=self.device)
         self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
+        self.sampled_host = torch.zeros(self.seqs_cap, dtype=torch.int32, pin_memory=True)
+        self.sampled_host_np = self.sampled_host.numpy()
         self.steps_run = 0
+        self.last_upload_bytes = 0
         self.graphs_enabled = bool(engine.cuda_graphs)
         self.decode_layout = self.rt.step_layout(self.seqs_cap, self.seqs_cap, self.seqs_cap, G, self.max_pages)
         self._graphs = {}
@@ -151,7 +154,8 @@ class ModelRunner:
 
     def upload(self, arrays) -> None:
         """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
-        n = arrays.total
+        n = arrays.used
+        self.last_upload_bytes = 4 * n
         arrays.copy_into(self.step_host_np)
         self.step_dev[:n].copy_(self.step_host[:n], non_blocking=True)
 
@@ -229,7 +233,7 @@ class ModelRunner:
         class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing), because
         at small batches launching ~10 kernels per layer costs more than running them
         (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51)."""
-        S = len(plan.entries)
+        S = plan.num_entries
         L = self.decode_layout
         arrays = scheduler.arrays(plan, L["rows_cap"], L["seqs_cap"], L["logits_cap"], self.max_pages, self.spec.vocab_size)
         if arrays.max_seq_len > self.max_model_len:
@@ -258,7 +262,11 @@ class ModelRunner:
             graph.replay()
             kernels.count_launches(self._graph_launches[b])
         self.steps_run += 1
-        return self.sampled[:S].tolist() if read else []
+        if not read:
+            return []
+        # the picked tokens were copied to pinned host memory by the step itself
+        torch.cuda.current_stream().synchronize()
+        return self.sampled_host_np[:S].tolist()
 
     def _decode_eager(self, b: int) -> None:
         L = self.decode_layout
@@ -267,6 +275,7 @@ class ModelRunner:
         ctx.decode_only, ctx.max_new = True, 1
         resid, pending = self._forward(ctx)
         self._head(resid, pending, ctx, b, None, L)
+        self.sampled_host[:b].copy_(self.sampled[:b], non_blocking=True)
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def admit(self, request_id: int) -> int:

@@ -141,7 +141,7 @@ def _fn(module: str, name: str, argtypes):
     key = (module, name)
     f = _fn_cache.get(key)
     if f is None:
-        lib = load_cuda_module(module)
+        lib = _load(module)
         try:
             f = getattr(lib, name)
         except AttributeError:
@@ -152,23 +152,52 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
+_pdl_on = False
+
+
+def modules_for(dtype) -> tuple:
+    """The kernel modules an engine of this compute dtype uses: only these are compiled at its
+    first start."""
+    if dtype == torch.float32:
+        return ("elementwise", "gemm_f32", "attention", "sampling")
+    return ("elementwise", "gemm_sm100", "attention", "attention_mma", "sampling")
+
+
 def preload(modules=_MODULES) -> None:
-    """Build and load kernel modules now (so that compile time is spent at start-up)."""
+    """Build (side by side) and load kernel modules now, so that compile time is spent at start-up."""
+    from .csrc.build import ensure_built
+    ensure_built(modules)
     for m in modules:
-        load_cuda_module(m)
+        _load(m)
+
+
+def _load(module: str):
+    """dlopen a module and hand it the current launch switches."""
+    from .csrc.build import _loaded
+    fresh = module not in _loaded
+    lib = load_cuda_module(module)
+    if fresh:
+        f = getattr(lib, f"vob_set_pdl_{module}")
+        f.argtypes = [_I]
+        f.restype = None
+        f(1 if _pdl_on else 0)
+    return lib
 
 
 def set_pdl(on: bool) -> None:
     """Switch programmatic dependent launch on or off for every kernel of this package: with it, a
     kernel's set-up (and a matrix product's first weight loads) overlaps the end of the kernel
     before it; each kernel still waits for its predecessors before it reads or writes anything
-    they touch."""
+    they touch. Modules loaded later take the switch over."""
+    global _pdl_on
+    from .csrc.build import _loaded
+    _pdl_on = bool(on)
     for m in _MODULES:
-        lib = load_cuda_module(m)
-        f = getattr(lib, f"vob_set_pdl_{m}")
-        f.argtypes = [_I]
-        f.restype = None
-        f(1 if on else 0)
+        if m in _loaded:
+            f = getattr(_loaded[m], f"vob_set_pdl_{m}")
+            f.argtypes = [_I]
+            f.restype = None
+            f(1 if _pdl_on else 0)
 
 
 # ------------------------------------------------------------------------------------ embedding

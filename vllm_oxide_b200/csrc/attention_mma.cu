@@ -53,21 +53,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Gather one tile of 64 keys (K and V of one kv head) into shared memory. Keys outside
-// [lo, hi) are zero-filled and never touched in global memory.
+// [lo, hi) are zero-filled and never touched in global memory. Page numbers come from `s_pages`,
+// this block's copy of its request's block-table entries starting at logical page `page0` (a
+// global lookup per key would put a dependent L2 round trip in front of every copy); page sizes
+// are powers of two (they divide 64), so positions split into page and offset by shift and mask.
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* __restrict__ kc,
-                                             const __nv_bfloat16* __restrict__ vc, const int* __restrict__ bt, int kvh,
-                                             int KV, int page_size, int tile_start, int lo, int hi) {
+                                             const __nv_bfloat16* __restrict__ vc, const int* s_pages, int page0, int kvh,
+                                             int KV, int page_shift, int tile_start, int lo, int hi) {
     constexpr int LD = HD + 8;
     constexpr int CH = HD / 8;                 // 16-byte pieces per key
-    for (int c = threadIdx.x; c < BN * CH; c += NTHREADS) {
-        int key = c / CH, ch = c - key * CH;
+    constexpr int KEYS_PER_PASS = NTHREADS / CH;
+    const int ch = threadIdx.x % CH;
+    const int k0 = threadIdx.x / CH;
+    const int page_size = 1 << page_shift;
+#pragma unroll
+    for (int key = k0; key < BN; key += KEYS_PER_PASS) {
         int j = tile_start + key;
         __nv_bfloat16* dk = sK + key * LD + ch * 8;
         __nv_bfloat16* dv = sV + key * LD + ch * 8;
         if (j >= lo && j < hi) {
-            int page = bt[j / page_size];
-            size_t off = (((size_t)page * KV + kvh) * page_size + (j % page_size)) * HD + ch * 8;
+            int page = s_pages[(j >> page_shift) - page0];
+            size_t off = ((((size_t)page * KV + kvh) << page_shift) + (j & (page_size - 1))) * HD + ch * 8;
             cp_async16(dk, kc + off);
             cp_async16(dv, vc + off);
         } else {
@@ -178,7 +185,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                         long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                         const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
-                        const int* __restrict__ context_lens, int H, int KV, int page_size, int window, float scale_log2) {
+                        const int* __restrict__ context_lens, int H, int KV, int page_shift, int window, float scale_log2) {
     constexpr int LD = HD + 8;
     constexpr int BM = 64;
     pdl_launch_dependents();
@@ -187,6 +194,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK0 = sQ + BM * LD;
     __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
+    int* s_pages = reinterpret_cast<int*>(sV0 + 2 * BN * LD);            // [max_pages]
 
     const int G = H / KV;
     const int seq = blockIdx.y, kvh = blockIdx.z;
@@ -217,8 +225,12 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     const int first_tok_pos = ctx + tile_row0 / G;
     const int lo_blk = window > 0 ? max(0, first_tok_pos + 1 - window) : 0;
     const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
+    // this block's pages: logical pages [page0, page_end) of the request, one coalesced read
+    const int page0 = lo_blk >> page_shift, page_end = ((hi - 1) >> page_shift) + 1;
+    for (int i = threadIdx.x; i < page_end - page0; i += NTHREADS) s_pages[i] = bt[page0 + i];
+    __syncthreads();
 
-    load_kv_tile<HD>(sK0, sV0, kc, vc, bt, kvh, KV, page_size, t_begin * BN, lo_blk, hi);
+    load_kv_tile<HD>(sK0, sV0, kc, vc, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
     cp_async_commit();
 
     int pos[2], lo[2];
@@ -243,7 +255,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         cp_async_wait<0>();
         __syncthreads();                       // tile t (and Q) visible; everyone is done with tile t-1
         if (t + 1 < t_end) {
-            load_kv_tile<HD>(sK0 + (buf ^ 1) * BN * LD, sV0 + (buf ^ 1) * BN * LD, kc, vc, bt, kvh, KV, page_size,
+            load_kv_tile<HD>(sK0 + (buf ^ 1) * BN * LD, sV0 + (buf ^ 1) * BN * LD, kc, vc, s_pages, page0, kvh, KV, page_shift,
                              (t + 1) * BN, lo_blk, hi);
             cp_async_commit();
         }
@@ -298,15 +310,18 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
-                       int H, int KV, int page_size, int window, float scale_log2) {
+                       int H, int KV, int page_shift, int window, float scale_log2) {
     constexpr int LD = HD + 8;
     pdl_launch_dependents();
-    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
     __nv_bfloat16* sK0 = sQ + 16 * LD;                                          // DEC_STAGES x BN x LD
     __nv_bfloat16* sV0 = sK0 + DEC_STAGES * BN * LD;
+    int* s_pages = reinterpret_cast<int*>(sV0 + DEC_STAGES * BN * LD);  // this block's pages
 
+    // Positions and block tables were put on the device before this step's kernels began, and
+    // every key but the newest was written by earlier steps: all of that may be read before the
+    // wait, while the kernel in front (which writes the newest key and this step's q) still runs.
     const int G = H / KV;
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const int p = positions[seq];                 // one row per request: row index == request index
@@ -319,19 +334,42 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     const int per = (n_tiles + splits - 1) / splits;
     const int t_begin = t_first + split * per;
     const int t_end = min(t_first + n_tiles, t_begin + per);
+    // this block's pages: those of its tiles, one coalesced read of the block table
+    const int page0 = (t_begin * BN) >> page_shift;
+    const int page_end = t_begin < t_end ? ((min(hi, t_end * BN) - 1) >> page_shift) + 1 : page0;
+    for (int i = threadIdx.x; i < page_end - page0; i += NTHREADS) s_pages[i] = bt[page0 + i];
+    __syncthreads();
 
-    for (int c = threadIdx.x; c < 16 * (HD / 8); c += NTHREADS) {
-        int r = c / (HD / 8), ch = c - r * (HD / 8);
-        __nv_bfloat16* dst = sQ + r * LD + ch * 8;
-        if (r < G && p >= 0) cp_async16(dst, q + (size_t)seq * q_stride + (size_t)(kvh * G + r) * HD + ch * 8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-    }
-    // prologue: the first DEC_STAGES - 1 tiles, one commit group each (empty groups keep the count)
+    // prologue: the first DEC_STAGES - 1 tiles, one commit group each (empty groups keep the
+    // count); tiles that end before the newest key go out before the wait, the rest after it
+    int s_done = 0;
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
-        if (t_begin + s < t_end)
-            load_kv_tile<HD>(sK0 + s * BN * LD, sV0 + s * BN * LD, kc, vc, bt, kvh, KV, page_size, (t_begin + s) * BN, lo_key, hi);
-        cp_async_commit();
+        int t = t_begin + s;
+        if (s_done == s && (t >= t_end || (t + 1) * BN <= p)) {
+            if (t < t_end)
+                load_kv_tile<HD>(sK0 + s * BN * LD, sV0 + s * BN * LD, kc, vc, s_pages, page0, kvh, KV, page_shift, t * BN, lo_key, hi);
+            cp_async_commit();
+            s_done = s + 1;
+        }
+    }
+    pdl_wait();
+    // q of this step: plain loads (it must be in shared memory before the first tile is used, and
+    // it is too small to deserve a commit group of its own)
+    for (int c = threadIdx.x; c < 16 * (HD / 8); c += NTHREADS) {
+        int r = c / (HD / 8), ch = c - r * (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < G && p >= 0) v = *reinterpret_cast<const uint4*>(q + (size_t)seq * q_stride + (size_t)(kvh * G + r) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(sQ + r * LD + ch * 8) = v;
+    }
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (s >= s_done) {
+            int t = t_begin + s;
+            if (t < t_end)
+                load_kv_tile<HD>(sK0 + s * BN * LD, sV0 + s * BN * LD, kc, vc, s_pages, page0, kvh, KV, page_shift, t * BN, lo_key, hi);
+            cp_async_commit();
+        }
     }
 
     int pos[2], lo[2];
@@ -359,7 +397,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             int tn = t + DEC_STAGES - 1;        // refill the buffer tile t-1 used
             int nb = (tn - t_begin) % DEC_STAGES;
             if (tn < t_end)
-                load_kv_tile<HD>(sK0 + nb * BN * LD, sV0 + nb * BN * LD, kc, vc, bt, kvh, KV, page_size, tn * BN, lo_key, hi);
+                load_kv_tile<HD>(sK0 + nb * BN * LD, sV0 + nb * BN * LD, kc, vc, s_pages, page0, kvh, KV, page_shift, tn * BN, lo_key, hi);
             cp_async_commit();
         }
         if (t == t_begin) {
@@ -458,40 +496,55 @@ template <int HD, int DEC_STAGES> constexpr size_t decode_smem() {
     return ring > combine ? ring : combine;
 }
 
+inline int log2_exact(int v) {
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
+
+// Raise a kernel's dynamic shared-memory limit when a launch needs more than any before it.
+template <typename Kern>
+int ensure_smem(Kern kernel, size_t bytes, size_t* configured) {
+    if (bytes > 227 * 1024) return VOB_ERR_UNSUPPORTED;
+    if (bytes > *configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return (int)e;
+        *configured = bytes;
+    }
+    return 0;
+}
+
 template <int HD>
 int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                    const int* bt, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new,
                    int H, int KV, int page_size, int window, float scale, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)prefill_smem<HD>());
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static size_t configured = 0;
+    size_t smem = prefill_smem<HD>() + (size_t)max_pages * sizeof(int);      // tiles + this request's page list
+    int e = ensure_smem(attn_prefill_mma_kernel<HD>, smem, &configured);
+    if (e) return e;
     int G = H / KV;
     dim3 grid(((long long)max_new * G + 63) / 64, S, KV);
-    return vob_launch(attn_prefill_mma_kernel<HD>, grid, dim3(NTHREADS), prefill_smem<HD>(), stream,
+    return vob_launch(attn_prefill_mma_kernel<HD>, grid, dim3(NTHREADS), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
-        (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, page_size, window,
+        (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size), window,
         scale * 1.4426950408889634f);
 }
 
 template <int HD, int ST>
 int launch_decode_st(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
-                  const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                  float scale, int splits, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)decode_smem<HD, ST>());
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+                     const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
+                     float scale, int splits, cudaStream_t stream) {
+    static size_t configured = 0;
+    // a block's page list: its share of the tiles of the longest request the block table can hold
+    long long tiles_max = ((long long)max_pages * page_size + BN - 1) / BN;
+    long long pages_cta = ((tiles_max + splits - 1) / splits) * (BN / page_size) + 1;
+    size_t smem = decode_smem<HD, ST>() + (size_t)pages_cta * sizeof(int);
+    int e = ensure_smem(attn_decode_mma_kernel<HD, ST>, smem, &configured);
+    if (e) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, KV, splits);
     cfg.blockDim = dim3(NTHREADS);
-    cfg.dynamicSmemBytes = decode_smem<HD, ST>();
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -502,10 +555,10 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
-                                       out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
-                                       H, KV, page_size, window, scale * 1.4426950408889634f);
-    return e != cudaSuccess ? (int)e : vob_launch_status();
+    cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
+                                        out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
+                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f);
+    return ce != cudaSuccess ? (int)ce : vob_launch_status();
 }
 
 template <int HD>
@@ -521,7 +574,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     }
     // three stages while every block of the grid can be resident at once with them; else two
     long long blocks = (long long)S * KV * splits;
-    long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>() + 1024));
+    long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>() + 2048));
     if (blocks <= fit3)
         return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
                                        window, scale, splits, stream);

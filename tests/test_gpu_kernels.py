@@ -232,17 +232,17 @@ def test_paged_attention_refuses_bad_sizes():
 
 
 @pytest.mark.parametrize("dt", DT, ids=IDS)
-@pytest.mark.parametrize("H,KV,hd,page", [(6, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (32, 8, 64, 16)])
-def test_rope_kv_write(dt, H, KV, hd, page):
+@pytest.mark.parametrize("T", [11, 70])
+@pytest.mark.parametrize("H,KV,hd,page", [(6, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (32, 8, 64, 16), (2, 1, 256, 16)])
+def test_rope_kv_write(dt, H, KV, hd, page, T):
     g = torch.Generator().manual_seed(hd)
-    T = 11
     cfg = {"head_dim": hd, "hidden_size": H * hd, "num_attention_heads": H, "rope_theta": 500000.0,
            "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                             "original_max_position_embeddings": 64}}
     inv = plain.rope_inv_freq(cfg)
     qkv = torch.randn(T, (H + 2 * KV) * hd, generator=g).to(dt)
-    positions = [0, 1, 2, 63, 64, 65, 1000, 4095, 7, 7, 300]
-    pages = 9
+    positions = ([0, 1, 2, 63, 64, 65, 1000, 4095, 7, 7, 300] + list(range(100, 100 + T)))[:T]
+    pages = -(-T // page) + 9
     slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
     slots[4] = -1                                                       # this token writes nothing
     kc = torch.full((pages, KV, page, hd), 7.0).to(dt)

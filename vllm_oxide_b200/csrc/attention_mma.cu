@@ -47,6 +47,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit (two units in the last place: far inside what a bfloat16
+// probability needs); -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -121,8 +128,9 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&
 }
 
 // Mask, running maximum, exponentials; returns P as A-fragments. s holds NB n-blocks of 8 keys
-// starting at key index key0; this thread's rows are r and r+8 with limits [lo, pos].
-template <int NB, int HDN>
+// starting at key index key0; this thread's rows are r and r+8 with limits [lo, pos]. With MASK
+// false the caller knows that every key of the tile is visible to every row of the warp.
+template <int NB, int HDN, bool MASK>
 __device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[NB / 2][4], float (&o)[HDN][4],
                                              float (&m)[2], float (&l)[2], int key0, const int (&lo)[2],
                                              const int (&pos)[2], float scale_log2) {
@@ -132,12 +140,12 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[N
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            int j = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
             int h = i >> 1;
-            bool ok = j >= lo[h] && j <= pos[h];
-            float v = ok ? s[nb][i] * scale_log2 : -INFINITY;
-            s[nb][i] = v;
-            mx[h] = fmaxf(mx[h], v);
+            if (MASK) {
+                int j = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
+                if (!(j >= lo[h] && j <= pos[h])) s[nb][i] = -INFINITY;
+            }
+            mx[h] = fmaxf(mx[h], s[nb][i]);
         }
     }
     float alpha[2], msafe[2];
@@ -145,9 +153,9 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[N
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        float mn = fmaxf(m[h], mx[h]);
+        float mn = fmaxf(m[h], mx[h] * scale_log2);   // scale > 0: the maximum of the scaled scores
         msafe[h] = mn == -INFINITY ? 0.f : mn;
-        alpha[h] = exp2f(m[h] - msafe[h]);            // m = -inf: 0
+        alpha[h] = fast_exp2(m[h] - msafe[h]);         // m = -inf: 0
         m[h] = mn;
         l[h] *= alpha[h];
     }
@@ -155,7 +163,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[N
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            float p = exp2f(s[nb][i] - msafe[i >> 1]);
+            float p = fast_exp2(fmaf(s[nb][i], scale_log2, -msafe[i >> 1]));
             s[nb][i] = p;
             l[i >> 1] += p;                           // this thread's share; the quad is summed at the end
         }
@@ -201,7 +209,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     const int row0 = seq_starts[seq];
     const int n_new = seq_starts[seq + 1] - row0;
     const int total_rows = n_new * G;
-    const int tile_row0 = blockIdx.x * BM;
+    // later row tiles see more keys: hand them out first, so that the long blocks do not all
+    // start last and leave the SMs idle behind them
+    const int tile_row0 = (gridDim.x - 1 - blockIdx.x) * BM;
     if (tile_row0 >= total_rows) return;
     const int ctx = context_lens[seq];
     const int* bt = block_tables + (size_t)seq * max_pages;
@@ -240,6 +250,15 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         pos[h] = rr < total_rows ? ctx + rr / G : -1;
         lo[h] = window > 0 ? max(0, pos[h] + 1 - window) : 0;
     }
+    // the warp's position range: tiles beyond its last position are skipped, tiles wholly inside
+    // every row's [lo, pos] need no mask (rows beyond the request count as position -1: masked)
+    int warp_last_pos = max(pos[0], pos[1]), warp_first_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
+#pragma unroll
+    for (int x = 4; x < 32; x <<= 1) {
+        warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
+        warp_first_pos = min(warp_first_pos, __shfl_xor_sync(0xffffffffu, warp_first_pos, x));
+        warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, x));
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HD / 8][4];
 #pragma unroll
@@ -265,14 +284,15 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
                 ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
         }
         // a warp whose rows all lie before this tile's first key has nothing to do here
-        int warp_last_pos = max(pos[0], pos[1]);
-#pragma unroll
-        for (int x = 4; x < 32; x <<= 1) warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
         if (t * BN <= warp_last_pos) {
             float s[8][4];
             qk_tile<HD, 8>(s, qf, sK, 0);
             uint32_t pa[4][4];
-            softmax_step<8, HD / 8>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+            // no masking where the whole tile lies inside [lo, pos] of every row of the warp
+            if ((t + 1) * BN - 1 <= warp_first_pos && t * BN >= warp_max_lo)
+                softmax_step<8, HD / 8, false>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+            else
+                softmax_step<8, HD / 8, true>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
             pv_tile<HD, 4>(o, pa, sV, 0);
         }
     }
@@ -408,7 +428,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         float s[2][4];
         qk_tile<HD, 2>(s, qf, sK, warp * 2);                    // this warp's 16 keys of the tile
         uint32_t pa[1][4];
-        softmax_step<2, HD / 8>(s, pa, o, m, l, t * BN + warp * 16, lo, pos, scale_log2);
+        softmax_step<2, HD / 8, true>(s, pa, o, m, l, t * BN + warp * 16, lo, pos, scale_log2);
         pv_tile<HD, 1>(o, pa, sV, warp);
     }
     cp_async_wait<0>();

@@ -286,6 +286,62 @@ rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, l
     }
 }
 
+// The same for many tokens: one block per token, thread (pair i, head group): the sine and cosine
+// of the pair's angle are taken once and reused for every head the thread walks over, instead
+// of once per (head, pair).
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kv_write_token_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+                           const T* __restrict__ v, long long v_stride, const int* __restrict__ positions,
+                           const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
+                           T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int groups = blockDim.x / half;          // head groups that work side by side
+    const int i = threadIdx.x % half, hg = threadIdx.x / half;
+    if (hg >= groups) return;
+    float c = 1.f, s = 0.f;
+    if (inv_freq) {
+        float theta = (float)positions[t] * inv_freq[i];
+        c = cosf(theta);
+        s = sinf(theta);
+    }
+    if (inv_freq) {
+        T* qr = q + (size_t)t * q_stride;
+        for (int head = hg; head < H; head += groups) {
+            T* x = qr + (size_t)head * hd;
+            float a = ld_f(x + i), b = ld_f(x + half + i);
+            st_f(x + i, a * c - b * s);
+            st_f(x + half + i, b * c + a * s);
+        }
+    }
+    if (!k) return;
+    const int slot = slots ? slots[t] : -1;
+    const size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0;
+    const int off = slot >= 0 ? slot % page_size : 0;
+    for (int kh = hg; kh < KV; kh += groups) {
+        T* x = k + (size_t)t * k_stride + (size_t)kh * hd;
+        float a = ld_f(x + i), b = ld_f(x + half + i);
+        float ra = a, rb = b;
+        if (inv_freq) {
+            ra = a * c - b * s;
+            rb = b * c + a * s;
+            st_f(x + i, ra);
+            st_f(x + half + i, rb);
+        }
+        if (slot >= 0) {
+            size_t base = ((page * KV + kh) * page_size + off) * (size_t)hd;
+            const T* vr = v + (size_t)t * v_stride + (size_t)kh * hd;
+            st_f(kcache + base + i, ra);
+            st_f(kcache + base + half + i, rb);
+            vcache[base + i] = vr[i];
+            vcache[base + half + i] = vr[half + i];
+        }
+    }
+}
+
 VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long k_stride, const void* v,
                                  long long v_stride, const int* positions, const int* slots,
                                  const float* inv_freq, void* kcache, void* vcache, int code, int T, int H,
@@ -293,6 +349,12 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
     if (T <= 0) return 0;
     if (hd <= 0 || (hd & 1) || H <= 0 || KV < 0 || page_size <= 0) return VOB_ERR_BAD_ARG;
     if (k && slots && (!kcache || !vcache || !v)) return VOB_ERR_BAD_ARG;
+    if (T >= 64 && hd / 2 <= 128) {
+        // many tokens: a block per token, sines and cosines shared across heads
+        VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_token_kernel<ElemT>, dim3(T), dim3(128), 0, stream,
+            (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
+            (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
+    }
     int pairs = (H + (k ? KV : 0)) * (hd / 2);
     dim3 grid(T, (pairs + 127) / 128);
     if (grid.y > 65535) return VOB_ERR_UNSUPPORTED;

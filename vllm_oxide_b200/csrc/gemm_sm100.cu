@@ -568,8 +568,8 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
                ? launch<BT, ST, float>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)      \
                : launch<BT, ST, __nv_bfloat16>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)
     switch (bt) {
-        case 16: GO(16, 4);
-        case 32: GO(32, 4);
+        case 16: GO(16, 6);
+        case 32: GO(32, 6);
         case 64: GO(64, 4);
         default: break;
     }

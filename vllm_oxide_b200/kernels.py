@@ -509,6 +509,8 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
     seq_starts int32 [S+1] (first row of each request), context_lens int32 [S] (keys cached before
     the step), max_new = the longest portion."""
     op = "attn_prefill_mma"
+    if not scale > 0:
+        raise ShapeError(op, f"the score scale must be positive, got {scale}")
     _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
     _cuda(op, seq_starts, context_lens)
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
@@ -529,6 +531,8 @@ def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: 
     With splits > 1 (at most 8) each request's keys are shared out over the blocks of a cluster,
     which merge their partial results through distributed shared memory."""
     op = "attn_decode_mma"
+    if not scale > 0:
+        raise ShapeError(op, f"the score scale must be positive, got {scale}")
     _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
     _cuda(op, positions)
     S = q.shape[0]

@@ -88,7 +88,7 @@ class Attention(Mixer):
         general kernel."""
         page = cache.k.shape[2]
         bt = ctx.block_tables[cache.group]
-        if self.dtype == torch.bfloat16 and self.impl != "general":
+        if self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0:
             if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
                 kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd,
                                         self.scale, self.window, self.decode_splits(ctx.rows))

@@ -52,7 +52,7 @@ paged_attention_warp_kernel(const T* __restrict__ q, long long q_stride, T* __re
                             const int* __restrict__ row_seq, const int* __restrict__ positions,
                             int T_rows, int H, int KV, int hd, int page_size, int window, float scale) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(6);
     extern __shared__ float qs_all[];
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long w = (long long)blockIdx.x * 4 + warp;

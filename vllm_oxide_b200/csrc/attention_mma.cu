@@ -197,7 +197,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     constexpr int LD = HD + 8;
     constexpr int BM = 64;
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(7);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK0 = sQ + BM * LD;
@@ -373,7 +373,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             s_done = s + 1;
         }
     }
-    pdl_wait();
+    pdl_wait(8);
     // q of this step: plain loads (it must be in shared memory before the first tile is used, and
     // it is too small to deserve a commit group of its own)
     for (int c = threadIdx.x; c < 16 * (HD / 8); c += NTHREADS) {

@@ -27,6 +27,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # No fast-math flag: division, sqrt, exp, sin and cos keep nvcc's precise defaults.
 _NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
                "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
+if os.environ.get("VOB_TIMELINE") == "1":      # per-kernel timeline recording (see common.cuh); a different build
+    _NVCC_FLAGS = _NVCC_FLAGS + ["-DVOB_TIMELINE"]
 _CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
 CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "attention_mma", "sampling", "gemm_sm100")

@@ -31,8 +31,32 @@ static inline int vob_launch_status() {
 // does between the two (barrier set-up, tensor-memory allocation, prefetch of weights, which no
 // kernel writes) overlaps the tail of its predecessors. Launches carry the attribute only while
 // the switch below is on; without it both instructions do nothing.
+// Optional timeline of a step (a debugging aid, compiled in only with -DVOB_TIMELINE, i.e. when the
+// libraries are built with VOB_TIMELINE=1 in the environment, and off unless a buffer is set): block 0 of every
+// kernel notes the global timer when it starts and when its wait returns; the wait of kernel n+1
+// returns when kernel n has completed, so consecutive entries give each kernel's place in time.
+// Layout: tl[0] = next free entry; entry e = {tag, start_ns, ready_ns} at tl[1 + 3e].
+__device__ unsigned long long* g_vob_timeline = nullptr;
+__device__ __forceinline__ unsigned long long vob_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait(int tag = 0) {
+#ifdef VOB_TIMELINE
+    unsigned long long* tl = g_vob_timeline;
+    bool rec = tl && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    unsigned long long t0 = rec ? vob_now_ns() : 0;
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef VOB_TIMELINE
+    if (rec) {
+        unsigned long long e = atomicAdd(tl, 1ull);
+        if (e < 4096) { tl[1 + 3 * e] = (unsigned long long)tag; tl[2 + 3 * e] = t0; tl[3 + 3 * e] = vob_now_ns(); }
+    }
+#endif
+}
 
 static int g_vob_pdl = 0;
 
@@ -52,7 +76,11 @@ static inline int vob_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }
 
-#define VOB_PDL_SWITCH(module) VOB_EXPORT void vob_set_pdl_##module(int on) { g_vob_pdl = on; }
+#define VOB_PDL_SWITCH(module)                                                              \
+    VOB_EXPORT void vob_set_pdl_##module(int on) { g_vob_pdl = on; }                        \
+    VOB_EXPORT int vob_set_timeline_##module(unsigned long long* buf) {                      \
+        return (int)cudaMemcpyToSymbol(g_vob_timeline, &buf, sizeof(buf));                   \
+    }
 
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {

@@ -18,7 +18,7 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int h, int vocab, int* err_flag) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(1);
     int t = blockIdx.x;
     int tok = tokens[t];
     bool ok = tok >= 0 && tok < vocab;
@@ -53,7 +53,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    const float* __restrict__ weight, const int* __restrict__ rows,
                                    TO* __restrict__ out, int h, float eps) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(2);
     extern __shared__ float row[];
     __shared__ float red[32];
     int r = blockIdx.x;
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
                        const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(2);
     __shared__ float red[32];
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
@@ -206,7 +206,7 @@ VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, 
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ resid, const TD* __restrict__ delta, size_t n) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(3);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += ld_f(delta + i);
 }
@@ -241,7 +241,7 @@ rope_kv_write_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, l
                      T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
     // one thread per (head, pair i): heads 0..H-1 are q heads, H..H+KV-1 are k heads (with their v)
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(4);
     int t = blockIdx.x;
     int half = hd >> 1;
     int e = blockIdx.y * blockDim.x + threadIdx.x;
@@ -296,7 +296,7 @@ rope_kv_write_token_kernel(T* __restrict__ q, long long q_stride, T* __restrict_
                            const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
                            T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(4);
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int groups = blockDim.x / half;          // head groups that work side by side
@@ -373,7 +373,7 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(5);
     int j = blockIdx.y * blockDim.x + threadIdx.x;
     if (j >= I) return;
     const T* r = in + (size_t)blockIdx.x * in_stride;
@@ -385,7 +385,7 @@ __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* 
 template <typename T, int N>
 __global__ void swiglu_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(5);
     int j = (blockIdx.y * blockDim.x + threadIdx.x) * N;
     if (j >= I) return;
     const T* r = in + (size_t)blockIdx.x * in_stride;

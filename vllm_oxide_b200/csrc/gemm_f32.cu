@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
                 float* __restrict__ C, long long ldc, int M, int N, int K) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(11);
     __shared__ float As[TK][TM + 4];
     __shared__ float Ws[TK][TN + 4];
     int tid = threadIdx.x;

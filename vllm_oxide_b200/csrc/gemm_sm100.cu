@@ -167,7 +167,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 mbar_expect_tx(full_bar + i, stage_bytes<BT>());
                 tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + i);
             }
-            pdl_wait();
+            pdl_wait(12);
             for (int i = 0; i < pre; ++i) {
                 unsigned char* b = tiles + i * stage_bytes<BT>() + BM * BK * 2;
                 tma_load_2d(b, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + i);
@@ -328,7 +328,7 @@ gemm_sm100_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_holder;
-    pdl_wait();
+    pdl_wait(13);
 
     if (warp == 0) {
         if (lane == 0) {

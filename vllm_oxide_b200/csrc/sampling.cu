@@ -58,7 +58,7 @@ pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const
                     const uint32_t* __restrict__ seeds, const int* __restrict__ steps, int splits,
                     float* __restrict__ part_val, int* __restrict__ part_idx, int* __restrict__ nan_flags) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(9);
     __shared__ Best sh[32];
     int r = blockIdx.y, sp = blockIdx.x;
     int per = (V + splits - 1) / splits;
@@ -94,7 +94,7 @@ pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const
 __global__ void pick_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                   int splits, int V, int* __restrict__ nan_flags, int* __restrict__ out) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait(10);
     __shared__ Best sh[32];
     int r = blockIdx.x;
     Best b{-INFINITY, 0x7fffffff};

@@ -200,6 +200,35 @@ def set_pdl(on: bool) -> None:
             f(1 if _pdl_on else 0)
 
 
+KERNEL_TAGS = {1: "embed", 2: "add_rmsnorm", 3: "add_residual", 4: "rope_kv_write", 5: "swiglu", 6: "paged_attention",
+               7: "attn_prefill_mma", 8: "attn_decode_mma", 9: "pick_partial", 10: "pick_final", 11: "gemm_f32",
+               12: "gemm_sm100", 13: "gemm_sm100_persistent"}
+
+
+def set_timeline(buf: Optional[torch.Tensor]) -> None:
+    """A debugging aid (needs libraries built with VOB_TIMELINE=1 in the environment; otherwise
+    nothing is recorded): with a zeroed int64 CUDA tensor of 1 + 3 * 4096 elements, block 0 of every
+    kernel launched afterwards appends (tag, time before its wait, time after its wait) in global
+    nanoseconds; `read_timeline` decodes it. None switches it off."""
+    from .csrc.build import _loaded
+    if buf is not None and (buf.dtype != torch.int64 or not buf.is_cuda or buf.numel() < 1 + 3 * 4096):
+        raise ShapeError("set_timeline", "need an int64 CUDA tensor of 1 + 3 * 4096 elements")
+    for m in _MODULES:
+        if m in _loaded:
+            f = getattr(_loaded[m], f"vob_set_timeline_{m}")
+            f.argtypes = [_P]
+            f.restype = _I
+            _check(f(_ptr(buf)), "set_timeline", launches=0)
+
+
+def read_timeline(buf: torch.Tensor):
+    """[(kernel name, ns before the wait, ns after the wait)] in the order the waits returned."""
+    h = buf.cpu().tolist()
+    n = min(h[0], 4096)
+    rows = [(KERNEL_TAGS.get(h[1 + 3 * e], str(h[1 + 3 * e])), h[2 + 3 * e], h[3 + 3 * e]) for e in range(n)]
+    return sorted(rows, key=lambda r: r[2])
+
+
 # ------------------------------------------------------------------------------------ embedding
 @_timed
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None) -> None:

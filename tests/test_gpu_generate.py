@@ -22,6 +22,28 @@ def sp(**kw):
     return SamplingParams(**kw)
 
 
+def assert_same_or_near_tie(model_dir, prompt, got, want, params, tol):
+    """Two runs of one request must give the same tokens; in bfloat16 a difference is allowed only
+    where it is a matter of rounding: at the first differing token both picks must be within
+    `tol` (relative to the largest logit) of each other in the plain implementation's logits (with
+    temperature sampling: in logit / temperature + noise). After such a near-tie the sequences
+    differ legitimately and are not compared further."""
+    if got == want:
+        return
+    assert tol > 0, f"tokens differ: {got} vs {want}"
+    i = next(k for k in range(min(len(got), len(want))) if got[k] != want[k])
+    pc, pt = plain.load_model(model_dir)
+    logits = plain.forward(pc, pt, list(prompt) + list(want[:i]))[-1]
+    scale = float(logits.abs().max())
+    if params.temperature > 0:
+        import numpy as np
+        score = lambda t: float(logits[t]) / params.temperature + plain.gumbel_noise(params.seed, i, t)
+        gap, scale = abs(score(got[i]) - score(want[i])), scale / params.temperature
+    else:
+        gap = abs(float(logits[got[i]]) - float(logits[want[i]]))
+    assert gap <= tol * scale, f"token {i}: {got[i]} vs {want[i]} differ by {gap:.3e} of {scale:.3e}: more than rounding"
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_equals_plain_in_f32(tmp_path_factory, name):
     cfg, _, page = TINY[name]
@@ -90,7 +112,10 @@ def test_batched_equals_alone_and_graphs_change_nothing(tmp_path_factory, dtype,
     for graphs in (False, True):
         llm = llm_for(d, dtype, page, cuda_graphs=graphs, prefill_chunk=16, max_batch_tokens=40)
         outs = llm.generate(prompts, params)
-        assert [o.token_ids for o in outs] == alone, f"graphs={graphs}"
+        # float32: exact. bfloat16: steps of different sizes use different kernels (and so round
+        # differently), so a pick may differ where the oracle's logits are tied within the tolerance.
+        for p, prm, o, a in zip(prompts, params, outs, alone):
+            assert_same_or_near_tie(d, p, o.token_ids, a, prm, 0.0 if dtype == "float32" else TOL[torch.bfloat16])
         assert all(o.finish_reason == "length" for o in outs)
         assert llm.stats["graph_steps"] > 0 if graphs else llm.stats["graph_steps"] == 0
         assert llm.runner.manager.check_invariants() == ""

@@ -447,3 +447,76 @@ def test_gemm_sm100_strided_and_refusals():
     o = torch.empty(9, 50, dtype=torch.bfloat16, device=DEV)
     k.linear(wide[:, :60].contiguous(), w[:, :60].contiguous(), o)
     assert rel(o, plain.linear(wide[:, :60].double().cpu(), w[:, :60].double().cpu())) <= 2 ** -8
+
+
+# ----------------------------------------------------------------------------- fused epilogues of the tcgen05 product
+@pytest.mark.parametrize("T,I,Kd,splits", [(1, 128, 64, 1), (8, 8192, 2048, None), (5, 224, 96, 1), (16, 300, 520, 3), (32, 1000, 256, 2), (17, 128, 1024, 8)])
+def test_gemm_swiglu(T, I, Kd, splits):
+    g = torch.Generator().manual_seed(T + I)
+    a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, Kd, generator=g) / math.sqrt(Kd) * 2).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    k = K()
+    k.gemm_swiglu(a, w, out, splits)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    gate = plain.linear(a.double().cpu(), w[:I].double().cpu())
+    up = plain.linear(a.double().cpu(), w[I:].double().cpu())
+    assert rel(out, plain.swiglu(gate, up)) <= 2 ** -8
+    out2 = torch.zeros_like(out)
+    k.gemm_swiglu(a, w, out2, splits)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("rope", [True, False])
+@pytest.mark.parametrize("T,H,KV,hd,Kd,page,splits", [(8, 32, 8, 64, 2048, 16, None), (1, 4, 2, 64, 128, 16, 1), (13, 3, 1, 32, 96, 8, 1),
+                                                      (32, 6, 2, 16, 200, 8, 2), (5, 2, 2, 128, 512, 32, 4), (20, 5, 5, 64, 320, 16, 5)])
+def test_gemm_qkv_rope(T, H, KV, hd, Kd, page, splits, rope):
+    g = torch.Generator().manual_seed(T + H + hd)
+    a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((H + 2 * KV) * hd, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
+    cfg = {"head_dim": hd, "hidden_size": H * hd, "num_attention_heads": H, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 64}}
+    inv = plain.rope_inv_freq(cfg)
+    positions = [(37 * i + 5) % 3000 for i in range(T)]
+    pages = -(-T // page) + 4
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    if T > 2:
+        slots[2] = -1                                                   # this token writes nothing
+    kc = torch.full((pages, KV, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((pages, KV, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    q = torch.full((T, H * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    k = K()
+    k.gemm_qkv_rope(a, w, q, torch.tensor(positions, dtype=torch.int32, device=DEV), slots.to(DEV),
+                    inv.to(DEV) if rope else None, kc, vc, H, KV, hd, splits)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    qkv = plain.linear(a.double().cpu(), w.double().cpu())
+    wq, wk, wv = qkv[:, :H * hd], qkv[:, H * hd:(H + KV) * hd], qkv[:, (H + KV) * hd:]
+    if rope:
+        wq, wk = plain.rope(wq, positions, inv, hd), plain.rope(wk, positions, inv, hd)
+    assert rel(q, wq) <= 2 ** -8
+    written = set()
+    for t in range(T):
+        s_ = int(slots[t])
+        if s_ < 0:
+            continue
+        written.add(s_)
+        pg, off = s_ // page, s_ % page
+        assert rel(kc[pg, :, off, :].reshape(-1), wk[t]) <= 2 ** -8
+        assert rel(vc[pg, :, off, :].reshape(-1), wv[t]) <= 2 ** -8
+    for s_ in range(pages * page):
+        if s_ not in written:
+            assert float((kc[s_ // page, :, s_ % page, :].float() - 7.0).abs().max()) == 0.0
+            assert float((vc[s_ // page, :, s_ % page, :].float() - 7.0).abs().max()) == 0.0
+
+
+def test_fused_gemm_refusals():
+    from vllm_oxide_b200.errors import ShapeError
+    k = K()
+    a = torch.zeros(40, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ShapeError, match="at most 32"):
+        k.gemm_swiglu(a, w, torch.zeros(40, 128, dtype=torch.bfloat16, device=DEV))
+    assert not k.gemm_qkv_rope_supported(48) and k.gemm_qkv_rope_supported(64)

@@ -118,22 +118,95 @@ template <typename OutT> __device__ __forceinline__ void store_out(OutT* p, floa
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <int BT> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
-template <int BT> __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
+// What the epilogue does with a finished element (token t, output feature f):
+//   EPI_STORE   C[t, f] = value
+//   EPI_SWIGLU  the block's 128 weight rows are 64 rows of the "gate" half and the same 64 rows of
+//               the "up" half of a [2I, K] weight matrix (two TMA boxes into one operand tile):
+//               C[t, f] = gate / (1 + exp(-gate)) * up (crates/engine/src/backend/cpu/mod.rs:341-349),
+//               so the SwiGLU input never exists in memory
+//   EPI_QKV     the weight matrix is [Wq; Wk; Wv]: q and k features are rotated by the rotary rule
+//               (crates/engine/src/backend/cpu/rope.rs:87-99; angle float(pos) * inv_freq, precise
+//               sinf/cosf), q goes to C, rotated k and v go straight to their cache slots
+//               (crates/engine/src/backend/cpu/mod.rs:257-285): no separate rotary / cache-write pass
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
 
-template <int BT, int STAGES, typename OutT>
+struct QkvArgs {                       // EPI_QKV only
+    const int* positions;              // [T]
+    const int* slots;                  // [T] cache slot of each token, -1: none
+    const float* inv_freq;             // [hd / 2] or null (no rotation)
+    __nv_bfloat16* kcache;             // [pages, KV, page_size, hd]
+    __nv_bfloat16* vcache;
+    int q_dim, kv_dim, hd, KV, page_size;
+};
+
+template <int BT, int EPI> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
+template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage_bytes<BT, EPI_STORE>(); }
+template <int BT, int EPI> __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
+template <int BT> __host__ __device__ constexpr int tmem_cols() { return tmem_cols<BT, EPI_STORE>(); }
+
+// One finished element of column `col` of the block's tile; `row` points at the 128 finished
+// values of the same token in shared memory (partners of a rotation, the "up" half of SwiGLU).
+// With `pre` the rotation's cosine, sine and the cache slot were worked out ahead of time.
+template <int EPI, typename OutT>
+__device__ __forceinline__ void finish_element(OutT* __restrict__ C, long long ldc, int t, int f, int col, float v,
+                                               const float* row, int m_tile, int N, const QkvArgs& qa, bool pre, float pc,
+                                               float ps, int pslot) {
+    if (EPI == EPI_STORE) {
+        if (f < N) store_out<OutT>(C + (size_t)t * ldc + f, v);
+    } else if (EPI == EPI_SWIGLU) {
+        // columns 0..63: gate of feature m_tile * 64 + col; columns 64..127: up of the same features
+        const int fo = m_tile * (BM / 2) + col;
+        if (col < BM / 2 && fo < N) store_out<OutT>(C + (size_t)t * ldc + fo, v / (1.0f + expf(-v)) * row[col + BM / 2]);
+    } else {
+        if (f >= N) return;
+        const int hd = qa.hd, half = hd >> 1;
+        const bool is_q = f < qa.q_dim, is_k = !is_q && f < qa.q_dim + qa.kv_dim;
+        float outv = v;
+        if ((is_q || is_k) && qa.inv_freq) {
+            const int i = f % hd;
+            const float partner = row[i < half ? col + half : col - half];
+            float c = pc, s = ps;
+            if (!pre) {
+                const float theta = (float)qa.positions[t] * qa.inv_freq[i < half ? i : i - half];
+                c = cosf(theta);
+                s = sinf(theta);
+            }
+            outv = i < half ? v * c - partner * s : v * c + partner * s;
+        }
+        if (is_q) {
+            store_out<OutT>(C + (size_t)t * ldc + f, outv);
+        } else {
+            const int slot = pre ? pslot : (qa.slots ? qa.slots[t] : -1);
+            if (slot >= 0) {
+                const int g = is_k ? f - qa.q_dim : f - qa.q_dim - qa.kv_dim;
+                const int kh = g / hd, d = g - kh * hd;
+                const size_t page = (size_t)(slot / qa.page_size);
+                const int off = slot % qa.page_size;
+                const size_t idx = ((page * qa.KV + kh) * qa.page_size + off) * (size_t)hd + d;
+                (is_k ? qa.kcache : qa.vcache)[idx] = __float2bfloat16_rn(outv);
+            }
+        }
+    }
+}
+
+template <int BT, int STAGES, typename OutT, int EPI>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ C,
-                  long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag) {
+                  long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag, int up_row0,
+                  const QkvArgs qa) {
+    constexpr int SB = stage_bytes<BT, EPI>();
+    constexpr int A_BYTES = BM * BK * 2;
+    constexpr int PRE = 4;                         // tokens per block whose rotation is worked out ahead
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * stage_bytes<BT>());
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * SB);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_bar = empty_bar + STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    float* xch = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);      // 128 floats (EPI_QKV)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -149,7 +222,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(tmem_cols<BT>()) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(tmem_cols<BT, EPI>()) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -163,24 +236,31 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // still runs before this kernel; the activations are loaded only after the wait.
             const int pre = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < pre; ++i) {
-                unsigned char* a = tiles + i * stage_bytes<BT>();
-                mbar_expect_tx(full_bar + i, stage_bytes<BT>());
-                tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + i);
+                unsigned char* a = tiles + i * SB;
+                mbar_expect_tx(full_bar + i, SB);
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * (BM / 2), full_bar + i);
+                    tma_load_2d(a + (BM / 2) * BK * 2, &map_w, (kb0 + i) * BK, up_row0 + m_tile * (BM / 2), full_bar + i);
+                } else {
+                    tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + i);
+                }
             }
             pdl_wait(12);
-            for (int i = 0; i < pre; ++i) {
-                unsigned char* b = tiles + i * stage_bytes<BT>() + BM * BK * 2;
-                tma_load_2d(b, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + i);
-            }
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + i * SB + A_BYTES, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + i);
             for (int i = pre; i < nkb; ++i) {
                 int s = i % STAGES;
                 uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, err_flag, 1)) break;
-                unsigned char* a = tiles + s * stage_bytes<BT>();
-                unsigned char* b = a + BM * BK * 2;
-                mbar_expect_tx(full_bar + s, stage_bytes<BT>());
-                tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + s);
-                tma_load_2d(b, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + s);
+                unsigned char* a = tiles + s * SB;
+                mbar_expect_tx(full_bar + s, SB);
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * (BM / 2), full_bar + s);
+                    tma_load_2d(a + (BM / 2) * BK * 2, &map_w, (kb0 + i) * BK, up_row0 + m_tile * (BM / 2), full_bar + s);
+                } else {
+                    tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * BM, full_bar + s);
+                }
+                tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + s);
             }
         }
     } else if (warp == 1) {
@@ -193,9 +273,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 ok = mbar_wait(full_bar + s, ph, abort_flag, err_flag, 2);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned char* a = tiles + s * stage_bytes<BT>();
+                unsigned char* a = tiles + s * SB;
                 uint64_t adesc = umma_desc_sw128(a);
-                uint64_t bdesc = umma_desc_sw128(a + BM * BK * 2);
+                uint64_t bdesc = umma_desc_sw128(a + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     // 16 K elements = 32 bytes = 2 units of the descriptor's start address
@@ -208,13 +288,36 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     } else {
         // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) ... + 31
         const int quad = warp & 3;
-        const int f = m_tile * BM + quad * 32 + lane;          // this thread's output feature
+        const int col = quad * 32 + lane;
+        const int f = m_tile * BM + col;                       // this thread's output feature
+        const int t0 = n_tile * BT;
+        // Rotary positions: what this thread will need for the tokens its block finishes (cosine,
+        // sine, cache slot) depends only on data that was on the device before the step began, so
+        // it is worked out now, while the weights stream, not after the accumulator is done.
+        float pc[PRE], ps[PRE];
+        int pslot[PRE];
+        if (EPI == EPI_QKV && splits > 1) {
+            const int hd = qa.hd, half = hd >> 1, i = f % hd;
+            const bool rot = qa.inv_freq && f < qa.q_dim + qa.kv_dim;
+            const float inv = rot ? qa.inv_freq[i < half ? i : i - half] : 0.f;
+#pragma unroll
+            for (int k = 0; k < PRE; ++k) {
+                const int j = split + k * splits;
+                pc[k] = 1.f; ps[k] = 0.f; pslot[k] = -1;
+                if (j < BT && t0 + j < T) {
+                    const float theta = (float)qa.positions[t0 + j] * inv;
+                    pc[k] = cosf(theta);
+                    ps[k] = sinf(theta);
+                    pslot[k] = qa.slots ? qa.slots[t0 + j] : -1;
+                }
+            }
+        }
         pdl_wait();
         bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const int t0 = n_tile * BT;
-        if (ok && splits == 1) {
+        float* tile = reinterpret_cast<float*>(tiles);         // [token][128] float32 over the operand stages
+        if (ok && splits == 1 && EPI == EPI_STORE) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 uint32_t r[16];
@@ -222,63 +325,80 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (f < N) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        int t = t0 + c + j;
-                        if (t < T) store_out<OutT>(C + (size_t)t * ldc + f, __uint_as_float(r[j]));
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, __uint_as_float(r[j]));
                 }
             }
         } else if (ok) {
-            // partial tile to this block's shared memory: [token][feature] float32, over the operand
-            // stages (every MMA that read them has completed once acc_bar has flipped)
-            float* mine = reinterpret_cast<float*>(tiles) + quad * 32 + lane;
+            // the tile to this block's shared memory (every MMA that read the operand stages has
+            // completed once acc_bar has flipped): a partial tile for the cluster to add up, or,
+            // without a split, the finished tile in which partners of a fused epilogue find each other
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 16; ++j) mine[(c + j) * BM] = __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = __uint_as_float(r[j]);
+            }
+            if (splits == 1) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int j = 0; j < BT && t0 + j < T; ++j)
+                    finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, tile[j * BM + col], tile + j * BM, m_tile, N, qa, false, 0.f, 0.f, -1);
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    }
-    if (splits > 1) {
-        // every thread of every block of the cluster: partials are written, peers may read them
-        __syncwarp();
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (warp >= 2 && !*abort_flag) {
-            const int quad = warp & 3;
-            const int col = quad * 32 + lane;
-            const int f = m_tile * BM + col;
-            const int t0 = n_tile * BT;
-            const uint32_t local = smem_u32(reinterpret_cast<float*>(tiles) + col);
-            // this block adds up the tokens j with j % splits == its rank
-            for (int j = split; j < BT && t0 + j < T; j += splits) {
-                float part[8];
+        if (splits > 1) {
+            // every thread of every block of the cluster: partials are written, peers may read them
+            __syncwarp();
+            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (!*abort_flag) {
+                const uint32_t local = smem_u32(tile + col);
+                // this block adds up the tokens j with j % splits == its rank
+                int k = 0;
+                for (int j = split; j < BT && t0 + j < T; j += splits, ++k) {
+                    float part[8];
 #pragma unroll
-                for (int p = 0; p < 8; ++p) {
-                    part[p] = 0.f;
-                    if (p < splits) {
-                        uint32_t remote;
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local + (uint32_t)(j * BM * 4)), "r"(p));
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[p]) : "r"(remote) : "memory");
+                    for (int p = 0; p < 8; ++p) {
+                        part[p] = 0.f;
+                        if (p < splits) {
+                            uint32_t remote;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local + (uint32_t)(j * BM * 4)), "r"(p));
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[p]) : "r"(remote) : "memory");
+                        }
+                    }
+                    float acc = 0.f;
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) acc += part[p];       // rank order, zeros beyond the last rank
+                    if (EPI == EPI_STORE) {
+                        if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
+                    } else {
+                        // partners meet in a row of shared memory
+                        xch[col] = acc;
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        const bool pre = EPI == EPI_QKV && k < PRE;
+                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, pre, pre ? pc[k < PRE ? k : 0] : 0.f,
+                                                  pre ? ps[k < PRE ? k : 0] : 0.f, pre ? pslot[k < PRE ? k : 0] : -1);
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
                     }
                 }
-                float acc = 0.f;
-#pragma unroll
-                for (int p = 0; p < 8; ++p) acc += part[p];           // rank order, zeros beyond the last rank
-                if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
             }
+            // nobody leaves (and frees its shared memory) while a peer may still be reading it
+            __syncwarp();
+            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
-        // nobody leaves (and frees its shared memory) while a peer may still be reading it
+    }
+    if (splits > 1 && warp < 2) {
+        // the producer and MMA warps take part in the cluster's two barriers as well
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols<BT>()) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols<BT, EPI>()) : "memory");
     }
 }
 
@@ -463,22 +583,25 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, 
     return 0;
 }
 
-template <int BT, int STAGES> constexpr size_t smem_bytes() { return (size_t)STAGES * stage_bytes<BT>() + 1024 + 256; }
+template <int BT, int STAGES, int EPI = EPI_STORE> constexpr size_t smem_bytes() {
+    return (size_t)STAGES * stage_bytes<BT, EPI>() + 1024 + 1024;       // tiles + alignment slack + barriers and exchange row
+}
 
-template <int BT, int STAGES, typename OutT>
+template <int BT, int STAGES, typename OutT, int EPI>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int splits, int kb_per,
-           int* err_flag, cudaStream_t stream) {
+           int* err_flag, int up_row0, const QkvArgs& qa, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BT, STAGES, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem_bytes<BT, STAGES>());
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BT, STAGES, OutT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem_bytes<BT, STAGES, EPI>());
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + BM - 1) / BM, (T + BT - 1) / BT, splits);
+    constexpr int FEATURES_PER_TILE = EPI == EPI_SWIGLU ? BM / 2 : BM;
+    cfg.gridDim = dim3((N + FEATURES_PER_TILE - 1) / FEATURES_PER_TILE, (T + BT - 1) / BT, splits);
     cfg.blockDim = dim3(NTHREADS);
-    cfg.dynamicSmemBytes = smem_bytes<BT, STAGES>();
+    cfg.dynamicSmemBytes = smem_bytes<BT, STAGES, EPI>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -489,7 +612,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<BT, STAGES, OutT>, mw, mx, (OutT*)C, ldc, T, N, K, kb_per, err_flag);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<BT, STAGES, OutT, EPI>, mw, mx, (OutT*)C, ldc, T, N, K, kb_per, err_flag,
+                                       up_row0, qa);
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }
 
@@ -565,8 +689,8 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
     if (e) return e;
 #define GO(BT, ST)                                                                                                         \
     return out_code == VOB_F32                                                                                             \
-               ? launch<BT, ST, float>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)      \
-               : launch<BT, ST, __nv_bfloat16>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, stream)
+               ? launch<BT, ST, float, EPI_STORE>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, 0, QkvArgs{}, stream)      \
+               : launch<BT, ST, __nv_bfloat16, EPI_STORE>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, 0, QkvArgs{}, stream)
     switch (bt) {
         case 16: GO(16, 6);
         case 32: GO(32, 6);
@@ -580,4 +704,63 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
     if (bt == 128) { GOP(128, 6); }
     GOP(256, 4);
 #undef GOP
+}
+
+
+// ------------------------------------------------------------------------------------------------ fused epilogues (few tokens)
+namespace {
+int fused_common(int T, int K, long long ldx, long long ldw, const void* X, const void* W, int* splits, int* kb_per) {
+    if (T <= 0 || T > 32) return VOB_ERR_UNSUPPORTED;
+    if (K <= 0 || ldx < K || ldw < K) return VOB_ERR_BAD_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0) return VOB_ERR_UNSUPPORTED;
+    int total_kb = (K + BK - 1) / BK;
+    if (*splits < 1) *splits = 1;
+    if (*splits > 8) *splits = 8;
+    if (*splits > total_kb) *splits = total_kb;
+    *kb_per = (total_kb + *splits - 1) / *splits;
+    *splits = (total_kb + *kb_per - 1) / *kb_per;
+    return 0;
+}
+}  // namespace
+
+// C[T, I] = silu(X Wg^T) * (X Wu^T), W = [Wg; Wu] of shape [2I, K]; T <= 32.
+VOB_EXPORT int vob_gemm_sm100_swiglu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int T,
+                                     int I, int K, int splits, int* err_flag, cudaStream_t stream) {
+    int kb_per = 0;
+    int e = fused_common(T, K, ldx, ldw, X, W, &splits, &kb_per);
+    if (e) return e;
+    if (I <= 0 || ldc < I) return VOB_ERR_BAD_ARG;
+    int bt = pick_bt(T);
+    CUtensorMap mw, mx;
+    e = make_map(&mw, W, 2LL * I, K, ldw, BM / 2);            // boxes of 64 rows: half a tile from each half of W
+    if (e) return e;
+    e = make_map(&mx, X, T, K, ldx, bt);
+    if (e) return e;
+    if (bt == 16) return launch<16, 6, __nv_bfloat16, EPI_SWIGLU>(mw, mx, C, ldc, T, I, K, splits, kb_per, err_flag, I, QkvArgs{}, stream);
+    return launch<32, 6, __nv_bfloat16, EPI_SWIGLU>(mw, mx, C, ldc, T, I, K, splits, kb_per, err_flag, I, QkvArgs{}, stream);
+}
+
+// [q | k | v] = X [Wq; Wk; Wv]^T with rotary positions on q and k; q (rotated) -> Q[T, q_dim], rotated k
+// and v -> their cache slots. T <= 32, 128 a multiple of head_dim.
+VOB_EXPORT int vob_gemm_sm100_qkv(const void* X, long long ldx, const void* W, long long ldw, void* Q, long long ldq, int T, int K,
+                                  int splits, int* err_flag, const int* positions, const int* slots, const float* inv_freq,
+                                  void* kcache, void* vcache, int H, int KV, int hd, int page_size, cudaStream_t stream) {
+    int kb_per = 0;
+    int e = fused_common(T, K, ldx, ldw, X, W, &splits, &kb_per);
+    if (e) return e;
+    if (H <= 0 || KV <= 0 || hd <= 0 || (hd & 1) || BM % hd != 0 || page_size <= 0) return VOB_ERR_UNSUPPORTED;
+    if (!positions || !kcache || !vcache || ldq < (long long)H * hd) return VOB_ERR_BAD_ARG;
+    QkvArgs qa;
+    qa.positions = positions; qa.slots = slots; qa.inv_freq = inv_freq;
+    qa.kcache = (__nv_bfloat16*)kcache; qa.vcache = (__nv_bfloat16*)vcache;
+    qa.q_dim = H * hd; qa.kv_dim = KV * hd; qa.hd = hd; qa.KV = KV; qa.page_size = page_size;
+    int N = (H + 2 * KV) * hd;
+    int bt = pick_bt(T);
+    CUtensorMap mw, mx;
+    e = make_map(&mw, W, N, K, ldw, BM);
+    if (e) return e;
+    e = make_map(&mx, X, T, K, ldx, bt);
+    if (e) return e;
+    if (bt == 16) return launch<16, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
+    return launch<32, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
 }

@@ -419,6 +419,81 @@ def gemm_sm100(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Opti
              _ptr(sc.err), _stream()), op)
 
 
+def _pick_splits(T: int, N: int, K: int, device) -> int:
+    f = _fn("gemm_sm100", "vob_gemm_sm100_pick_splits", [_I, _I, _I, _I])
+    return int(f(T, N, K, _scratch_for(device).num_sms))
+
+
+FUSED_GEMM_MAX_ROWS = 32
+
+
+@_timed
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
+    """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16): one tcgen05
+    kernel with two accumulators whose epilogue applies the activation, for at most 32 rows."""
+    op = "gemm_swiglu"
+    _cuda(op, a, w_gate_up, out)
+    if not gemm_sm100_supported(a, w_gate_up):
+        raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    T, K = a.shape
+    if w_gate_up.shape[0] % 2 != 0 or w_gate_up.shape[1] != K:
+        raise ShapeError(op, f"w_gate_up must be [2I, {K}], got {list(w_gate_up.shape)}")
+    I = w_gate_up.shape[0] // 2
+    if T > FUSED_GEMM_MAX_ROWS:
+        raise ShapeError(op, f"{T} rows: the fused kernel takes at most {FUSED_GEMM_MAX_ROWS}")
+    if out.shape != (T, I) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ShapeError(op, f"out must be bfloat16 [{T}, {I}], got {out.dtype} {list(out.shape)}")
+    if splits is None:
+        splits = _pick_splits(T, 2 * I, K, a.device)
+    f = _fn("gemm_sm100", "vob_gemm_sm100_swiglu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w_gate_up), w_gate_up.stride(0), _ptr(out), out.stride(0), T, I, K, int(splits),
+             _ptr(_scratch_for(a.device).err), _stream()), op)
+
+
+def gemm_qkv_rope_supported(head_dim: int) -> bool:
+    return head_dim > 0 and head_dim % 2 == 0 and 128 % head_dim == 0
+
+
+@_timed
+def gemm_qkv_rope(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                  slots: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], kcache: torch.Tensor, vcache: torch.Tensor,
+                  num_heads: int, num_kv_heads: int, head_dim: int, splits: Optional[int] = None) -> None:
+    """[q | k | v] = a @ [Wq; Wk; Wv]^T in one tcgen05 kernel whose epilogue rotates q and k (float32
+    angles position * inv_freq), writes q to q_out [T, H*hd] and the rotated k and v straight to their
+    cache slots. At most 32 rows; 128 must be a multiple of head_dim."""
+    op = "gemm_qkv_rope"
+    _cuda(op, a, w_qkv, q_out, positions, slots, inv_freq, kcache, vcache)
+    if not gemm_sm100_supported(a, w_qkv):
+        raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    T, K = a.shape
+    H, KV, hd = num_heads, num_kv_heads, head_dim
+    if not gemm_qkv_rope_supported(hd):
+        raise ShapeError(op, f"head_dim {hd}: 128 must be a multiple of it")
+    if w_qkv.shape != ((H + 2 * KV) * hd, K):
+        raise ShapeError(op, f"w_qkv must be [{(H + 2 * KV) * hd}, {K}], got {list(w_qkv.shape)}")
+    if T > FUSED_GEMM_MAX_ROWS:
+        raise ShapeError(op, f"{T} rows: the fused kernel takes at most {FUSED_GEMM_MAX_ROWS}")
+    if q_out.shape != (T, H * hd) or q_out.dtype != torch.bfloat16 or q_out.stride(1) != 1:
+        raise ShapeError(op, f"q_out must be bfloat16 [{T}, {H * hd}], got {q_out.dtype} {list(q_out.shape)}")
+    _int32_vec(positions, T, op, "positions")
+    if slots is not None:
+        _int32_vec(slots, T, op, "slots")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape != (hd // 2,) or not inv_freq.is_contiguous()):
+        raise ShapeError(op, f"inv_freq must be float32 [{hd // 2}]")
+    for name, c in (("kcache", kcache), ("vcache", vcache)):
+        if c.dim() != 4 or c.shape[1] != KV or c.shape[3] != hd or not c.is_contiguous() or c.dtype != torch.bfloat16:
+            raise ShapeError(op, f"{name} must be contiguous bfloat16 [pages, {KV}, page_size, {hd}], got {c.dtype} {list(c.shape)}")
+    if kcache.shape != vcache.shape:
+        raise ShapeError(op, "kcache and vcache differ in shape")
+    if splits is None:
+        splits = _pick_splits(T, (H + 2 * KV) * hd, K, a.device)
+    f = _fn("gemm_sm100", "vob_gemm_sm100_qkv",
+            [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w_qkv), w_qkv.stride(0), _ptr(q_out), q_out.stride(0), T, K, int(splits),
+             _ptr(_scratch_for(a.device).err), _ptr(positions), _ptr(slots), _ptr(inv_freq), _ptr(kcache), _ptr(vcache),
+             H, KV, hd, kcache.shape[2], _stream()), op)
+
+
 def gemm_sm100_check() -> None:
     """Raise if a wait inside the tensor-core product ever timed out (reads one word from the device)."""
     for dev, sc in _gemm_scratch.items():

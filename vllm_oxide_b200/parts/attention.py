@@ -52,6 +52,7 @@ class Attention(Mixer):
         self.hidden = hidden
         self.dtype = dtype
         self.impl = "auto"            # "general" forces the general attention kernel (tests)
+        self.fused = True             # False forces the separate projection / rotary / cache-write kernels
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
 
     def cache_spec(self) -> Optional[CacheSpec]:
@@ -69,9 +70,19 @@ class Attention(Mixer):
             raise ValueError("attention needs a cache")
         T = x.shape[0]
         qd, kd = self.H * self.hd, self.KV * self.hd
+        inv_freq = self.position.inv_freq if self.position is not None else None
+        if (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and cache.write
+                and T <= kernels.FUSED_GEMM_MAX_ROWS and kernels.gemm_qkv_rope_supported(self.hd)
+                and kernels.gemm_sm100_supported(x, self.w_qkv)):
+            # few rows: rotary positions and the cache write happen in the projection's epilogue
+            q = ctx.alloc((T, qd))
+            kernels.gemm_qkv_rope(x, self.w_qkv, q, ctx.positions, ctx.slot_mapping[cache.group], inv_freq,
+                                  cache.k, cache.v, self.H, self.KV, self.hd)
+            attn = ctx.alloc((T, qd))
+            self.attend(q, attn, ctx, cache)
+            return matmul(attn, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
         qkv = matmul(x, self.w_qkv, ctx.alloc((T, self.w_qkv.shape[0])))
         q = qkv[:, :qd]
-        inv_freq = self.position.inv_freq if self.position is not None else None
         if self.owns_cache and cache.write:
             k, v = qkv[:, qd:qd + kd], qkv[:, qd + kd:]
             kernels.rope_kv_write(q, k, v, ctx.positions, ctx.slot_mapping[cache.group], inv_freq,

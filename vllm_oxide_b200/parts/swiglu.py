@@ -20,6 +20,7 @@ class SwiGLU(FeedForward):
         self.w_gate_up = to_compute(torch.cat([w_gate, w_up], dim=0), dtype, device)
         self.w_down = to_compute(w_down, dtype, device)
         self.dtype = dtype
+        self.fused = True             # False forces the separate product + activation kernels (tests)
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
@@ -30,7 +31,12 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]
-        gate_up = matmul(x, self.w_gate_up, ctx.alloc((T, 2 * self.inter)))
         act = ctx.alloc((T, self.inter))
-        kernels.swiglu(gate_up, act)
+        if (self.dtype == torch.bfloat16 and T <= kernels.FUSED_GEMM_MAX_ROWS and self.fused
+                and kernels.gemm_sm100_supported(x, self.w_gate_up)):
+            # few rows: one kernel, the activation applied in the product's epilogue
+            kernels.gemm_swiglu(x, self.w_gate_up, act)
+        else:
+            gate_up = matmul(x, self.w_gate_up, ctx.alloc((T, 2 * self.inter)))
+            kernels.swiglu(gate_up, act)
         return matmul(act, self.w_down, out if out is not None else ctx.alloc((T, self.hidden)))

@@ -44,6 +44,7 @@ class EngineConfig:
     prefill_chunk: Optional[int] = None  # most prompt tokens of one request per step
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
     pdl: bool = True                   # programmatic dependent launch between the engine's kernels
+    fold_norms: bool = True            # steps of few rows: norms and residual adds folded into the products
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -128,16 +128,43 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 //               (crates/engine/src/backend/cpu/rope.rs:87-99; angle float(pos) * inv_freq, precise
 //               sinf/cosf), q goes to C, rotated k and v go straight to their cache slots
 //               (crates/engine/src/backend/cpu/mod.rs:257-285): no separate rotary / cache-write pass
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
+//   EPI_RESID   the product is a block's output (attention's or the feed-forward's): it is added to the
+//               float32 residual (crates/engine/src/backend/cpu/mod.rs:351-358), and the input of the
+//               NEXT norm is prepared in the same pass: x' = bf16(residual * next norm's weight) and,
+//               per 128-feature tile and token, the sum of the residual's squares. The next product
+//               multiplies its accumulator by 1 / sqrt(mean(residual^2) + eps), a per-token scalar
+//               that commutes with the product, so the RMSNorm (:182-197) needs no kernel of its own.
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_RESID = 3 };
 
-struct QkvArgs {                       // EPI_QKV only
+// Everything an epilogue may need beyond C; a plain struct that the host fills (same layout in
+// kernels.py). Unused members are null / 0.
+struct EpiArgs {
+    // EPI_QKV
     const int* positions;              // [T]
     const int* slots;                  // [T] cache slot of each token, -1: none
     const float* inv_freq;             // [hd / 2] or null (no rotation)
     __nv_bfloat16* kcache;             // [pages, KV, page_size, hd]
     __nv_bfloat16* vcache;
+    // any mode: scale token t's accumulator by 1 / sqrt(sum_i ssq_in[i * ld_ssq + t] * inv_h + eps)
+    const float* ssq_in;
+    // EPI_RESID
+    float* resid;                      // [T, N] float32, updated in place
+    const float* next_w;               // [N] weight of the norm that follows
+    __nv_bfloat16* xn_out;             // [T, N] bf16(residual * next_w)
+    float* ssq_out;                    // [ceil(N / 128), ld_ssq] partial sums of squares
+    long long ld_resid, ld_xn;
     int q_dim, kv_dim, hd, KV, page_size;
+    int ssq_tiles, ld_ssq;
+    float inv_h, eps;
+    int pad_;
 };
+typedef EpiArgs QkvArgs;
+
+__device__ __forceinline__ float token_scale(const EpiArgs& ea, int t) {
+    float s = 0.f;
+    for (int i = 0; i < ea.ssq_tiles; ++i) s += ea.ssq_in[(size_t)i * ea.ld_ssq + t];      // tile order: fixed
+    return 1.0f / sqrtf(s * ea.inv_h + ea.eps);
+}
 
 template <int BT, int EPI> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
 template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage_bytes<BT, EPI_STORE>(); }
@@ -153,6 +180,21 @@ __device__ __forceinline__ void finish_element(OutT* __restrict__ C, long long l
                                                float ps, int pslot) {
     if (EPI == EPI_STORE) {
         if (f < N) store_out<OutT>(C + (size_t)t * ldc + f, v);
+    } else if (EPI == EPI_RESID) {
+        // all 128 threads of the tile come here together: `row` is scratch for the sum of squares
+        float sq = 0.f;
+        if (f < N) {
+            const float r_new = (pre ? pc : qa.resid[(size_t)t * qa.ld_resid + f]) + v;
+            qa.resid[(size_t)t * qa.ld_resid + f] = r_new;
+            qa.xn_out[(size_t)t * qa.ld_xn + f] = __float2bfloat16_rn(r_new * qa.next_w[f]);
+            sq = r_new * r_new;
+        }
+        sq = warp_sum(sq);
+        float* red = const_cast<float*>(row);
+        if ((col & 31) == 0) red[col >> 5] = sq;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (col == 0) qa.ssq_out[(size_t)m_tile * qa.ld_ssq + t] = (red[0] + red[1]) + (red[2] + red[3]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
     } else if (EPI == EPI_SWIGLU) {
         // columns 0..63: gate of feature m_tile * 64 + col; columns 64..127: up of the same features
         const int fo = m_tile * (BM / 2) + col;
@@ -206,7 +248,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     uint64_t* acc_bar = empty_bar + STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-    float* xch = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);      // 128 floats (EPI_QKV)
+    float* xch = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);      // 128 floats: partners meet here
+    float* sc = xch + 128;                                                        // BT floats: per-token scales
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -313,6 +356,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         }
         pdl_wait();
+        // per-token scale of the accumulator (the folded RMSNorm of this product's input) and, for a
+        // residual epilogue, the old residual of the tokens this block finishes: both come from
+        // kernels in front, so they are fetched after the wait, while the product itself runs
+        if (col < BT) sc[col] = (qa.ssq_in && t0 + col < T) ? token_scale(qa, t0 + col) : 1.f;
+        if (EPI == EPI_RESID && splits > 1) {
+#pragma unroll
+            for (int k = 0; k < PRE; ++k) {
+                const int j = split + k * splits;
+                pc[k] = (j < BT && t0 + j < T && f < N) ? qa.resid[(size_t)(t0 + j) * qa.ld_resid + f] : 0.f;
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -326,7 +381,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (f < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, __uint_as_float(r[j]));
+                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, __uint_as_float(r[j]) * sc[c + j]);
                 }
             }
         } else if (ok) {
@@ -339,12 +394,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 tmem_ld16(taddr + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = __uint_as_float(r[j]) * sc[c + j];
             }
             if (splits == 1) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 for (int j = 0; j < BT && t0 + j < T; ++j)
-                    finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, tile[j * BM + col], tile + j * BM, m_tile, N, qa, false, 0.f, 0.f, -1);
+                    finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, tile[j * BM + col], EPI == EPI_RESID ? xch : tile + j * BM, m_tile, N,
+                                              qa, false, 0.f, 0.f, -1);
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -372,6 +428,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     for (int p = 0; p < 8; ++p) acc += part[p];       // rank order, zeros beyond the last rank
                     if (EPI == EPI_STORE) {
                         if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
+                    } else if (EPI == EPI_RESID) {
+                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, k < PRE, pc[k < PRE ? k : 0], 0.f, -1);
                     } else {
                         // partners meet in a row of shared memory
                         xch[col] = acc;
@@ -750,7 +808,7 @@ VOB_EXPORT int vob_gemm_sm100_qkv(const void* X, long long ldx, const void* W, l
     if (e) return e;
     if (H <= 0 || KV <= 0 || hd <= 0 || (hd & 1) || BM % hd != 0 || page_size <= 0) return VOB_ERR_UNSUPPORTED;
     if (!positions || !kcache || !vcache || ldq < (long long)H * hd) return VOB_ERR_BAD_ARG;
-    QkvArgs qa;
+    QkvArgs qa = {};
     qa.positions = positions; qa.slots = slots; qa.inv_freq = inv_freq;
     qa.kcache = (__nv_bfloat16*)kcache; qa.vcache = (__nv_bfloat16*)vcache;
     qa.q_dim = H * hd; qa.kv_dim = KV * hd; qa.hd = hd; qa.KV = KV; qa.page_size = page_size;
@@ -763,4 +821,52 @@ VOB_EXPORT int vob_gemm_sm100_qkv(const void* X, long long ldx, const void* W, l
     if (e) return e;
     if (bt == 16) return launch<16, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
     return launch<32, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
+}
+
+// The general entry point for few tokens (T <= 32): any epilogue mode, with an optional per-token
+// scale of the accumulator (`ea->ssq_in`, the folded RMSNorm of X). `mode` is one of EPI_*;
+// `n_features` is the number of output features (for EPI_SWIGLU: I, with W of shape [2I, K]; for
+// EPI_QKV: (H + 2 KV) * hd). `ea` is read on the host at launch time and passed by value.
+VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int out_code,
+                                 int T, int n_features, int K, int splits, int mode, const EpiArgs* ea, int* err_flag,
+                                 cudaStream_t stream) {
+    int kb_per = 0;
+    int e = fused_common(T, K, ldx, ldw, X, W, &splits, &kb_per);
+    if (e) return e;
+    if (!ea || n_features <= 0) return VOB_ERR_BAD_ARG;
+    if (ea->ssq_in && (ea->ssq_tiles <= 0 || ea->ld_ssq < T)) return VOB_ERR_BAD_ARG;
+    const int N = n_features;
+    const long long w_rows = mode == EPI_SWIGLU ? 2LL * N : N;
+    int bt = pick_bt(T);
+    CUtensorMap mw, mx;
+    e = make_map(&mw, W, w_rows, K, ldw, mode == EPI_SWIGLU ? BM / 2 : BM);
+    if (e) return e;
+    e = make_map(&mx, X, T, K, ldx, bt);
+    if (e) return e;
+#define GOX(BT_, OUT_, EPI_) return launch<BT_, 6, OUT_, EPI_>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, mode == EPI_SWIGLU ? N : 0, *ea, stream)
+    switch (mode) {
+        case EPI_STORE:
+            if (ldc < N) return VOB_ERR_BAD_ARG;
+            if (out_code == VOB_F32) { if (bt == 16) GOX(16, float, EPI_STORE); GOX(32, float, EPI_STORE); }
+            if (out_code == VOB_BF16) { if (bt == 16) GOX(16, __nv_bfloat16, EPI_STORE); GOX(32, __nv_bfloat16, EPI_STORE); }
+            return VOB_ERR_BAD_ARG;
+        case EPI_SWIGLU:
+            if (ldc < N || out_code != VOB_BF16) return VOB_ERR_BAD_ARG;
+            if (bt == 16) GOX(16, __nv_bfloat16, EPI_SWIGLU);
+            GOX(32, __nv_bfloat16, EPI_SWIGLU);
+        case EPI_QKV:
+            if (out_code != VOB_BF16 || ea->hd <= 0 || (ea->hd & 1) || BM % ea->hd != 0 || ea->page_size <= 0 || !ea->positions ||
+                !ea->kcache || !ea->vcache || ldc < ea->q_dim || N != ea->q_dim + 2 * ea->kv_dim)
+                return VOB_ERR_BAD_ARG;
+            if (bt == 16) GOX(16, __nv_bfloat16, EPI_QKV);
+            GOX(32, __nv_bfloat16, EPI_QKV);
+        case EPI_RESID:
+            if (!ea->resid || !ea->next_w || !ea->xn_out || !ea->ssq_out || ea->ld_resid < N || ea->ld_xn < N || ea->ld_ssq < T)
+                return VOB_ERR_BAD_ARG;
+            if (bt == 16) GOX(16, __nv_bfloat16, EPI_RESID);
+            GOX(32, __nv_bfloat16, EPI_RESID);
+        default:
+            return VOB_ERR_BAD_ARG;
+    }
+#undef GOX
 }

@@ -25,7 +25,7 @@ from ..cache.pools import CachePools
 from ..config import EngineConfig, architecture_for, read_config_json
 from ..csrc.build import runtime_module
 from ..errors import CapacityError, KernelError, ShapeError
-from ..parts.base import ModelSpec, StepContext, Workspace
+from ..parts.base import FOLD_ROWS, ModelSpec, StepContext, Workspace
 from ..weights import load_safetensors_weights, weights_from_tensors
 
 
@@ -104,6 +104,8 @@ class ModelRunner:
         self.graphs_enabled = bool(engine.cuda_graphs)
         self.decode_layout = self.rt.step_layout(self.seqs_cap, self.seqs_cap, self.seqs_cap, G, self.max_pages)
         self._graphs = {}
+        self._foldable = None
+        self._folded = None
         self._graph_launches = {}
         self._graph_pool = None
 
@@ -164,10 +166,35 @@ class ModelRunner:
         return self.rt.build_step(self.manager, entries, self.rows_cap, self.seqs_cap, self.logits_cap,
                                   self.max_pages, self.spec.vocab_size)
 
+    def _can_fold(self, rows: int) -> bool:
+        """Few rows and parts that all offer the folded form (see parts.base.FoldedState)."""
+        if self._foldable is None:
+            spec = self.spec
+            from ..parts.rmsnorm import RMSNorm
+            self._foldable = bool(
+                self.dtype == torch.bfloat16 and self.engine.fold_norms and spec.schedule
+                and hasattr(spec.embedding, "forward_folded") and isinstance(spec.final_norm, RMSNorm)
+                and all(getattr(spec.blocks[c.layer], "can_fold", lambda: False)() and c.cache is not None and c.write
+                        for c in spec.schedule))
+        return self._foldable and rows <= FOLD_ROWS
+
+    def _forward_folded(self, ctx: StepContext):
+        spec = self.spec
+        calls = spec.schedule
+        st = spec.embedding.forward_folded(ctx, spec.blocks[calls[0].layer].norm1)
+        for i, call in enumerate(calls):
+            nxt = spec.blocks[calls[i + 1].layer].norm1 if i + 1 < len(calls) else spec.final_norm
+            spec.blocks[call.layer].forward_folded(st, ctx, self.pools.layer_cache(call.cache, call.write), nxt)
+        return st
+
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         """Embedding and every scheduled block; returns (residual, pending): the float32 residual
         and the last block's output that is still to be added to it."""
         spec, ws = self.spec, ctx.workspace
+        self._folded = None
+        if self._can_fold(ctx.rows):
+            self._folded = self._forward_folded(ctx)
+            return self._folded.resid, None
         resid = spec.embedding.forward(ctx)
         es_shape = (ctx.rows, spec.hidden_size)
         pend = [ctx.alloc(es_shape), ctx.alloc(es_shape)]
@@ -190,9 +217,14 @@ class ModelRunner:
             n = min(self.logit_chunk, num_logit_rows - c0)
             with ctx.workspace.scope():
                 rows = d[L["logit_rows"] + c0:L["logit_rows"] + c0 + n]
-                normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n)
                 logits = ctx.workspace.alloc((n, V), torch.float32)
-                spec.lm_head.forward(normed, logits)
+                if (self._folded is not None and ctx.decode_only and n == num_logit_rows == ctx.rows
+                        and getattr(spec.lm_head, "can_fold", lambda: False)()):
+                    # every row is wanted, in order: the head reads the folded residual directly
+                    spec.lm_head.forward_folded(self._folded, spec.final_norm.eps, n, logits)
+                else:
+                    normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n)
+                    spec.lm_head.forward(normed, logits)
                 temp = d[L["temperature"] + c0:L["temperature"] + c0 + n].view(torch.float32)
                 seeds = d[L["seeds"] + 2 * c0:L["seeds"] + 2 * (c0 + n)]
                 steps = d[L["sample_steps"] + c0:L["sample_steps"] + c0 + n]

@@ -494,6 +494,126 @@ def gemm_qkv_rope(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
              H, KV, hd, kcache.shape[2], _stream()), op)
 
 
+# ------------------------------------------------------------------------------------ folded norms (few rows)
+EPI_STORE, EPI_SWIGLU, EPI_QKV, EPI_RESID = 0, 1, 2, 3
+
+
+class _EpiArgs(ctypes.Structure):
+    """Mirror of `EpiArgs` in csrc/gemm_sm100.cu."""
+    _fields_ = [("positions", _P), ("slots", _P), ("inv_freq", _P), ("kcache", _P), ("vcache", _P),
+                ("ssq_in", _P), ("resid", _P), ("next_w", _P), ("xn_out", _P), ("ssq_out", _P),
+                ("ld_resid", _L), ("ld_xn", _L),
+                ("q_dim", _I), ("kv_dim", _I), ("hd", _I), ("KV", _I), ("page_size", _I),
+                ("ssq_tiles", _I), ("ld_ssq", _I), ("inv_h", _F), ("eps", _F), ("pad_", _I)]
+
+
+def _dp(t: Optional[torch.Tensor]) -> int:
+    return t.data_ptr() if t is not None else 0
+
+
+@_timed
+def embed_fold(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, next_w: torch.Tensor, xn: torch.Tensor,
+               ssq: torch.Tensor, err_flag: Optional[torch.Tensor] = None) -> None:
+    """resid[t] = table[tokens[t]] (float32), xn[t] = bf16(resid * next_w), ssq[tile, t] = sum of squares of
+    resid over features 128*tile .. +127: the embedding with the first norm's input prepared."""
+    op = "embed_fold"
+    _cuda(op, table, tokens, resid, next_w, xn, ssq, err_flag)
+    T, h = resid.shape
+    if table.dim() != 2 or table.shape[1] != h or not table.is_contiguous():
+        raise ShapeError(op, f"table must be contiguous [vocab, {h}], got {list(table.shape)}")
+    _int32_vec(tokens, T, op, "tokens")
+    if resid.dtype != torch.float32 or not resid.is_contiguous() or xn.dtype != torch.bfloat16 or xn.shape != resid.shape or not xn.is_contiguous():
+        raise ShapeError(op, "resid must be contiguous float32 [T, h] and xn contiguous bfloat16 of the same shape")
+    if next_w.dtype != torch.float32 or next_w.shape != (h,) or not next_w.is_contiguous():
+        raise ShapeError(op, f"next_w must be float32 [{h}]")
+    tiles = -(-h // 128)
+    if ssq.dtype != torch.float32 or ssq.dim() != 2 or ssq.shape[0] < tiles or ssq.shape[1] < T or not ssq.is_contiguous():
+        raise ShapeError(op, f"ssq must be contiguous float32 [>={tiles}, >={T}], got {list(ssq.shape)}")
+    f = _fn("elementwise", "vob_embed_fold", [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P])
+    _check(f(_ptr(table), _code(table, op), _ptr(tokens), _ptr(resid), _ptr(next_w), _ptr(xn), _ptr(ssq), ssq.shape[1], T, h,
+             table.shape[0], _ptr(err_flag), _stream()), op)
+
+
+@_timed
+def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mode: int, n_features: int, *,
+               ssq_in: Optional[torch.Tensor] = None, eps: float = 0.0, qkv=None, resid=None,
+               splits: Optional[int] = None) -> None:
+    """The tcgen05 product for at most 32 rows with a fused epilogue and, optionally, the RMSNorm of
+    its input folded in: `a` holds bf16(x * norm weight), `ssq_in` [tiles, ld] the per-tile sums of
+    squares of x, and each token's accumulator is multiplied by 1 / sqrt(mean(x^2) + eps).
+      EPI_STORE  out[T, n] (bfloat16 or float32) = result
+      EPI_SWIGLU out[T, n] = silu(gate) * up, w = [Wg; Wu] of shape [2n, K]
+      EPI_QKV    qkv = (positions, slots, inv_freq, kcache, vcache, H, KV, hd): out[T, H*hd] = rotated q,
+                 rotated k and v go to their cache slots
+      EPI_RESID  resid = (resid float32 [T, n] updated in place, next_w float32 [n], xn_out bfloat16 [T, n],
+                 ssq_out float32 [tiles(n), ld]); out is None"""
+    op = "gemm_fused"
+    _cuda(op, a, w, out, ssq_in)
+    if not gemm_sm100_supported(a, w):
+        raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    T, K = a.shape
+    if T > FUSED_GEMM_MAX_ROWS:
+        raise ShapeError(op, f"{T} rows: the fused kernel takes at most {FUSED_GEMM_MAX_ROWS}")
+    w_rows = 2 * n_features if mode == EPI_SWIGLU else n_features
+    if w.shape != (w_rows, K):
+        raise ShapeError(op, f"w must be [{w_rows}, {K}], got {list(w.shape)}")
+    ea = _EpiArgs()
+    if ssq_in is not None:
+        if ssq_in.dtype != torch.float32 or ssq_in.dim() != 2 or ssq_in.shape[0] != -(-K // 128) or ssq_in.shape[1] < T or not ssq_in.is_contiguous():
+            raise ShapeError(op, f"ssq_in must be contiguous float32 [{-(-K // 128)}, >={T}], got {list(ssq_in.shape)}")
+        ea.ssq_in, ea.ssq_tiles, ea.ld_ssq, ea.inv_h, ea.eps = _dp(ssq_in), ssq_in.shape[0], ssq_in.shape[1], 1.0 / K, float(eps)
+    out_code, ldc, out_ptr = 1, n_features, 0
+    if mode in (EPI_STORE, EPI_SWIGLU):
+        if out is None or out.shape != (T, n_features) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise ShapeError(op, f"out must be [{T}, {n_features}] bfloat16 or float32")
+        if mode == EPI_SWIGLU and out.dtype != torch.bfloat16:
+            raise ShapeError(op, "the SwiGLU epilogue writes bfloat16")
+        out_code, ldc, out_ptr = _code(out, op), out.stride(0), out.data_ptr()
+    elif mode == EPI_QKV:
+        positions, slots, inv_freq, kcache, vcache, H, KV, hd = qkv
+        _cuda(op, positions, slots, inv_freq, kcache, vcache)
+        if not gemm_qkv_rope_supported(hd) or n_features != (H + 2 * KV) * hd:
+            raise ShapeError(op, f"qkv sizes do not fit: heads {H}/{KV}, head_dim {hd}, features {n_features}")
+        if out is None or out.shape != (T, H * hd) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+            raise ShapeError(op, f"out must be bfloat16 [{T}, {H * hd}]")
+        _int32_vec(positions, T, op, "positions")
+        if slots is not None:
+            _int32_vec(slots, T, op, "slots")
+        for name, c in (("kcache", kcache), ("vcache", vcache)):
+            if c.dim() != 4 or c.shape[1] != KV or c.shape[3] != hd or not c.is_contiguous() or c.dtype != torch.bfloat16:
+                raise ShapeError(op, f"{name} must be contiguous bfloat16 [pages, {KV}, page_size, {hd}]")
+        if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape != (hd // 2,)):
+            raise ShapeError(op, f"inv_freq must be float32 [{hd // 2}]")
+        ea.positions, ea.slots, ea.inv_freq, ea.kcache, ea.vcache = _dp(positions), _dp(slots), _dp(inv_freq), _dp(kcache), _dp(vcache)
+        ea.q_dim, ea.kv_dim, ea.hd, ea.KV, ea.page_size = H * hd, KV * hd, hd, KV, kcache.shape[2]
+        ldc, out_ptr = out.stride(0), out.data_ptr()
+    elif mode == EPI_RESID:
+        r, next_w, xn_out, ssq_out = resid
+        _cuda(op, r, next_w, xn_out, ssq_out)
+        tiles = -(-n_features // 128)
+        if r.dtype != torch.float32 or r.shape != (T, n_features) or r.stride(1) != 1:
+            raise ShapeError(op, f"resid must be float32 [{T}, {n_features}]")
+        if xn_out.dtype != torch.bfloat16 or xn_out.shape != (T, n_features) or xn_out.stride(1) != 1:
+            raise ShapeError(op, f"xn_out must be bfloat16 [{T}, {n_features}]")
+        if next_w.dtype != torch.float32 or next_w.shape != (n_features,) or not next_w.is_contiguous():
+            raise ShapeError(op, f"next_w must be float32 [{n_features}]")
+        if ssq_out.dtype != torch.float32 or ssq_out.dim() != 2 or ssq_out.shape[0] < tiles or ssq_out.shape[1] < T or not ssq_out.is_contiguous():
+            raise ShapeError(op, f"ssq_out must be contiguous float32 [>={tiles}, >={T}]")
+        ea.resid, ea.next_w, ea.xn_out, ea.ssq_out = _dp(r), _dp(next_w), _dp(xn_out), _dp(ssq_out)
+        ea.ld_resid, ea.ld_xn = r.stride(0), xn_out.stride(0)
+        if ea.ld_ssq == 0:
+            ea.ld_ssq = ssq_out.shape[1]
+        elif ea.ld_ssq != ssq_out.shape[1]:
+            raise ShapeError(op, "ssq_in and ssq_out must have the same row length")
+    else:
+        raise ShapeError(op, f"unknown epilogue mode {mode}")
+    if splits is None:
+        splits = _pick_splits(T, w_rows, K, a.device)
+    f = _fn("gemm_sm100", "vob_gemm_sm100_ex", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, ctypes.POINTER(_EpiArgs), _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _P(out_ptr), ldc, out_code, T, n_features, K, int(splits), int(mode),
+             ctypes.byref(ea), _ptr(_scratch_for(a.device).err), _stream()), op)
+
+
 def gemm_sm100_check() -> None:
     """Raise if a wait inside the tensor-core product ever timed out (reads one word from the device)."""
     for dev, sc in _gemm_scratch.items():

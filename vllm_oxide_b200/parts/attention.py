@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import CacheSpec, LayerCache, Mixer, StepContext
+from .base import CacheSpec, FoldedState, LayerCache, Mixer, StepContext
 from .linear import matmul, to_compute
 
 
@@ -92,6 +92,27 @@ class Attention(Mixer):
         attn = ctx.alloc((T, qd))
         self.attend(q, attn, ctx, cache)
         return matmul(attn, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
+
+    def can_fold(self) -> bool:
+        """Whether this mixer can take its input in folded form (see FoldedState): bfloat16, its own
+        k/v projections, a head size the fused projection epilogue takes, TMA-addressable weights."""
+        return (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and kernels.gemm_qkv_rope_supported(self.hd)
+                and self.hidden % 8 == 0 and (self.H * self.hd) % 8 == 0)
+
+    def forward_folded(self, st: FoldedState, eps: float, ctx: StepContext, cache: LayerCache, next_w: torch.Tensor) -> None:
+        """q/k/v projection with the preceding norm folded in, rotary + cache write in its epilogue;
+        attention; output projection whose epilogue adds into the residual and prepares the next
+        norm's input (weight `next_w`). Updates `st` in place."""
+        T = st.xn.shape[0]
+        qd = self.H * self.hd
+        inv_freq = self.position.inv_freq if self.position is not None else None
+        q = ctx.alloc((T, qd))
+        kernels.gemm_fused(st.xn, self.w_qkv, q, kernels.EPI_QKV, self.w_qkv.shape[0], ssq_in=st.ssq, eps=eps,
+                           qkv=(ctx.positions, ctx.slot_mapping[cache.group] if cache.write else None, inv_freq, cache.k, cache.v,
+                                self.H, self.KV, self.hd))
+        attn = ctx.alloc((T, qd))
+        self.attend(q, attn, ctx, cache)
+        kernels.gemm_fused(attn, self.w_o, None, kernels.EPI_RESID, self.hidden, resid=(st.resid, next_w, st.xn, st.ssq))
 
     def attend(self, q, out, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with sizes the tensor-core kernels take: the decode kernel for steps of single

@@ -126,6 +126,21 @@ class StepContext:
         return self.workspace.alloc(shape, dtype or self.dtype)
 
 
+@dataclass
+class FoldedState:
+    """The residual stream of a step of few rows with the next norm's input prepared ("folded"
+    form): the kernel that produced `resid` also wrote `xn` = bf16(resid * weight of the norm that
+    follows) and `ssq` [tile, row] = sums of squares of `resid` over tiles of 128 features. The
+    matrix product that consumes `xn` multiplies its result by 1 / sqrt(mean(resid^2) + eps), so no
+    norm kernel runs. Parts that can work on this form offer `can_fold()` and `forward_folded`."""
+    resid: torch.Tensor     # float32 [rows, hidden]
+    xn: torch.Tensor        # bfloat16 [rows, hidden]
+    ssq: torch.Tensor       # float32 [ceil(hidden / 128), FOLD_ROWS]
+
+
+FOLD_ROWS = 32              # most rows a step may have for the folded form
+
+
 # ------------------------------------------------------------------------------ part interfaces
 class Mixer:
     """Mixes information between the tokens of a request (attention here)."""

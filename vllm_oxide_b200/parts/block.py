@@ -11,7 +11,8 @@ from typing import Optional
 
 import torch
 
-from .base import FeedForward, LayerCache, Mixer, Norm, StepContext
+from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StepContext
+from .rmsnorm import RMSNorm
 
 
 class Block:
@@ -26,6 +27,23 @@ class Block:
         (normed input + mixer scratch) and (normed input + feed-forward scratch)."""
         row = rows * hidden * act_bytes + 256
         return 2 * row + max(self.mixer.workspace_bytes(rows), self.feed_forward.workspace_bytes(rows))
+
+    def can_fold(self) -> bool:
+        """Whether this block can run in folded form (see FoldedState): both norms are RMSNorms (a
+        per-token scale and a per-feature weight, which is what folds into the neighbouring
+        products) and mixer and feed-forward both offer it."""
+        return (isinstance(self.norm1, RMSNorm) and isinstance(self.norm2, RMSNorm)
+                and getattr(self.mixer, "can_fold", lambda: False)() and getattr(self.feed_forward, "can_fold", lambda: False)()
+                and self.mixer.state_spec() is None)
+
+    def forward_folded(self, st: FoldedState, ctx: StepContext, cache: Optional[LayerCache], next_norm: RMSNorm) -> None:
+        """The block on the folded residual: no norm kernel, no separate residual add. `next_norm`
+        is the norm that will read the residual after this block (the next block's first norm, or
+        the model's final norm)."""
+        with ctx.workspace.scope():
+            self.mixer.forward_folded(st, self.norm1.eps, ctx, cache, self.norm2.weight)
+        with ctx.workspace.scope():
+            self.feed_forward.forward_folded(st, self.norm2.eps, ctx, next_norm.weight)
 
     def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import StepContext
+from .base import FOLD_ROWS, FoldedState, StepContext
 from .linear import to_compute
 
 
@@ -25,6 +25,15 @@ class Embedding:
         return resid
 
 
+    def forward_folded(self, ctx: StepContext, next_norm) -> FoldedState:
+        """The embedding with the first norm's input prepared (see FoldedState)."""
+        h = self.hidden
+        st = FoldedState(resid=ctx.alloc((ctx.rows, h), torch.float32), xn=ctx.alloc((ctx.rows, h), torch.bfloat16),
+                         ssq=ctx.alloc((-(-h // 128), FOLD_ROWS), torch.float32))
+        kernels.embed_fold(self.table, ctx.tokens, st.resid, next_norm.weight, st.xn, st.ssq, self.err_flag)
+        return st
+
+
 class LMHead:
     """`weight` may be the Embedding's own table (tied): no copy is made then."""
 
@@ -37,4 +46,13 @@ class LMHead:
 
     def forward(self, normed: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         kernels.linear(normed, self.weight, out)
+        return out
+
+    def can_fold(self) -> bool:
+        return self.weight.dtype == torch.bfloat16 and self.hidden % 8 == 0
+
+    def forward_folded(self, st: FoldedState, eps: float, rows: int, out: torch.Tensor) -> torch.Tensor:
+        """Logits of the first `rows` rows straight from the folded residual: the final norm is the
+        per-token scale of the product."""
+        kernels.gemm_fused(st.xn[:rows], self.weight, out, kernels.EPI_STORE, self.vocab, ssq_in=st.ssq, eps=eps)
         return out

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import FeedForward, StepContext
+from .base import FeedForward, FoldedState, StepContext
 from .linear import matmul, to_compute
 
 
@@ -28,6 +28,17 @@ class SwiGLU(FeedForward):
     def workspace_bytes(self, rows: int) -> int:
         es = 2 if self.dtype == torch.bfloat16 else 4
         return rows * 3 * self.inter * es + 2 * 256
+
+    def can_fold(self) -> bool:
+        return self.dtype == torch.bfloat16 and self.fused and self.hidden % 8 == 0 and self.inter % 8 == 0
+
+    def forward_folded(self, st: FoldedState, eps: float, ctx: StepContext, next_w: torch.Tensor) -> None:
+        """gate/up product with the preceding norm folded in and the activation in its epilogue;
+        down product whose epilogue adds into the residual and prepares the next norm's input."""
+        T = st.xn.shape[0]
+        act = ctx.alloc((T, self.inter))
+        kernels.gemm_fused(st.xn, self.w_gate_up, act, kernels.EPI_SWIGLU, self.inter, ssq_in=st.ssq, eps=eps)
+        kernels.gemm_fused(act, self.w_down, None, kernels.EPI_RESID, self.hidden, resid=(st.resid, next_w, st.xn, st.ssq))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]

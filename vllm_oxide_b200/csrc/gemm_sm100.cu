@@ -186,7 +186,7 @@ __device__ __forceinline__ void finish_element(OutT* __restrict__ C, long long l
         if (f < N) {
             const float r_new = (pre ? pc : qa.resid[(size_t)t * qa.ld_resid + f]) + v;
             qa.resid[(size_t)t * qa.ld_resid + f] = r_new;
-            qa.xn_out[(size_t)t * qa.ld_xn + f] = __float2bfloat16_rn(r_new * qa.next_w[f]);
+            qa.xn_out[(size_t)t * qa.ld_xn + f] = __float2bfloat16_rn(r_new * ps);
             sq = r_new * r_new;
         }
         sq = warp_sum(sq);
@@ -359,7 +359,20 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // per-token scale of the accumulator (the folded RMSNorm of this product's input) and, for a
         // residual epilogue, the old residual of the tokens this block finishes: both come from
         // kernels in front, so they are fetched after the wait, while the product itself runs
-        if (col < BT) sc[col] = (qa.ssq_in && t0 + col < T) ? token_scale(qa, t0 + col) : 1.f;
+        {
+            // 128 threads = BT tokens x (128 / BT) lanes: lane l adds the tiles l, l + L, ... of its
+            // token, then the lanes' sums are added pairwise in a fixed tree (one L2 round trip
+            // instead of one per tile)
+            constexpr int L = 128 / BT;
+            const int tk = col / L, ln = col % L;
+            float part = 0.f;
+            if (qa.ssq_in && t0 + tk < T)
+                for (int i = ln; i < qa.ssq_tiles; i += L) part += qa.ssq_in[(size_t)i * qa.ld_ssq + t0 + tk];
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (ln == 0) sc[tk] = (qa.ssq_in && t0 + tk < T) ? 1.0f / sqrtf(part * qa.inv_h + qa.eps) : 1.f;
+        }
+        if (EPI == EPI_RESID) ps[0] = f < N ? qa.next_w[f] : 0.f;       // the next norm's weight of this feature
         if (EPI == EPI_RESID && splits > 1) {
 #pragma unroll
             for (int k = 0; k < PRE; ++k) {
@@ -400,7 +413,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 for (int j = 0; j < BT && t0 + j < T; ++j)
                     finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, tile[j * BM + col], EPI == EPI_RESID ? xch : tile + j * BM, m_tile, N,
-                                              qa, false, 0.f, 0.f, -1);
+                                              qa, false, 0.f, EPI == EPI_RESID ? ps[0] : 0.f, -1);
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -429,7 +442,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     if (EPI == EPI_STORE) {
                         if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
                     } else if (EPI == EPI_RESID) {
-                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, k < PRE, pc[k < PRE ? k : 0], 0.f, -1);
+                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, k < PRE, pc[k < PRE ? k : 0], ps[0], -1);
                     } else {
                         // partners meet in a row of shared memory
                         xch[col] = acc;

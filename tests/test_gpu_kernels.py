@@ -130,13 +130,16 @@ def test_linear_bf16_library_product():
     assert rel(o16, want) <= 2 ** -8
 
 
-def _paged_case(dt, H, KV, hd, page, seqs, seed, scale_key=None):
+def _paged_case(dt, H, KV, hd, page, seqs, seed, scale_key=None, poison=False):
     """seqs: list of (context_len, num_new). Returns tensors for the kernel and per-sequence q/k/v."""
     g = torch.Generator().manual_seed(seed)
     total_pages = sum(-(-(c + n) // page) for c, n in seqs) + 3
     perm = torch.randperm(total_pages, generator=g).tolist()          # shuffled, non-identity tables
     kc = torch.randn(total_pages, KV, page, hd, generator=g).to(dt)   # stale values everywhere
     vc = torch.randn(total_pages, KV, page, hd, generator=g).to(dt)
+    if poison:                                                        # what no request wrote is NaN: it must reach no result
+        kc.fill_(float("nan"))
+        vc.fill_(float("nan"))
     max_pages = max(-(-(c + n) // page) for c, n in seqs) + 1
     bt = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)
     qs, ks, vs, row_seq, positions = [], [], [], [], []
@@ -353,6 +356,61 @@ def test_attn_prefill_mma(H, KV, hd, page, window):
         want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd, window=window or None)[c:]
         assert rel(out[r:r + n], want) <= 2 ** -6, (s, c, n)     # P is rounded to bfloat16 before P V: one more 2^-9 rounding per key
         r += n
+
+
+@pytest.mark.parametrize("H,KV,hd,page", [(8, 2, 64, 16), (3, 3, 64, 8), (16, 2, 64, 32), (32, 8, 64, 64), (2, 1, 64, 128)])
+def test_attn_prefill_sm100(H, KV, hd, page):
+    """The tcgen05 kernel for prompt portions: portions that start mid-page, at a page edge, at
+    zero; single tokens beside them; more than one row tile and more than one key tile; one key far
+    back scaled so that a wrong or missing key shows. Cache slots no request wrote hold NaN."""
+    dt = torch.bfloat16
+    seqs = [(5, 6), (0, 3), (2 * page, page), (137, 1), (0, 1), (3 * page - 1, 2), (0, 150), (201, 77), (0, 300), (250, 130)]
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=hd + H + page,
+                                                              scale_key=lambda L: min(3, L - 1), poison=True)
+    starts, ctxs = _starts_ctx(seqs)
+    out = torch.full_like(qrows, 7.0).to(DEV)
+    k = K()
+    assert k.attn_prefill_sm100_supported(H, KV, hd, page, bt.shape[1])
+    args = (qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), starts, ctxs, len(seqs), max(n for _, n in seqs),
+            H, KV, hd, 1.0 / math.sqrt(hd))
+    k.attn_prefill_sm100(*args)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd)[c:]
+        assert rel(out[r:r + n], want) <= 2 ** -6, (s, c, n)     # P is rounded to bfloat16 before P V
+        r += n
+    first = out.clone()
+    out.fill_(3.0)
+    k.attn_prefill_sm100(*args)                                   # nothing needs resetting between launches
+    assert torch.equal(out, first)
+
+
+def test_attn_prefill_sm100_far_key_and_refusals():
+    from vllm_oxide_b200.errors import ShapeError
+    k = K()
+    H, KV, hd, page = 4, 1, 64, 16
+    seqs = [(0, 1000), (900, 100)]
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(torch.bfloat16, H, KV, hd, page, seqs, seed=5,
+                                                              scale_key=lambda L: 3, poison=True)
+    starts, ctxs = _starts_ctx(seqs)
+    out = torch.empty_like(qrows).to(DEV)
+    k.attn_prefill_sm100(qrows.to(DEV), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), starts, ctxs, 2, 1000, H, KV, hd, 0.125)
+    r = 0
+    for s, (c, n) in enumerate(seqs):
+        want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd)[c:]
+        assert rel(out[r:r + n], want) <= 2 ** -6, (s, c, n)
+        r += n
+    k.gemm_sm100_check()
+    assert not k.attn_prefill_sm100_supported(6, 2, 64, 16, 64)      # 3 heads per kv head: no power of two
+    assert not k.attn_prefill_sm100_supported(4, 2, 128, 16, 64) and not k.attn_prefill_sm100_supported(4, 2, 64, 24, 64)
+    assert not k.attn_prefill_sm100_supported(4, 2, 64, 16, 1 << 20)  # the page list would not fit shared memory
+    q = torch.zeros(1, 6 * 64, dtype=torch.bfloat16, device=DEV)
+    kc6 = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ShapeError, match="not supported"):
+        k.attn_prefill_sm100(q, q.clone(), kc6, kc6, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 6, 2, 64, 1.0)
 
 
 @pytest.mark.parametrize("splits", [1, 3, 8])

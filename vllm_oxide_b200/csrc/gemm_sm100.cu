@@ -28,91 +28,18 @@
 // exception. No TMA load uses cluster multicast.
 #include "common.cuh"
 VOB_PDL_SWITCH(gemm_sm100)
-#include <cuda.h>
-#include <mutex>
+#include "sm100.cuh"
 #include <unordered_map>
 
 namespace {
+using namespace vob_sm100;
 
 constexpr int BM = 128;           // weight rows (output features) per block
 constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait. Returns false (and raises the flags) when the limit passes or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_flag, int code) {
-    unsigned long long t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u) {
-            if (*abort_flag) return false;
-            unsigned long long now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                if (err_flag) atomicExch(err_flag, code);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups of 8 rows
-// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
-    uint64_t addr = smem_u32(tile);
-    uint64_t d = (addr & 0x3FFFF) >> 4;          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                      // leading byte offset: unused for swizzled K-major
-    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset
-    d |= (uint64_t)1 << 46;                      // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
-    return d;
-}
-
-// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-}
+// kind::f16 instruction descriptor of this file's products: M = 128 weight rows, N = n tokens, both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) { return umma_idesc_bf16(BM, n, false); }
 
 template <typename OutT> __device__ __forceinline__ void store_out(OutT* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
@@ -481,9 +408,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 // buffer to C, the MMA warp already fills the other, and the TMA ring runs ahead across tile
 // boundaries; so the tensor cores never wait for an epilogue. Bound: tensor-core throughput.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 template <int BT, int STAGES, typename OutT>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -601,22 +525,6 @@ gemm_sm100_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
 struct MapKey {
     const void* ptr; long long rows, cols, ld; int box_rows;
     bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }

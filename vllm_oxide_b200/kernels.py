@@ -87,7 +87,7 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 
 _fn_cache = {}
-_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "sampling")
+_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "attention_sm100", "sampling")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -160,7 +160,7 @@ def modules_for(dtype) -> tuple:
     first start."""
     if dtype == torch.float32:
         return ("elementwise", "gemm_f32", "attention", "sampling")
-    return ("elementwise", "gemm_sm100", "attention", "attention_mma", "sampling")
+    return ("elementwise", "gemm_sm100", "attention", "attention_mma", "attention_sm100", "sampling")
 
 
 def preload(modules=_MODULES) -> None:
@@ -615,13 +615,15 @@ def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mo
 
 
 def gemm_sm100_check() -> None:
-    """Raise if a wait inside the tensor-core product ever timed out (reads one word from the device)."""
+    """Raise if a bounded wait inside a tcgen05 kernel (matrix product or attention) ever expired
+    (reads one word from the device)."""
     for dev, sc in _gemm_scratch.items():
         code = int(sc.err.item())
         if code:
             sc.err.zero_()
-            raise KernelError(f"gemm_sm100: a bounded wait expired inside the kernel (role {code}: 1 = TMA producer, "
-                              "2 = MMA issuer, 3 = epilogue); its result is not valid")
+            raise KernelError(f"a bounded wait expired inside a tensor-core kernel (code {code}: 1-3 = matrix product: TMA "
+                              "producer, MMA issuer, epilogue; 11-21 = attention: 11-12 TMA producer, 13-17 MMA issuer, "
+                              "18-21 softmax rows); its result is not valid")
 
 
 # Above this many rows the library product is used for bfloat16 (None: the tensor-core kernel of this
@@ -746,6 +748,53 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
              block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
              head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
+
+
+def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:
+    """Whether the tcgen05 attention kernel for prompt portions takes these sizes (bfloat16, no window)."""
+    f = _fn("attention_sm100", "vob_attn_prefill_sm100_supported", [_I, _I, _I, _I, _I])
+    return bool(f(num_heads, num_kv_heads, head_dim, page_size, max_pages))
+
+
+@_timed
+def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
+                       num_heads: int, num_kv_heads: int, head_dim: int, scale: float) -> None:
+    """Attention for portions of prompts and mixed batches on the tcgen05 tensor cores (bfloat16,
+    head_dim 64, no window): Q, K and V tiles by TMA straight from the pages of the cache, scores
+    and output in tensor memory. Arguments as `attn_prefill_mma`."""
+    op = "attn_prefill_sm100"
+    if not scale > 0:
+        raise ShapeError(op, f"the score scale must be positive, got {scale}")
+    _cuda(op, q, out, kcache, vcache, block_tables, seq_starts, context_lens)
+    _rows_2d(q, op, "q")
+    _rows_2d(out, op, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or vcache.dtype != torch.bfloat16:
+        raise ShapeError(op, "the tensor-core attention kernels are bfloat16 only")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise ShapeError(op, f"q and out must be [T, {num_heads * head_dim}], got {list(q.shape)} and {list(out.shape)}")
+    for name, c in (("kcache", kcache), ("vcache", vcache)):
+        if c.dim() != 4 or c.shape[1] != num_kv_heads or c.shape[3] != head_dim or not c.is_contiguous():
+            raise ShapeError(op, f"{name} must be contiguous [pages, {num_kv_heads}, page_size, {head_dim}], got {list(c.shape)}")
+    if kcache.shape != vcache.shape:
+        raise ShapeError(op, "kcache and vcache differ in shape")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, "block_tables must be contiguous int32 [S, max_pages]")
+    if block_tables.shape[0] < num_seqs:
+        raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {num_seqs} requests")
+    for name, t in (("q", q), ("out", out)):
+        if t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+            raise ShapeError(op, f"{name} rows must be 16-byte aligned")
+    if not attn_prefill_sm100_supported(num_heads, num_kv_heads, head_dim, kcache.shape[2], block_tables.shape[1]):
+        raise ShapeError(op, f"sizes not supported: heads {num_heads}/{num_kv_heads}, head_dim {head_dim}, page "
+                             f"{kcache.shape[2]}, {block_tables.shape[1]} pages per request (head_dim 64, heads per kv head "
+                             "a power of two, page size a power of two from 8 to 128)")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(context_lens, num_seqs, op, "context_lens")
+    f = _fn("attention_sm100", "vob_attn_prefill_sm100",
+            [_P, _L, _L, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P])
+    _check(f(_ptr(q), q.shape[0], q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
+             _ptr(block_tables), block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads,
+             num_kv_heads, head_dim, kcache.shape[2], float(scale), _ptr(_scratch_for(q.device).err), _stream()), op)
 
 
 @_timed

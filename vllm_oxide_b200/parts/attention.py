@@ -51,7 +51,7 @@ class Attention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         self.hidden = hidden
         self.dtype = dtype
-        self.impl = "auto"            # "general" forces the general attention kernel (tests)
+        self.impl = "auto"            # "general" forces the general attention kernel, "mma" the mma.sync kernels (tests)
         self.fused = True             # False forces the separate projection / rotary / cache-write kernels
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
 
@@ -116,14 +116,19 @@ class Attention(Mixer):
 
     def attend(self, q, out, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with sizes the tensor-core kernels take: the decode kernel for steps of single
-        tokens, the portion kernel for everything else. Otherwise (float32, other head sizes) the
-        general kernel."""
+        tokens; for everything else the tcgen05 kernel (head size 64, no window) or the mma.sync
+        portion kernel. Otherwise (float32, other head sizes) the general kernel."""
         page = cache.k.shape[2]
         bt = ctx.block_tables[cache.group]
         if self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0:
             if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
                 kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd,
                                         self.scale, self.window, self.decode_splits(ctx.rows))
+                return
+            if (not ctx.decode_only and ctx.max_new > 0 and self.window == 0 and self.impl != "mma"
+                    and kernels.attn_prefill_sm100_supported(self.H, self.KV, self.hd, page, bt.shape[1])):
+                kernels.attn_prefill_sm100(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,
+                                           ctx.max_new, self.H, self.KV, self.hd, self.scale)
                 return
             if not ctx.decode_only and ctx.max_new > 0 and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, False):
                 kernels.attn_prefill_mma(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,

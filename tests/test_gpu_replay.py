@@ -175,6 +175,24 @@ def test_mixed_batches_reuse_pages(tmp_path_factory, name, dtype):
     print(f"{name} {dtype}: mixed worst rel diff {worst:.2e}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_four_ways_at_the_benchmark_layer_sizes(tmp_path_factory, dtype):
+    """Two layers of Llama 3.2 1B's sizes (vocabulary 128256, 32 heads on 8 kv heads, K = 8192 in the
+    down projection): the kernels at the sizes the benchmark runs, cut four ways. The longer request
+    spans several row tiles and key tiles of the attention kernels."""
+    cfg, _, page = TINY["1B"]
+    model_dir = make_model_dir(tmp_path_factory.getbasetemp(), "1B")
+    reqs = _requests(cfg.vocab_size, [150, 70], 77)
+    s = _session(model_dir, dtype, 256, page)
+    w1 = check(run_trace(s, whole_steps(reqs)), model_dir, reqs, dtype, "whole")
+    w2 = check(run_trace(s, bulk_tail_steps(reqs)), model_dir, reqs, dtype, "bulk+tail")
+    w3 = check(run_trace(s, portion_steps(reqs, sizes=(64, 7, 2, 33, 3, 16, 2, 1, 40))), model_dir, reqs, dtype, "portions")
+    w4 = check(run_trace(s, mixed_steps(reqs, seed=11)), model_dir, reqs, dtype, "mixed")
+    assert s.runner.manager.check_invariants() == ""
+    assert s.runner.manager.num_free_pages(0) == s.runner.manager.num_pages(0)
+    print(f"1B sizes {dtype}: worst rel diff whole {w1:.2e} bulk+tail {w2:.2e} portions {w3:.2e} mixed {w4:.2e}")
+
+
 def test_f32_cuts_agree_closely(tmp_path_factory):
     """In 32-bit, the same position computed whole, token by token and in portions agrees far
     inside the tolerance against the oracle: the reference's bound between two of its own paths

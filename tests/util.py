@@ -31,7 +31,17 @@ TINY_D = LlamaConfig(
     head_dim=64, vocab_size=200, max_position_embeddings=1024, rms_norm_eps=1e-5, rope_theta=500000.0,
     rope_scaling=RopeScaling(32.0, 1.0, 4.0, 128), tie_word_embeddings=True)
 
-TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16)}   # config, std, page size
+# The layer sizes of Llama 3.2 1B (hidden 2048, 32/8 heads of 64, intermediate 8192, vocabulary
+# 128256, llama3 scaling 32/1/4/8192, tied), two layers: the sizes the benchmark runs, small enough
+# for the plain implementation. Weights as in a checkpoint (std 0.02): with this width larger ones
+# would saturate every softmax.
+LAYERS_1B = LlamaConfig(
+    hidden_size=2048, intermediate_size=8192, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=64, vocab_size=128256, max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192), tie_word_embeddings=True)
+
+TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16),
+        "1B": (LAYERS_1B, 0.02, 16)}   # config, std, page size
 
 
 def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:
@@ -40,7 +50,7 @@ def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:
     if not os.path.exists(os.path.join(d, "model.safetensors")):
         # larger weights than a checkpoint's so that attention is far from uniform and a wrong
         # key or a stale page changes the logits visibly; norm weights away from 1
-        write_random_model(d, cfg, seed, std=(std if std is not None else max(s, 0.08)), norm_jitter=0.3)
+        write_random_model(d, cfg, seed, std=(std if std is not None else (s if name == "1B" else max(s, 0.08))), norm_jitter=0.3)
     return d
 
 

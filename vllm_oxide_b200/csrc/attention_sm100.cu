@@ -8,17 +8,25 @@
 // One block = 128 rows of one (request, kv head): the G = H / KV query heads that share the kv
 // head are stacked as rows (row rr = token rr / G, head kvh * G + rr % G), so a K/V tile is read
 // once per kv head. Per tile of 64 keys:
-//   S[128, 64] = Q K^T       tcgen05.mma, both operands K-major in shared memory, S in tensor memory
+//   S[128, 64] = Q K^T       tcgen05.mma, A = Q from tensor memory, B = the K tile (K-major) from
+//                            shared memory, S in tensor memory
 //   P = exp2(S * scale * log2 e - m)   128 threads, one row each: the row's 64 scores come to
 //                                      registers with tcgen05.ld, P goes back over them as bfloat16
 //                                      pairs (tcgen05.st)
 //   O[128, 64] += P V        tcgen05.mma with A = P from tensor memory, B = the V tile exactly as
 //                            it lies in the cache ([key][head_dim]: an MN-major operand)
-// S has two buffers: the product for tile j+1 is issued before the rows have finished tile j, so
-// the rows never wait for the tensor cores and the tensor cores are busy under the exponentials.
-// The running maximum only moves when a tile's maximum exceeds it by more than 2^8 (the sums stay
-// exact: the same reference is used for P, for the row sum and for O), so O in tensor memory is
-// rescaled rarely, and only then do the rows wait for the previous P V.
+// S has two buffers: the product for tile j+2 is issued right behind P V of tile j (tcgen05.mma
+// of one thread run in issue order, and P lies over the first half of its S), so the rows find
+// the next scores waiting. Q is copied to tensor memory once and is the A operand of every Q K^T
+// from there. The running maximum only moves when a tile's maximum exceeds it by more than 2^8
+// (the sums stay exact: the same reference is used for P, for the row sum and for O), so O in
+// tensor memory is rescaled rarely, and only then do the rows wait for the previous P V.
+//
+// What bounds it (measured): a thread gets one tcgen05.mma or commit through in about 125 clocks
+// whatever its size, and a tile of 64 keys costs ten of them (4 + 4 products of 32 clocks of
+// tensor-core work each, two commits); two blocks per SM overlap their chains. Tried and
+// measured slower: two threads per row (16 softmax warps per SM), exponentials shared with the
+// FMA pipe by a cubic, separate issuing threads for the two products.
 //
 // Data movement: Q by one TMA box [tokens][G heads][64]; K and V page by page, one TMA box
 // [page_size][64] per page straight from the page's place in the cache (a page of one kv head is
@@ -53,6 +61,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -89,13 +102,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + ST * tile_bytes<HD>());
     uint64_t* q_full = bars;                 // [1]
     uint64_t* k_full = bars + 1;             // [ST]
-    uint64_t* k_empty = k_full + ST;         // [ST]
-    uint64_t* v_full = k_empty + ST;         // [ST]
-    uint64_t* v_empty = v_full + ST;         // [ST]
-    uint64_t* s_full = v_empty + ST;         // [2] S of a tile is complete (one barrier per S buffer)
+    uint64_t* v_full = k_full + ST;          // [ST]
+    uint64_t* kv_free = v_full + ST;         // [ST] P V of the tile has completed: its K and V stage are free, O holds it
+    uint64_t* s_full = kv_free + ST;         // [2] S of a tile is complete (one barrier per S buffer)
     uint64_t* p_ready = s_full + 2;          // [2] 128 rows have read S and written P over it
-    uint64_t* pv_done = p_ready + 2;         // [1] O holds the tile
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* q_ready = p_ready + 2;         // [1] Q has been copied to tensor memory
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(q_ready + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     int* s_pages = reinterpret_cast<int*>(bars) + 64;         // [page_end], behind 256 bytes of barriers
 
@@ -105,14 +117,14 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const int first_tok_pos = ctx + tile_row0 / G;
     const int n_tiles = (hi + BN - 1) / BN;
     const int page_end = ((hi - 1) >> page_shift) + 1;
-    constexpr int TMEM_COLS = 256;                            // S0 64 | S1 64 | O 64 (P lies over the first half of its S)
-    constexpr uint32_t COL_O = 2 * BN;
+    constexpr int TMEM_COLS = 256;                            // S0 64 | S1 64 | O 64 | Q 32 (P lies over the first half of its S)
+    constexpr uint32_t COL_O = 2 * BN, COL_Q = 2 * BN + HD;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < ST; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(kv_free + s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(s_full + b, 1); mbar_init(p_ready + b, 128); }
-        mbar_init(pv_done, 1);
+        mbar_init(q_ready, 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -150,19 +162,18 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             const int y = key0 & (page_size - 1);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(k_empty + s, ph ^ 1, abort_flag, err_flag, 11) ? 1 : 0;
-                if (ok) mbar_expect_tx(k_full + s, tile_bytes<HD>());
+                ok = mbar_wait(kv_free + s, ph ^ 1, abort_flag, err_flag, 11) ? 1 : 0;
+                if (ok) {
+                    mbar_expect_tx(k_full + s, tile_bytes<HD>());
+                    mbar_expect_tx(v_full + s, tile_bytes<HD>());
+                }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (lane < ppt) tma_load_4d(sK + s * tile_bytes<HD>() + lane * box_bytes, &map_k, 0, y, kvh, phys, k_full + s);
-            if (lane == 0) {
-                ok = mbar_wait(v_empty + s, ph ^ 1, abort_flag, err_flag, 12) ? 1 : 0;
-                if (ok) mbar_expect_tx(v_full + s, tile_bytes<HD>());
+            if (lane < ppt) {
+                tma_load_4d(sK + s * tile_bytes<HD>() + lane * box_bytes, &map_k, 0, y, kvh, phys, k_full + s);
+                tma_load_4d(sV + s * tile_bytes<HD>() + lane * box_bytes, &map_v, 0, y, kvh, phys, v_full + s);
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane < ppt) tma_load_4d(sV + s * tile_bytes<HD>() + lane * box_bytes, &map_v, 0, y, kvh, phys, v_full + s);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -170,7 +181,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, HD, true);
             const uint32_t tO = tmem_base + COL_O;
-            const uint64_t qdesc = umma_desc_sw128(sQ);
+            const uint32_t tQ = tmem_base + COL_Q;
             // S[j & 1] = Q K_j^T; tcgen05.mma of one thread run in issue order, so a product may be
             // issued as soon as what it overwrites has been handed over (p_ready of tile j - 2)
             auto issue_qk = [&](int j) -> bool {
@@ -180,12 +191,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 const uint64_t kdesc = umma_desc_sw128(sK + s * tile_bytes<HD>());
                 const uint32_t tS = tmem_base + (uint32_t)(j & 1) * BN;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) umma_bf16(tS, qdesc + 2 * k, kdesc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-                umma_commit(k_empty + s);
+                for (int k = 0; k < HD / 16; ++k) umma_bf16_ts(tS, tQ + 8 * k, kdesc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
                 umma_commit(s_full + (j & 1));
                 return true;
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, err_flag, 13) && issue_qk(0);
+            bool ok = mbar_wait(q_ready, 0, abort_flag, err_flag, 13);
+            if (ok) { tcgen05_fence_after(); ok = issue_qk(0); }
             if (ok && n_tiles > 1) ok = issue_qk(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % ST;
@@ -197,8 +208,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)          // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
                     umma_bf16_ts(tO, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(v_empty + s);
-                umma_commit(pv_done);
+                umma_commit(kv_free + s);                   // K and V of the tile may be overwritten; O holds the tile
                 if (j + 2 < n_tiles) ok = issue_qk(j + 2);
             }
         }
@@ -216,7 +226,25 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
             return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, err_flag, code) ? 1 : 0) != 0;
         };
-        for (int j = 0; j < n_tiles; ++j) {
+        // Q goes to tensor memory once: as the A operand of every Q K^T it is then read from there
+        // and not from shared memory again (16 KB per tile of keys less for the tensor cores to
+        // fetch). Row r of the swizzled tile: 16-byte chunk c lies at chunk position c ^ (r & 7).
+        if (wait_all(q_full, 0, 22)) {
+            uint32_t qv[32];
+            const uint4* qrow = reinterpret_cast<const uint4*>(sQ + (size_t)r * HD * 2);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 x = qrow[c ^ (r & 7)];
+                qv[4 * c] = x.x; qv[4 * c + 1] = x.y; qv[4 * c + 2] = x.z; qv[4 * c + 3] = x.w;
+            }
+            tmem_st32(lane_addr + COL_Q, qv);
+            tmem_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(q_ready);
+        } else {
+            ok = false;
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
             const int kbase = j * BN;
             const uint32_t tS = lane_addr + (uint32_t)(j & 1) * BN;
             const bool masked_tile = kbase + BN - 1 > first_tok_pos;      // some row of the block does not see every key
@@ -236,8 +264,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                mx0 = fmaxf(mx0, fmaxf(__uint_as_float(va[i]), __uint_as_float(vb[i])));
-                mx1 = fmaxf(mx1, fmaxf(__uint_as_float(va[i + 1]), __uint_as_float(vb[i + 1])));
+                mx0 = max3(mx0, __uint_as_float(va[i]), __uint_as_float(vb[i]));
+                mx1 = max3(mx1, __uint_as_float(va[i + 1]), __uint_as_float(vb[i + 1]));
             }
             const float mx2 = fmaxf(mx0, mx1) * scale_log2;               // scale > 0: the maximum commutes
             const bool grow = mx2 > m_ref + 8.f;                          // also the first finite maximum
@@ -248,7 +276,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
                 // O may be touched once the previous tile's product has completed
-                if (!wait_all(pv_done, (j - 1) & 1, 19)) { ok = false; break; }
+                if (!wait_all(kv_free + (j - 1) % ST, ((j - 1) / ST) & 1, 19)) { ok = false; break; }
                 tcgen05_fence_after();
 #pragma unroll
                 for (int c = 0; c < HD; c += 16) {
@@ -260,20 +288,23 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                     tmem_st16(lane_addr + COL_O + c, v);
                 }
             }
-            float sum0 = 0.f, sum1 = 0.f;
+            // two scores at a time: the packed float32 pair instructions of sm_100 halve the issue
+            // slots of the scale-and-subtract and of the row sum
+            const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(va[i]), scale_log2, -m_use));        // -inf: 0
-                float p1 = fast_exp2(fmaf(__uint_as_float(va[i + 1]), scale_log2, -m_use));
-                float p2 = fast_exp2(fmaf(__uint_as_float(vb[i]), scale_log2, -m_use));
-                float p3 = fast_exp2(fmaf(__uint_as_float(vb[i + 1]), scale_log2, -m_use));
-                sum0 += p0 + p1;
-                sum1 += p2 + p3;
-                pk[i >> 1] = pack_bf16(p0, p1);
-                pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+                const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(va[i]), __uint_as_float(va[i + 1])), sc2, nm2);
+                const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(vb[i]), __uint_as_float(vb[i + 1])), sc2, nm2);
+                const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));        // -inf: 0
+                const float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+                acc0 = __fadd2_rn(acc0, p0);
+                acc1 = __fadd2_rn(acc1, p1);
+                pk[i >> 1] = pack_bf16(p0.x, p0.y);
+                pk[16 + (i >> 1)] = pack_bf16(p1.x, p1.y);
             }
-            l += sum0 + sum1;
+            l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
             tmem_st32(tS, pk);                                            // P over the first half of its S
             if (j == n_tiles - 1 && quad < 2 && kbase + quad * 32 + 31 >= hi) {
                 // the last tile: V rows past the last key hold whatever the page held before
@@ -291,7 +322,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             tcgen05_fence_before();
             mbar_arrive(p_ready + (j & 1));
         }
-        if (ok && wait_all(pv_done, (n_tiles - 1) & 1, 21)) {
+        if (ok && wait_all(kv_free + (n_tiles - 1) % ST, ((n_tiles - 1) / ST) & 1, 21)) {
             tcgen05_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst = out + (size_t)(row0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;

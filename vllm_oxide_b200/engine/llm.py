@@ -142,6 +142,8 @@ class LLM:
                 raise NaNError("pick_tokens")        # crates/engine/src/backend/cpu/mod.rs:377-379
             self.stats["steps"] += 1
             self.stats["decode_steps"] += int(decode_only)
+            if self.stats["steps"] % 64 == 0:
+                r.check_kernels()                    # one word from the device: a kernel's bounded wait that expired
             gen = self._generated
             for rid in sampling:
                 gen[rid] += 1
@@ -202,6 +204,7 @@ class LLM:
         while self.has_unfinished():
             for out in self.step():
                 results[out.request_id] = out
+        self.runner.check_kernels()
         return [results[i] for i in ids]
 
 

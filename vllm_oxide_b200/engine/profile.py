@@ -33,7 +33,7 @@ def profile_decode_step(runner, prompt, steps: int = 4):
 # Single kernels on synthetic operands, for profilers:
 #   python -m vllm_oxide_b200.engine.profile gemm --rows 8 --out 16384 --in 2048 [--copies 6] [--iters 3]
 #   python -m vllm_oxide_b200.engine.profile attn_decode --batch 8 --context 2200
-#   python -m vllm_oxide_b200.engine.profile attn_prefill --tokens 2048
+#   python -m vllm_oxide_b200.engine.profile attn_prefill --tokens 2048 [--impl sm100|mma]
 # Each launch works on operands of its own (several copies, together larger than L2), so that DRAM
 # counters mean something; device time per launch is printed from CUDA events.
 # ------------------------------------------------------------------------------------------------
@@ -55,6 +55,7 @@ def _kernel_cases(argv):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--copies", type=int, default=6)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--impl", default="sm100", choices=["sm100", "mma"], help="attn_prefill: the tcgen05 or the mma.sync kernel")
     a = ap.parse_args(argv)
     dev = "cuda:0"
     bf = torch.bfloat16
@@ -90,8 +91,12 @@ def _kernel_cases(argv):
         else:
             starts = torch.tensor([0, new], dtype=torch.int32, device=dev)
             ctxs = torch.zeros(1, dtype=torch.int32, device=dev)
-            launches = [lambda kc=kc, vc=vc: kernels.attn_prefill_mma(q, out, kc, vc, bt, starts, ctxs, 1, new, H, KV, hd, scale, 0)
-                        for kc, vc in caches]
+            if a.impl == "sm100":
+                launches = [lambda kc=kc, vc=vc: kernels.attn_prefill_sm100(q, out, kc, vc, bt, starts, ctxs, 1, new, H, KV, hd, scale)
+                            for kc, vc in caches]
+            else:
+                launches = [lambda kc=kc, vc=vc: kernels.attn_prefill_mma(q, out, kc, vc, bt, starts, ctxs, 1, new, H, KV, hd, scale, 0)
+                            for kc, vc in caches]
             nbytes = 2 * L * KV * hd * 2 + 2 * new * H * hd * 2
             flops = 4.0 * H * hd * new * (new + 1) / 2
     for f in launches:

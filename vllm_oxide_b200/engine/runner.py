@@ -310,6 +310,12 @@ class ModelRunner:
         self.sampled_host[:b].copy_(self.sampled[:b], non_blocking=True)
 
     # ------------------------------------------------------------------ bookkeeping helpers
+    def check_kernels(self) -> None:
+        """Raise `KernelError` if a bounded wait inside one of the tensor-core kernels expired since
+        the last check (their results are then invalid). Reads one word from the device."""
+        if self.dtype == torch.bfloat16:
+            kernels.gemm_sm100_check()
+
     def admit(self, request_id: int) -> int:
         """Take a state slot for a request and zero its state. -1 when no slot is free."""
         slot = self.manager.admit(request_id)

@@ -58,6 +58,7 @@ class TraceSession:
             out = torch.empty((R, runner.spec.vocab_size), dtype=torch.float32) if R else None
             runner.step(arrays, logits_out=out)
             torch.cuda.synchronize()
+            runner.check_kernels()
             for rid, n in zip(arrays.ids, arrays.new_counts):
                 runner.manager.commit(rid, n)
         for name in msg.get("end", []):

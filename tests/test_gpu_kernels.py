@@ -508,7 +508,8 @@ def test_gemm_sm100_strided_and_refusals():
 
 
 # ----------------------------------------------------------------------------- fused epilogues of the tcgen05 product
-@pytest.mark.parametrize("T,I,Kd,splits", [(1, 128, 64, 1), (8, 8192, 2048, None), (5, 224, 96, 1), (16, 300, 520, 3), (32, 1000, 256, 2), (17, 128, 1024, 8)])
+@pytest.mark.parametrize("T,I,Kd,splits", [(1, 128, 64, 1), (8, 8192, 2048, None), (5, 224, 96, 1), (16, 300, 520, 3), (32, 1000, 256, 2), (17, 128, 1024, 8),
+                                            (33, 224, 96, 1), (64, 8192, 2048, None), (50, 300, 520, 3)])
 def test_gemm_swiglu(T, I, Kd, splits):
     g = torch.Generator().manual_seed(T + I)
     a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
@@ -528,7 +529,8 @@ def test_gemm_swiglu(T, I, Kd, splits):
 
 @pytest.mark.parametrize("rope", [True, False])
 @pytest.mark.parametrize("T,H,KV,hd,Kd,page,splits", [(8, 32, 8, 64, 2048, 16, None), (1, 4, 2, 64, 128, 16, 1), (13, 3, 1, 32, 96, 8, 1),
-                                                      (32, 6, 2, 16, 200, 8, 2), (5, 2, 2, 128, 512, 32, 4), (20, 5, 5, 64, 320, 16, 5)])
+                                                      (32, 6, 2, 16, 200, 8, 2), (5, 2, 2, 128, 512, 32, 4), (20, 5, 5, 64, 320, 16, 5),
+                                                      (64, 32, 8, 64, 2048, 16, None), (41, 3, 1, 32, 96, 8, 2)])
 def test_gemm_qkv_rope(T, H, KV, hd, Kd, page, splits, rope):
     g = torch.Generator().manual_seed(T + H + hd)
     a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
@@ -573,8 +575,58 @@ def test_gemm_qkv_rope(T, H, KV, hd, Kd, page, splits, rope):
 def test_fused_gemm_refusals():
     from vllm_oxide_b200.errors import ShapeError
     k = K()
-    a = torch.zeros(40, 64, dtype=torch.bfloat16, device=DEV)
+    a = torch.zeros(70, 64, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(ShapeError, match="at most 32"):
-        k.gemm_swiglu(a, w, torch.zeros(40, 128, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ShapeError, match="at most 64"):
+        k.gemm_swiglu(a, w, torch.zeros(70, 128, dtype=torch.bfloat16, device=DEV))
     assert not k.gemm_qkv_rope_supported(48) and k.gemm_qkv_rope_supported(64)
+
+
+def _folded_input(T, Kd, g):
+    """A residual x [T, Kd], the next norm's weight, and what the folded form hands to a product:
+    bf16(x * weight) and the sums of squares of x per 128-feature tile."""
+    x = torch.randn(T, Kd, generator=g) * 1.5
+    wn = 1.0 + 0.3 * torch.randn(Kd, generator=g)
+    xn = (x * wn).to(torch.bfloat16)
+    tiles = -(-Kd // 128)
+    ssq = torch.zeros(tiles, 64)
+    for i in range(tiles):
+        ssq[i, :T] = (x[:, i * 128:(i + 1) * 128] ** 2).sum(1)
+    return x, wn, xn, ssq
+
+
+@pytest.mark.parametrize("T,N,Kd,splits", [(1, 128, 128, 1), (8, 2048, 2048, None), (20, 200, 320, 2), (32, 640, 8192, 8),
+                                           (33, 200, 320, 1), (64, 2048, 8192, None), (47, 384, 256, 3)])
+def test_gemm_fused_residual_and_folded_norm(T, N, Kd, splits):
+    """EPI_RESID with the RMSNorm of the input folded in: resid += rmsnorm(x) W^T (the norm as a
+    per-token scale of the accumulator), the next norm's input bf16(resid * next_w) and the
+    per-tile sums of squares of the new residual come out of the same kernel."""
+    from vllm_oxide_b200.kernels import EPI_RESID, EPI_STORE
+    g = torch.Generator().manual_seed(T * 3 + N)
+    eps = 1e-5
+    x, wn, xn, ssq = _folded_input(T, Kd, g)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16)
+    resid0 = torch.randn(T, N, generator=g)
+    next_w = 1.0 + 0.3 * torch.randn(N, generator=g)
+    k = K()
+    resid = resid0.clone().to(DEV)
+    xn_out = torch.full((T, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ssq_out = torch.full((-(-N // 128), 64), 7.0, device=DEV)
+    k.gemm_fused(xn.to(DEV), w.to(DEV), None, EPI_RESID, N, ssq_in=ssq.to(DEV), eps=eps,
+                 resid=(resid, next_w.to(DEV), xn_out, ssq_out), splits=splits)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    # the plain norm of x with weight wn (x * wn rounded to bfloat16 as the kernel's operand), then the product
+    inv = 1.0 / torch.sqrt((x.double() ** 2).mean(1) + eps)
+    want_delta = plain.linear(xn.double(), w.double()) * inv[:, None]
+    want_resid = resid0.double() + want_delta
+    assert rel(resid, want_resid) <= max(2e-6, 2.0 ** -22 * math.sqrt(Kd)) * 4
+    assert rel(xn_out, want_resid * next_w.double()) <= 2 ** -8
+    got = resid.double().cpu()
+    for i in range(-(-N // 128)):
+        want_ssq = (got[:, i * 128:(i + 1) * 128] ** 2).sum(1)
+        assert rel(ssq_out[i, :T], want_ssq) <= 1e-5
+    # the same scale on a plain store
+    out = torch.empty(T, N, device=DEV)
+    k.gemm_fused(xn.to(DEV), w.to(DEV), out, EPI_STORE, N, ssq_in=ssq.to(DEV), eps=eps, splits=splits)
+    assert rel(out, want_delta) <= max(2e-6, 2.0 ** -22 * math.sqrt(Kd)) * 4

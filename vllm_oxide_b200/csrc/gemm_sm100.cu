@@ -87,12 +87,6 @@ struct EpiArgs {
 };
 typedef EpiArgs QkvArgs;
 
-__device__ __forceinline__ float token_scale(const EpiArgs& ea, int t) {
-    float s = 0.f;
-    for (int i = 0; i < ea.ssq_tiles; ++i) s += ea.ssq_in[(size_t)i * ea.ld_ssq + t];      // tile order: fixed
-    return 1.0f / sqrtf(s * ea.inv_h + ea.eps);
-}
-
 template <int BT, int EPI> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
 template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage_bytes<BT, EPI_STORE>(); }
 template <int BT, int EPI> __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
@@ -626,7 +620,7 @@ VOB_EXPORT int vob_gemm_sm100_pick_splits(int T, int N, int K, int num_sms) {
     int bt = pick_bt(T);
     int tiles = ((N + BM - 1) / BM) * ((T + bt - 1) / bt);
     int total_kb = (K + BK - 1) / BK;
-    if (T > 32 || tiles * 2 > num_sms) return 1;
+    if (T > 64 || tiles * 2 > num_sms) return 1;
     int want = num_sms / tiles;
     if (want > 8) want = 8;                                           // the portable cluster size
     int max_splits = total_kb / 4 > 0 ? total_kb / 4 : 1;             // at least 4 k-blocks (256 of K) per split
@@ -689,7 +683,7 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
 // ------------------------------------------------------------------------------------------------ fused epilogues (few tokens)
 namespace {
 int fused_common(int T, int K, long long ldx, long long ldw, const void* X, const void* W, int* splits, int* kb_per) {
-    if (T <= 0 || T > 32) return VOB_ERR_UNSUPPORTED;
+    if (T <= 0 || T > 64) return VOB_ERR_UNSUPPORTED;
     if (K <= 0 || ldx < K || ldw < K) return VOB_ERR_BAD_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0) return VOB_ERR_UNSUPPORTED;
     int total_kb = (K + BK - 1) / BK;
@@ -702,49 +696,7 @@ int fused_common(int T, int K, long long ldx, long long ldw, const void* X, cons
 }
 }  // namespace
 
-// C[T, I] = silu(X Wg^T) * (X Wu^T), W = [Wg; Wu] of shape [2I, K]; T <= 32.
-VOB_EXPORT int vob_gemm_sm100_swiglu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int T,
-                                     int I, int K, int splits, int* err_flag, cudaStream_t stream) {
-    int kb_per = 0;
-    int e = fused_common(T, K, ldx, ldw, X, W, &splits, &kb_per);
-    if (e) return e;
-    if (I <= 0 || ldc < I) return VOB_ERR_BAD_ARG;
-    int bt = pick_bt(T);
-    CUtensorMap mw, mx;
-    e = make_map(&mw, W, 2LL * I, K, ldw, BM / 2);            // boxes of 64 rows: half a tile from each half of W
-    if (e) return e;
-    e = make_map(&mx, X, T, K, ldx, bt);
-    if (e) return e;
-    if (bt == 16) return launch<16, 6, __nv_bfloat16, EPI_SWIGLU>(mw, mx, C, ldc, T, I, K, splits, kb_per, err_flag, I, QkvArgs{}, stream);
-    return launch<32, 6, __nv_bfloat16, EPI_SWIGLU>(mw, mx, C, ldc, T, I, K, splits, kb_per, err_flag, I, QkvArgs{}, stream);
-}
-
-// [q | k | v] = X [Wq; Wk; Wv]^T with rotary positions on q and k; q (rotated) -> Q[T, q_dim], rotated k
-// and v -> their cache slots. T <= 32, 128 a multiple of head_dim.
-VOB_EXPORT int vob_gemm_sm100_qkv(const void* X, long long ldx, const void* W, long long ldw, void* Q, long long ldq, int T, int K,
-                                  int splits, int* err_flag, const int* positions, const int* slots, const float* inv_freq,
-                                  void* kcache, void* vcache, int H, int KV, int hd, int page_size, cudaStream_t stream) {
-    int kb_per = 0;
-    int e = fused_common(T, K, ldx, ldw, X, W, &splits, &kb_per);
-    if (e) return e;
-    if (H <= 0 || KV <= 0 || hd <= 0 || (hd & 1) || BM % hd != 0 || page_size <= 0) return VOB_ERR_UNSUPPORTED;
-    if (!positions || !kcache || !vcache || ldq < (long long)H * hd) return VOB_ERR_BAD_ARG;
-    QkvArgs qa = {};
-    qa.positions = positions; qa.slots = slots; qa.inv_freq = inv_freq;
-    qa.kcache = (__nv_bfloat16*)kcache; qa.vcache = (__nv_bfloat16*)vcache;
-    qa.q_dim = H * hd; qa.kv_dim = KV * hd; qa.hd = hd; qa.KV = KV; qa.page_size = page_size;
-    int N = (H + 2 * KV) * hd;
-    int bt = pick_bt(T);
-    CUtensorMap mw, mx;
-    e = make_map(&mw, W, N, K, ldw, BM);
-    if (e) return e;
-    e = make_map(&mx, X, T, K, ldx, bt);
-    if (e) return e;
-    if (bt == 16) return launch<16, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
-    return launch<32, 6, __nv_bfloat16, EPI_QKV>(mw, mx, Q, ldq, T, N, K, splits, kb_per, err_flag, 0, qa, stream);
-}
-
-// The general entry point for few tokens (T <= 32): any epilogue mode, with an optional per-token
+// The general entry point for few tokens (T <= 64): any epilogue mode, with an optional per-token
 // scale of the accumulator (`ea->ssq_in`, the folded RMSNorm of X). `mode` is one of EPI_*;
 // `n_features` is the number of output features (for EPI_SWIGLU: I, with W of shape [2I, K]; for
 // EPI_QKV: (H + 2 KV) * hd). `ea` is read on the host at launch time and passed by value.
@@ -768,26 +720,49 @@ VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, lo
     switch (mode) {
         case EPI_STORE:
             if (ldc < N) return VOB_ERR_BAD_ARG;
-            if (out_code == VOB_F32) { if (bt == 16) GOX(16, float, EPI_STORE); GOX(32, float, EPI_STORE); }
-            if (out_code == VOB_BF16) { if (bt == 16) GOX(16, __nv_bfloat16, EPI_STORE); GOX(32, __nv_bfloat16, EPI_STORE); }
+            if (out_code == VOB_F32) { if (bt == 16) GOX(16, float, EPI_STORE); if (bt == 32) GOX(32, float, EPI_STORE); GOX(64, float, EPI_STORE); }
+            if (out_code == VOB_BF16) { if (bt == 16) GOX(16, __nv_bfloat16, EPI_STORE); if (bt == 32) GOX(32, __nv_bfloat16, EPI_STORE); GOX(64, __nv_bfloat16, EPI_STORE); }
             return VOB_ERR_BAD_ARG;
         case EPI_SWIGLU:
             if (ldc < N || out_code != VOB_BF16) return VOB_ERR_BAD_ARG;
             if (bt == 16) GOX(16, __nv_bfloat16, EPI_SWIGLU);
-            GOX(32, __nv_bfloat16, EPI_SWIGLU);
+            if (bt == 32) GOX(32, __nv_bfloat16, EPI_SWIGLU);
+            GOX(64, __nv_bfloat16, EPI_SWIGLU);
         case EPI_QKV:
             if (out_code != VOB_BF16 || ea->hd <= 0 || (ea->hd & 1) || BM % ea->hd != 0 || ea->page_size <= 0 || !ea->positions ||
                 !ea->kcache || !ea->vcache || ldc < ea->q_dim || N != ea->q_dim + 2 * ea->kv_dim)
                 return VOB_ERR_BAD_ARG;
             if (bt == 16) GOX(16, __nv_bfloat16, EPI_QKV);
-            GOX(32, __nv_bfloat16, EPI_QKV);
+            if (bt == 32) GOX(32, __nv_bfloat16, EPI_QKV);
+            GOX(64, __nv_bfloat16, EPI_QKV);
         case EPI_RESID:
             if (!ea->resid || !ea->next_w || !ea->xn_out || !ea->ssq_out || ea->ld_resid < N || ea->ld_xn < N || ea->ld_ssq < T)
                 return VOB_ERR_BAD_ARG;
             if (bt == 16) GOX(16, __nv_bfloat16, EPI_RESID);
-            GOX(32, __nv_bfloat16, EPI_RESID);
+            if (bt == 32) GOX(32, __nv_bfloat16, EPI_RESID);
+            GOX(64, __nv_bfloat16, EPI_RESID);
         default:
             return VOB_ERR_BAD_ARG;
     }
 #undef GOX
+}
+
+// C[T, I] = silu(X Wg^T) * (X Wu^T), W = [Wg; Wu] of shape [2I, K]; T <= 64.
+VOB_EXPORT int vob_gemm_sm100_swiglu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int T,
+                                     int I, int K, int splits, int* err_flag, cudaStream_t stream) {
+    EpiArgs ea = {};
+    return vob_gemm_sm100_ex(X, ldx, W, ldw, C, ldc, VOB_BF16, T, I, K, splits, EPI_SWIGLU, &ea, err_flag, stream);
+}
+
+// [q | k | v] = X [Wq; Wk; Wv]^T with rotary positions on q and k; q (rotated) -> Q[T, q_dim], rotated k
+// and v -> their cache slots. T <= 64, 128 a multiple of head_dim.
+VOB_EXPORT int vob_gemm_sm100_qkv(const void* X, long long ldx, const void* W, long long ldw, void* Q, long long ldq, int T, int K,
+                                  int splits, int* err_flag, const int* positions, const int* slots, const float* inv_freq,
+                                  void* kcache, void* vcache, int H, int KV, int hd, int page_size, cudaStream_t stream) {
+    if (H <= 0 || KV <= 0 || hd <= 0 || (hd & 1) || BM % hd != 0 || page_size <= 0) return VOB_ERR_UNSUPPORTED;
+    EpiArgs ea = {};
+    ea.positions = positions; ea.slots = slots; ea.inv_freq = inv_freq;
+    ea.kcache = (__nv_bfloat16*)kcache; ea.vcache = (__nv_bfloat16*)vcache;
+    ea.q_dim = H * hd; ea.kv_dim = KV * hd; ea.hd = hd; ea.KV = KV; ea.page_size = page_size;
+    return vob_gemm_sm100_ex(X, ldx, W, ldw, Q, ldq, VOB_BF16, T, (H + 2 * KV) * hd, K, splits, EPI_QKV, &ea, err_flag, stream);
 }

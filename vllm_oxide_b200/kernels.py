@@ -424,13 +424,14 @@ def _pick_splits(T: int, N: int, K: int, device) -> int:
     return int(f(T, N, K, _scratch_for(device).num_sms))
 
 
-FUSED_GEMM_MAX_ROWS = 32
+FUSED_GEMM_MAX_ROWS = 64      # what the fused kernels take
+FUSED_GEMM_BEST_ROWS = 32     # up to here they beat the library product plus separate kernels (measured at 64 rows: 25 % slower)
 
 
 @_timed
 def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
     """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16): one tcgen05
-    kernel with two accumulators whose epilogue applies the activation, for at most 32 rows."""
+    kernel with two accumulators whose epilogue applies the activation, for at most 64 rows."""
     op = "gemm_swiglu"
     _cuda(op, a, w_gate_up, out)
     if not gemm_sm100_supported(a, w_gate_up):
@@ -460,7 +461,7 @@ def gemm_qkv_rope(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
                   num_heads: int, num_kv_heads: int, head_dim: int, splits: Optional[int] = None) -> None:
     """[q | k | v] = a @ [Wq; Wk; Wv]^T in one tcgen05 kernel whose epilogue rotates q and k (float32
     angles position * inv_freq), writes q to q_out [T, H*hd] and the rotated k and v straight to their
-    cache slots. At most 32 rows; 128 must be a multiple of head_dim."""
+    cache slots. At most 64 rows; 128 must be a multiple of head_dim."""
     op = "gemm_qkv_rope"
     _cuda(op, a, w_qkv, q_out, positions, slots, inv_freq, kcache, vcache)
     if not gemm_sm100_supported(a, w_qkv):
@@ -538,7 +539,7 @@ def embed_fold(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n
 def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mode: int, n_features: int, *,
                ssq_in: Optional[torch.Tensor] = None, eps: float = 0.0, qkv=None, resid=None,
                splits: Optional[int] = None) -> None:
-    """The tcgen05 product for at most 32 rows with a fused epilogue and, optionally, the RMSNorm of
+    """The tcgen05 product for at most 64 rows with a fused epilogue and, optionally, the RMSNorm of
     its input folded in: `a` holds bf16(x * norm weight), `ssq_in` [tiles, ld] the per-tile sums of
     squares of x, and each token's accumulator is multiplied by 1 / sqrt(mean(x^2) + eps).
       EPI_STORE  out[T, n] (bfloat16 or float32) = result

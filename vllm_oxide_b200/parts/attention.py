@@ -72,7 +72,7 @@ class Attention(Mixer):
         qd, kd = self.H * self.hd, self.KV * self.hd
         inv_freq = self.position.inv_freq if self.position is not None else None
         if (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and cache.write
-                and T <= kernels.FUSED_GEMM_MAX_ROWS and kernels.gemm_qkv_rope_supported(self.hd)
+                and T <= kernels.FUSED_GEMM_BEST_ROWS and kernels.gemm_qkv_rope_supported(self.hd)
                 and kernels.gemm_sm100_supported(x, self.w_qkv)):
             # few rows: rotary positions and the cache write happen in the projection's epilogue
             q = ctx.alloc((T, qd))

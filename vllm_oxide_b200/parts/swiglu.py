@@ -43,7 +43,7 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]
         act = ctx.alloc((T, self.inter))
-        if (self.dtype == torch.bfloat16 and T <= kernels.FUSED_GEMM_MAX_ROWS and self.fused
+        if (self.dtype == torch.bfloat16 and T <= kernels.FUSED_GEMM_BEST_ROWS and self.fused
                 and kernels.gemm_sm100_supported(x, self.w_gate_up)):
             # few rows: one kernel, the activation applied in the product's epilogue
             kernels.gemm_swiglu(x, self.w_gate_up, act)

@@ -163,14 +163,22 @@ def main():
     prefill = {"value": PROMPT_LEN / (pre_ms / 1e3), "tokens": PROMPT_LEN, "ms": pre_ms,
                "frac": pre_flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
 
+    def prefill_all(ids):
+        """Step until every request has its first token (none may finish on the way: GEN_LEN is
+        far above the number of steps that takes)."""
+        for _ in range(4 * len(ids) + 16):
+            if all(llm._generated.get(r, 0) >= 1 for r in ids):
+                return
+            llm.step()
+        raise RuntimeError("bench: the prompts did not finish prefilling")
+
     # ---------------------------------------------------------------- decode, device-timed
     def decode_device(B, steps, warmup):
         """B requests with their prompts in the cache; time `steps` decode steps on the device."""
         ids = []
         for i in range(B):
             ids.append(llm.add_request(prompts[i], never_stop))
-        while any(llm._generated.get(r, 0) < 1 for r in ids):     # chunked prefill through the scheduler
-            llm.step()
+        prefill_all(ids)                                          # chunked prefill through the scheduler
         for _ in range(warmup):
             llm.step()
         torch.cuda.synchronize()
@@ -200,8 +208,7 @@ def main():
     # ---------------------------------------------------------------- decode, end to end
     def decode_e2e(B, steps, warmup):
         ids = [llm.add_request(prompts[i], never_stop) for i in range(B)]
-        while any(llm._generated.get(r, 0) < 1 for r in ids):
-            llm.step()
+        prefill_all(ids)
         for _ in range(warmup):
             llm.step()
         torch.cuda.synchronize()

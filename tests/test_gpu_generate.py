@@ -185,3 +185,28 @@ def test_long_decoding_and_first_tokens(tmp_path_factory, dtype):
     got = run_trace(s, steps)
     assert len(got) == 220
     check(got, d, {"x": toks}, dtype, "token by token")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_workspace_formula_covers_the_largest_step(tmp_path_factory, name, dtype):
+    """The step workspace is sized by a formula (the reference's arena formula,
+    crates/engine/src/model.rs:68-90): a step of as many tokens as the engine admits, wanting
+    every row's logits, fits, and the formula is no loose bound."""
+    from vllm_oxide_b200.config import EngineConfig
+    from vllm_oxide_b200.engine import ModelRunner
+    cfg, _, page = TINY[name]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), name)
+    eng = EngineConfig(max_batch_tokens=96, max_seqs=4, max_model_len=96, block_size=page, num_pages=4 * 96 // page,
+                       dtype=dtype, cuda_graphs=False)
+    r = ModelRunner.from_dir(d, eng)
+    toks = random_tokens(96, cfg.vocab_size, 3)
+    r.admit(1)
+    r.manager.reserve(1, 96)
+    out = torch.empty((96, cfg.vocab_size), dtype=torch.float32)
+    r.step(r.build_arrays([r.rt.StepEntry(1, toks, list(range(96)))]), logits_out=out)
+    torch.cuda.synchronize()
+    assert r.workspace.high_water <= r.workspace_bytes == r.workspace_formula(r.rows_cap)
+    assert r.workspace.high_water >= 0.5 * r.workspace_bytes
+    pc, pt = plain.load_model(d)
+    assert max_rel_diff(out[-1], plain.forward(pc, pt, toks)[-1]) <= TOL[torch.float32 if dtype == "float32" else torch.bfloat16]

@@ -210,3 +210,30 @@ def test_workspace_formula_covers_the_largest_step(tmp_path_factory, name, dtype
     assert r.workspace.high_water >= 0.5 * r.workspace_bytes
     pc, pt = plain.load_model(d)
     assert max_rel_diff(out[-1], plain.forward(pc, pt, toks)[-1]) <= TOL[torch.float32 if dtype == "float32" else torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_no_token_and_sees_stop_tokens(tmp_path_factory, dtype):
+    """Steady decode steps are launched one ahead of the host's reads. Outputs are the same with
+    and without, for requests that run to their length and for requests that meet a stop token
+    (seen one step late: what was computed past it is dropped)."""
+    cfg, _, page = TINY["B"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "B")
+    prompts = [random_tokens(L, cfg.vocab_size, 700 + i) for i, L in enumerate([3, 11, 26, 7, 19])]
+    free = sp(max_new_tokens=30, stop_token_ids=())
+    base = llm_for(d, dtype, page, run_ahead=False)
+    full = [o.token_ids for o in base.generate(prompts, free)]
+    assert base.stats["ahead_steps"] == 0
+    # stop tokens that come up at different places (a request's own 4th, 9th, ... token), one request without
+    params = [sp(max_new_tokens=30, stop_token_ids=(full[i][3 + 5 * i],)) if i < 4 else free for i in range(5)]
+    want = base.generate(prompts, params)
+    assert [o.finish_reason for o in want][:4] == ["stop"] * 4 and want[4].finish_reason == "length"
+    ahead = llm_for(d, dtype, page, run_ahead=True)
+    got = ahead.generate(prompts, params)
+    assert ahead.stats["ahead_steps"] > 0
+    for g, w, p, prm in zip(got, want, prompts, params):
+        assert g.finish_reason == w.finish_reason
+        assert_same_or_near_tie(d, p, g.token_ids, w.token_ids, prm, 0.0 if dtype == "float32" else TOL[torch.bfloat16])
+    assert [o.token_ids for o in ahead.generate(prompts, free)] == full or dtype == "bfloat16"
+    assert ahead.runner.manager.check_invariants() == ""
+    assert ahead.runner.manager.num_free_pages(0) == ahead.runner.manager.num_pages(0)

@@ -204,3 +204,103 @@ def test_random_traces_finish_everything_and_leak_nothing(seed):
     for rid, f in got.items():
         assert f.reason == "length" and f.output == [rid] * want[rid]      # preempted or not, the output is whole
     assert c.num_free_pages(0) == pages and c.num_free_slots() == 5
+
+
+# ----------------------------------------------------------------------------- running ahead of the host's reads
+def _ahead_run(s, tokens_of, stops_seen=None):
+    """Drive the scheduler the way the engine does when it launches step n + 1 before it reads
+    step n. `tokens_of(id, k)` is the k-th generated token of a request. Returns what ended."""
+    count, ended, flight = {}, [], None
+
+    def picks(plan):
+        out = []
+        for e in plan.entries:
+            k = count.get(e.id, 0)
+            out.append(tokens_of(e.id, k))
+            count[e.id] = k + 1
+        return out
+    guard = 0
+    while s.has_unfinished() or flight is not None:
+        guard += 1
+        assert guard < 500
+        if flight is None:
+            if s.steady_decode():
+                plan = s.schedule()
+                assert plan.decode_only and not plan.preempted and not plan.admitted
+                toks = picks(plan)
+                s.advance(plan)
+                flight = (plan, toks, list(s.running()))
+            else:
+                plan = s.schedule()
+                ended += s.update(plan, [tokens_of(e.id, count.setdefault(e.id, 0)) for e in plan.entries if e.sample])
+                for e in plan.entries:
+                    if e.sample:
+                        count[e.id] += 1
+            continue
+        nxt = None
+        if s.steady_decode() and list(s.running()) == flight[2]:
+            plan = s.schedule()
+            assert [e.id for e in plan.entries] == flight[2]
+            toks = picks(plan)
+            s.advance(plan)
+            nxt = (plan, toks, list(s.running()))
+        got = s.resolve(flight[0], flight[1], 1 if nxt else 0)
+        ended += got
+        if got and nxt:
+            ended += s.resolve(nxt[0], nxt[1], 0)
+            nxt = None
+        flight = nxt
+    return ended
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_running_ahead_gives_the_same_outputs_as_reading_every_step(seed):
+    """Requests of different lengths, some with stop tokens that come up mid-way, through the
+    run-ahead protocol and through plain update(): same outputs, same reasons, nothing leaks."""
+    rng = random.Random(seed)
+    reqs = []
+    for i in range(6):
+        prompt = [rng.randrange(50) for _ in range(rng.randrange(1, 12))]
+        n = rng.randrange(1, 14)
+        stop = [7] if i % 2 == 0 else []
+        reqs.append((i, prompt, n, stop))
+    gen = {i: [rng.choice([3, 5, 7, 9, 11]) for _ in range(20)] for i, *_ in reqs}
+    tokens_of = lambda rid, k: gen[rid][k]
+
+    c1, s1 = make(pages=64, page=4, budget=16)
+    c2, s2 = make(pages=64, page=4, budget=16)
+    for i, prompt, n, stop in reqs:
+        s1.add_request(i, prompt, sp(n, stop))
+        s2.add_request(i, prompt, sp(n, stop))
+    plain_done, count = [], {}
+    while s1.has_unfinished():
+        plan = s1.schedule()
+        sampled = []
+        for e in plan.entries:
+            if e.sample:
+                sampled.append(tokens_of(e.id, count.get(e.id, 0)))
+                count[e.id] = count.get(e.id, 0) + 1
+        plain_done += s1.update(plan, sampled)
+    ahead_done = _ahead_run(s2, tokens_of)
+    key = lambda fs: sorted((f.id, f.reason, tuple(f.output)) for f in fs)
+    assert key(ahead_done) == key(plain_done)
+    assert c2.check_invariants() == "" and c2.num_free_pages(0) == 64 and c2.num_free_slots() == 8
+
+
+def test_steady_decode_is_false_whenever_the_next_step_could_differ():
+    c, s = make(pages=8, page=4, budget=16)
+    s.add_request(1, [1, 2, 3], sp(4))
+    assert not s.steady_decode()                     # still waiting
+    run_step(s)
+    assert s.steady_decode()                         # decoding, 1 of 4 generated
+    s.add_request(2, [4, 5], sp(4))
+    assert not s.steady_decode()                     # someone waits
+    run_step(s)
+    assert s.steady_decode()
+    run_step(s)                                      # request 1 has 3 of 4: its next token ends it by length
+    assert not s.steady_decode()
+    c2, s2 = make(pages=3, page=4, budget=16)
+    s2.add_request(1, list(range(7)), sp(6))
+    s2.add_request(2, [1], sp(6))
+    run_step(s2)
+    assert c2.num_free_pages(0) == 0 and not s2.steady_decode()      # no free page for every running request

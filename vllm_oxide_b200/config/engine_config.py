@@ -4,7 +4,9 @@ The five knobs and their defaults are the reference's `EngineConfig`
 (crates/engine/src/model.rs:37-66): max_batch_tokens 2048, max_seqs 32,
 max_model_len 8192, block_size 16, kv_pool_bytes 2 GiB. Added here: the compute
 dtype, an explicit page count (tests want tiny pools), the largest portion of a
-prompt that one step takes, and whether decode steps replay CUDA graphs.
+prompt that one step takes, whether decode steps replay CUDA graphs, and the switches of
+what makes a decode step fast (programmatic dependent launch, folded norms, running one
+step ahead of the host's reads).
 """
 from __future__ import annotations
 
@@ -45,6 +47,7 @@ class EngineConfig:
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
     pdl: bool = True                   # programmatic dependent launch between the engine's kernels
     fold_norms: bool = True            # steps of few rows: norms and residual adds folded into the products
+    run_ahead: bool = True             # steady decode: launch step n + 1 before reading step n's tokens (needs cuda_graphs)
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -135,6 +135,9 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def("schedule", &Scheduler::schedule)
         .def("arrays", &Scheduler::arrays)
         .def("update", &Scheduler::update)
+        .def("steady_decode", &Scheduler::steady_decode)
+        .def("advance", &Scheduler::advance)
+        .def("resolve", &Scheduler::resolve)
         .def("take_done", &Scheduler::take_done)
         .def("abort", &Scheduler::abort)
         .def("tokens_of", [](const Scheduler& s, int64_t id) { return s.request(id).tokens; })

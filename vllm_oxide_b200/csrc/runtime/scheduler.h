@@ -221,6 +221,68 @@ public:
         return out;
     }
 
+    // ------------------------------------------------------------------ running ahead of the host's reads
+    // A decode step's picked tokens reach the host one step late when the engine launches step
+    // n + 1 (which takes its input tokens from step n's picks on the device) before it reads
+    // step n. For that the scheduler must plan step n + 1 without knowing step n's tokens:
+    //   steady_decode()   the next step is sure to be a pure decode step of exactly the running
+    //                     requests in their present order, whatever the steps in flight pick (a
+    //                     stop token aside, which `resolve` handles): nobody waits, everybody
+    //                     decodes, nobody reaches max_new_tokens or max_model_len with the next
+    //                     token, every group has a free page for every running request;
+    //   advance(plan)     the step was launched: its bookkeeping with a placeholder for each
+    //                     token that is not known yet;
+    //   resolve(plan, sampled, ahead)   the step's tokens are known; `ahead` steps (0 or 1) were
+    //                     launched after it. A request that picked a stop token ends there:
+    //                     what it was given in the steps launched since is dropped.
+    bool steady_decode() const {
+        if (!waiting_.empty() || running_.empty()) return false;
+        for (int64_t id : running_) {
+            const Request& r = requests_.at(id);
+            if ((int)r.tokens.size() - r.computed != 1) return false;
+            if (r.generated + 1 >= r.params.max_new_tokens) return false;
+            if ((int)r.tokens.size() + 1 > max_model_len_) return false;
+        }
+        for (int g = 0; g < cache_->num_groups(); ++g)
+            if (cache_->num_free_pages(g) < (int64_t)running_.size()) return false;
+        return true;
+    }
+
+    void advance(const StepPlan& plan) {
+        for (const auto& pe : plan.entries) {
+            Request& r = requests_.at(pe.id);
+            if (pe.count != 1 || !pe.sample) throw CacheError("advance: not a decode step");
+            cache_->commit(pe.id, pe.count);
+            r.computed += pe.count;
+            r.tokens.push_back(0);           // placeholder until resolve()
+            r.generated += 1;
+        }
+    }
+
+    std::vector<Finished> resolve(const StepPlan& plan, const std::vector<int32_t>& sampled, int ahead) {
+        std::vector<Finished> out;
+        if (sampled.size() < plan.entries.size()) throw CacheError("resolve: fewer sampled tokens than entries");
+        size_t si = 0;
+        for (const auto& pe : plan.entries) {
+            int32_t tok = sampled[si++];
+            auto it = requests_.find(pe.id);
+            if (it == requests_.end()) continue;                     // ended by an earlier resolve, or aborted
+            Request& r = it->second;
+            if ((int)r.tokens.size() < r.prompt_len + 1 + ahead) throw CacheError("resolve: no placeholder to fill");
+            r.tokens[r.tokens.size() - 1 - ahead] = tok;
+            const auto& stops = r.params.stop_token_ids;
+            if (std::find(stops.begin(), stops.end(), tok) == stops.end()) continue;
+            r.tokens.resize(r.tokens.size() - ahead);
+            r.generated -= ahead;
+            Finished f{pe.id, "stop", generated_of(r)};
+            cache_->release(pe.id);
+            running_.erase(std::remove(running_.begin(), running_.end(), pe.id), running_.end());
+            requests_.erase(it);
+            out.push_back(std::move(f));
+        }
+        return out;
+    }
+
     // Requests finished without a step (capacity failures found while planning).
     std::vector<Finished> take_done() {
         std::vector<Finished> out;

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from ..config import EngineConfig
-from ..errors import CapacityError, NaNError, ShapeError
+from ..errors import CapacityError, EngineError, NaNError, ShapeError
 from ..sampling import SamplingParams
 from .runner import ModelRunner
 
@@ -61,7 +61,11 @@ class LLM:
         self._preempt: Dict[int, int] = {}
         self._tokenizer = None
         self._logit_buf = None
-        self.stats = {"steps": 0, "preemptions": 0, "decode_steps": 0, "graph_steps": 0}
+        self._inflight = None            # a decode step launched but not read yet: (plan, ids, parity, event)
+        self._late: List[RequestOutput] = []
+        self._capturing = 0              # live requests that want logits (they are never run ahead of)
+        self.run_ahead = bool(e.run_ahead) and bool(e.cuda_graphs)
+        self.stats = {"steps": 0, "preemptions": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0}
         tok = os.path.join(model, "tokenizer.json") if isinstance(model, str) else None
         if tok and os.path.exists(tok):
             try:
@@ -102,14 +106,79 @@ class LLM:
         self._prompts[rid] = ids
         self._captured[rid] = {}
         self._generated[rid] = 0
+        if params.capture_logits:
+            self._capturing += 1
         return rid
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None or bool(self._late)
 
     # ------------------------------------------------------------------ one engine step
     def step(self) -> List[RequestOutput]:
-        """schedule -> arrays -> forward -> pick -> update. Returns the requests that finished."""
+        """One engine step: schedule -> arrays -> forward -> pick -> update. Returns the requests
+        that finished.
+
+        While every running request decodes and none can end by length with its next token, the
+        engine runs one step ahead of its own reads: this call launches step n + 1, whose input
+        tokens are step n's picks taken on the device, and only then waits for step n's tokens
+        (`EngineConfig.run_ahead`). The GPU never waits for the host between such steps; a request
+        that picks a stop token is seen one step late and what it was given since is dropped.
+        Tokens do not depend on whether steps are run ahead."""
+        outs, self._late = self._late, []
+        fl = self._inflight
+        if fl is None:
+            if self._may_run_ahead():
+                self._launch_ahead(feed=False, parity=0)
+                return outs
+            return outs + self._step_now()
+        nxt = None
+        if self._may_run_ahead() and list(self.scheduler.running()) == fl[1]:
+            nxt = self._launch_ahead(feed=True, parity=1 - fl[2])
+        else:
+            self._inflight = None
+        ended = self._resolve(fl, 1 if nxt else 0)
+        if ended and nxt:
+            # the rows of the step in flight no longer match the running set: read it now
+            self._inflight = None
+            ended += self._resolve(nxt, 0)
+        return outs + ended
+
+    def _may_run_ahead(self) -> bool:
+        return self.run_ahead and self._capturing == 0 and self.scheduler.steady_decode()
+
+    def _launch_ahead(self, feed: bool, parity: int):
+        r, sched = self.runner, self.scheduler
+        plan = sched.schedule()
+        if not plan.decode_only or plan.preempted or plan.admitted:
+            raise EngineError("run-ahead: the scheduler planned something else than a steady decode step")
+        ids = plan.sampling_ids()
+        event = r.decode_step_graph(sched, plan, feed_from_device=feed, read=False, parity=parity)
+        sched.advance(plan)
+        for rid in ids:
+            self._generated[rid] += 1
+        self.stats["steps"] += 1
+        self.stats["decode_steps"] += 1
+        self.stats["graph_steps"] += 1
+        self.stats["ahead_steps"] += 1
+        if self.stats["steps"] % 64 == 0:
+            r.check_kernels()
+        self._inflight = (plan, ids, parity, event)
+        return self._inflight
+
+    def _resolve(self, flight, ahead: int) -> List[RequestOutput]:
+        plan, ids, parity, event = flight
+        sampled = self.runner.read_decode(event, len(ids), parity)
+        if min(sampled, default=0) < 0:
+            raise NaNError("pick_tokens")            # crates/engine/src/backend/cpu/mod.rs:377-379
+        return self._outputs(self.scheduler.resolve(plan, sampled, ahead))
+
+    def _finish_inflight(self) -> None:
+        """Read the step in flight, if any; requests it ends are handed out by the next `step`."""
+        fl, self._inflight = self._inflight, None
+        if fl is not None:
+            self._late += self._resolve(fl, 0)
+
+    def _step_now(self) -> List[RequestOutput]:
         r, sched = self.runner, self.scheduler
         plan = sched.schedule()
         self.stats["preemptions"] += len(plan.preempted)
@@ -152,9 +221,14 @@ class LLM:
             done = sched.take_done()
             if not done and not plan.preempted and sched.has_unfinished():
                 raise CapacityError("scheduler made no progress: pages", 1, 0)
+        return self._outputs(done)
+
+    def _outputs(self, done) -> List[RequestOutput]:
         outs = []
         for f in done:
             rid = f.id
+            if self._params[rid].capture_logits:
+                self._capturing -= 1
             outs.append(RequestOutput(rid, self._prompts.pop(rid), list(f.output), f.reason,
                                       self.decode(f.output), self._captured.pop(rid), self._preempt.pop(rid, 0)))
             self._params.pop(rid)
@@ -166,6 +240,7 @@ class LLM:
         the host does not wait. For throughput measurement of requests that never stop early; the
         host-side token lists receive placeholders."""
         r, sched = self.runner, self.scheduler
+        self._finish_inflight()
         plan = sched.schedule()
         if not plan.decode_only or plan.preempted or plan.admitted:
             raise ShapeError("step_async", "only steady decode steps can run without reading tokens back")
@@ -181,11 +256,16 @@ class LLM:
         torch.cuda.synchronize()
 
     def abort(self, request_id: int) -> None:
+        self._finish_inflight()
+        if request_id not in self._params:
+            return
         if self.scheduler.abort(request_id):
             self.scheduler.take_done()
         self._forget(request_id)
 
     def _forget(self, rid: int) -> None:
+        if rid in self._params and self._params[rid].capture_logits:
+            self._capturing -= 1
         for d in (self._params, self._prompts, self._captured, self._generated, self._preempt):
             d.pop(rid, None)
 

@@ -85,8 +85,12 @@ class ModelRunner:
         G = self.pools.num_groups
         self.layout = self.rt.step_layout(self.rows_cap, self.seqs_cap, self.logits_cap, G, self.max_pages)
         total = self.layout["total"]
-        self.step_host = torch.empty(total, dtype=torch.int32, pin_memory=True)
-        self.step_host_np = self.step_host.numpy()
+        # a ring of pinned staging buffers: the host may run several steps ahead of the device, and a
+        # buffer is written again only after the copy that reads it has been executed
+        self._stage = [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._stage_np = [t.numpy() for t in self._stage]
+        self._stage_done = [None] * len(self._stage)
+        self._stage_next = 0
         self.step_dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         # workspace: residual + two pending buffers + the largest block + the head's chunk
         V = self.spec.vocab_size
@@ -97,7 +101,8 @@ class ModelRunner:
         self.pick_idx = torch.empty(self.logit_chunk * splits, dtype=torch.int32, device=self.device)
         self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
-        self.sampled_host = torch.zeros(self.seqs_cap, dtype=torch.int32, pin_memory=True)
+        # two pinned buffers: a step's picks may still be unread when the next step writes its own
+        self.sampled_host = torch.zeros((2, self.seqs_cap), dtype=torch.int32, pin_memory=True)
         self.sampled_host_np = self.sampled_host.numpy()
         self.steps_run = 0
         self.last_upload_bytes = 0
@@ -158,8 +163,15 @@ class ModelRunner:
         """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
         n = arrays.used
         self.last_upload_bytes = 4 * n
-        arrays.copy_into(self.step_host_np)
-        self.step_dev[:n].copy_(self.step_host[:n], non_blocking=True)
+        i = self._stage_next
+        self._stage_next = (i + 1) % len(self._stage)
+        if self._stage_done[i] is not None:
+            self._stage_done[i].synchronize()        # the copy that last read this buffer has run
+        arrays.copy_into(self._stage_np[i])
+        self.step_dev[:n].copy_(self._stage[i][:n], non_blocking=True)
+        if self._stage_done[i] is None:
+            self._stage_done[i] = torch.cuda.Event()
+        self._stage_done[i].record()
 
     def build_arrays(self, entries):
         """Lay out a batch given as runtime StepEntry objects (pages must be reserved already)."""
@@ -259,12 +271,14 @@ class ModelRunner:
             b *= 2
         return min(b, self.seqs_cap)
 
-    def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True) -> List[int]:
+    def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True, parity: int = 0):
         """A step in which every request brings exactly one token. Its kernels are the same as any
         step's, but their launches are replayed from a CUDA graph captured once per batch-size
         class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing), because
         at small batches launching ~10 kernels per layer costs more than running them
-        (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51)."""
+        (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51).
+        The picked tokens land in pinned host buffer `parity`. With `read` the call waits and
+        returns them; without, it returns an event to hand to `read_decode` later."""
         S = plan.num_entries
         L = self.decode_layout
         arrays = scheduler.arrays(plan, L["rows_cap"], L["seqs_cap"], L["logits_cap"], self.max_pages, self.spec.vocab_size)
@@ -276,38 +290,46 @@ class ModelRunner:
             # runs ahead without reading them back; request order must not have changed)
             self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
         b = self._bucket(S)
-        graph = self._graphs.get(b)
+        key = (b, parity)
+        graph = self._graphs.get(key)
         if graph is None:
             # first step of this class: run it eagerly (that is this step's result), then record
             # the same launches for the steps to come
-            self._decode_eager(b)
+            self._decode_eager(b, parity)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = kernels.launch_count()
             with torch.cuda.graph(g, pool=self._graph_pool):
-                self._decode_eager(b)
-            self._graph_launches[b] = kernels.launch_count() - n0
-            kernels.count_launches(-self._graph_launches[b])      # recorded, not run
-            self._graphs[b] = g
+                self._decode_eager(b, parity)
+            self._graph_launches[key] = kernels.launch_count() - n0
+            kernels.count_launches(-self._graph_launches[key])      # recorded, not run
+            self._graphs[key] = g
             self._graph_pool = self._graph_pool or g.pool()
         else:
             graph.replay()
-            kernels.count_launches(self._graph_launches[b])
+            kernels.count_launches(self._graph_launches[key])
         self.steps_run += 1
         if not read:
-            return []
+            ev = torch.cuda.Event()
+            ev.record()
+            return ev
         # the picked tokens were copied to pinned host memory by the step itself
         torch.cuda.current_stream().synchronize()
-        return self.sampled_host_np[:S].tolist()
+        return self.sampled_host_np[parity, :S].tolist()
 
-    def _decode_eager(self, b: int) -> None:
+    def read_decode(self, event, count: int, parity: int) -> List[int]:
+        """The picked tokens of a decode step launched without reading."""
+        event.synchronize()
+        return self.sampled_host_np[parity, :count].tolist()
+
+    def _decode_eager(self, b: int, parity: int = 0) -> None:
         L = self.decode_layout
         self.workspace.reset()
         ctx = self.context(b, b, None, L)
         ctx.decode_only, ctx.max_new = True, 1
         resid, pending = self._forward(ctx)
         self._head(resid, pending, ctx, b, None, L)
-        self.sampled_host[:b].copy_(self.sampled[:b], non_blocking=True)
+        self.sampled_host[parity, :b].copy_(self.sampled[:b], non_blocking=True)
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def check_kernels(self) -> None:

@@ -205,13 +205,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     int* s_pages = reinterpret_cast<int*>(sV0 + 2 * BN * LD);            // [max_pages]
 
     const int G = H / KV;
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    // Blocks are handed out in the order x, y, z: the kv head runs fastest and the row tile slowest,
+    // later row tiles (which see more keys) first, so that over the whole grid the long blocks
+    // start first and the short ones fill the gaps behind them.
+    const int kvh = blockIdx.x, seq = blockIdx.y;
     const int row0 = seq_starts[seq];
     const int n_new = seq_starts[seq + 1] - row0;
     const int total_rows = n_new * G;
-    // later row tiles see more keys: hand them out first, so that the long blocks do not all
-    // start last and leave the SMs idle behind them
-    const int tile_row0 = (gridDim.x - 1 - blockIdx.x) * BM;
+    const int tile_row0 = (gridDim.z - 1 - blockIdx.z) * BM;
     if (tile_row0 >= total_rows) return;
     const int ctx = context_lens[seq];
     const int* bt = block_tables + (size_t)seq * max_pages;
@@ -543,7 +544,9 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     int e = ensure_smem(attn_prefill_mma_kernel<HD>, smem, &configured);
     if (e) return e;
     int G = H / KV;
-    dim3 grid(((long long)max_new * G + 63) / 64, S, KV);
+    const long long row_tiles = ((long long)max_new * G + 63) / 64;
+    if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
+    dim3 grid(KV, S, (unsigned)row_tiles);
     return vob_launch(attn_prefill_mma_kernel<HD>, grid, dim3(NTHREADS), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size), window,

@@ -86,11 +86,13 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     pdl_launch_dependents();
     // The step's metadata was copied before the first kernel of the step started: readable now.
     const int G = H / KV;
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    // Blocks are handed out in the order x, y, z: the kv head runs fastest and the row tile
+    // slowest, later row tiles (which see more keys) first, so that over the whole grid the long
+    // blocks start first and the short ones fill the gaps behind them.
+    const int kvh = blockIdx.x, seq = blockIdx.y;
     const int row0 = seq_starts[seq];
     const int total_rows = (seq_starts[seq + 1] - row0) * G;
-    // later row tiles see more keys: hand them out first
-    const int tile_row0 = (gridDim.x - 1 - blockIdx.x) * BM;
+    const int tile_row0 = (gridDim.z - 1 - blockIdx.z) * BM;
     if (tile_row0 >= total_rows) return;
     const int ctx = context_lens[seq];
 
@@ -439,7 +441,9 @@ VOB_EXPORT int vob_attn_prefill_sm100(const void* q, long long q_rows, long long
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    dim3 grid(((long long)max_new * G + BM - 1) / BM, S, KV);
+    const long long row_tiles = ((long long)max_new * G + BM - 1) / BM;
+    if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
+    dim3 grid(KV, S, (unsigned)row_tiles);
     return vob_launch(attn_prefill_sm100_kernel<64>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride,
                       block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size), (int)num_pages,
                       scale * 1.4426950408889634f, err_flag);

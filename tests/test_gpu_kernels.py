@@ -235,9 +235,9 @@ def test_paged_attention_refuses_bad_sizes():
 
 
 @pytest.mark.parametrize("dt", DT, ids=IDS)
-@pytest.mark.parametrize("T", [11, 70])
+@pytest.mark.parametrize("T,pad", [(11, 0), (70, 0), (70, 1)])      # few tokens; many (16-byte accesses); many, rows not 16-byte aligned
 @pytest.mark.parametrize("H,KV,hd,page", [(6, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (32, 8, 64, 16), (2, 1, 256, 16)])
-def test_rope_kv_write(dt, H, KV, hd, page, T):
+def test_rope_kv_write(dt, H, KV, hd, page, T, pad):
     g = torch.Generator().manual_seed(hd)
     cfg = {"head_dim": hd, "hidden_size": H * hd, "num_attention_heads": H, "rope_theta": 500000.0,
            "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
@@ -250,7 +250,9 @@ def test_rope_kv_write(dt, H, KV, hd, page, T):
     slots[4] = -1                                                       # this token writes nothing
     kc = torch.full((pages, KV, page, hd), 7.0).to(dt)
     vc = torch.full((pages, KV, page, hd), 7.0).to(dt)
-    d_qkv, d_kc, d_vc = qkv.to(DEV), kc.to(DEV), vc.to(DEV)
+    d_kc, d_vc = kc.to(DEV), vc.to(DEV)
+    d_qkv = torch.zeros(T, qkv.shape[1] + pad, dtype=dt, device=DEV)[:, :qkv.shape[1]]
+    d_qkv.copy_(qkv)
     q, k, v = d_qkv[:, :H * hd], d_qkv[:, H * hd:(H + KV) * hd], d_qkv[:, (H + KV) * hd:]
     K().rope_kv_write(q, k, v, torch.tensor(positions, dtype=torch.int32, device=DEV), slots.to(DEV), inv.to(DEV),
                       d_kc, d_vc, H, KV, hd)

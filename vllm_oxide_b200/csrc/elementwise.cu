@@ -387,6 +387,84 @@ rope_kv_write_token_kernel(T* __restrict__ q, long long q_stride, T* __restrict_
     }
 }
 
+// The same with 16-byte accesses: the token's sines and cosines go to shared memory once, then
+// every thread rotates 16 bytes of the first half of a head against the 16 bytes of the second
+// half that pair with them (8 bfloat16 or 4 float32 pairs per step). Needs 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kv_write_token_vec_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+                               const T* __restrict__ v, long long v_stride, const int* __restrict__ positions,
+                               const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
+                               T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
+    constexpr int E = 16 / sizeof(T);              // elements per 16 bytes
+    pdl_launch_dependents();
+    pdl_wait(4);
+    extern __shared__ float s_cs[];                // [half] cosines, [half] sines
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    float* sc = s_cs;
+    float* ss = s_cs + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float c = 1.f, s = 0.f;
+        if (inv_freq) {
+            float theta = (float)positions[t] * inv_freq[i];
+            c = cosf(theta);
+            s = sinf(theta);
+        }
+        sc[i] = c;
+        ss[i] = s;
+    }
+    __syncthreads();
+    const int chunks = half / E;                   // 16-byte pieces per half head
+    auto rotate = [&](const uint4& ua, const uint4& ub, int i0, uint4& ra, uint4& rb) {
+        const T* a = reinterpret_cast<const T*>(&ua);
+        const T* b = reinterpret_cast<const T*>(&ub);
+        T* oa = reinterpret_cast<T*>(&ra);
+        T* ob = reinterpret_cast<T*>(&rb);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float x = ld_f(a + e), y = ld_f(b + e), c = sc[i0 + e], s = ss[i0 + e];
+            st_f(oa + e, x * c - y * s);
+            st_f(ob + e, y * c + x * s);
+        }
+    };
+    if (inv_freq) {
+        T* qr = q + (size_t)t * q_stride;
+        for (int u = threadIdx.x; u < H * chunks; u += blockDim.x) {
+            const int head = u / chunks, ch = u - head * chunks;
+            uint4* pa = reinterpret_cast<uint4*>(qr + (size_t)head * hd + ch * E);
+            uint4* pb = reinterpret_cast<uint4*>(qr + (size_t)head * hd + half + ch * E);
+            uint4 ra, rb;
+            rotate(*pa, *pb, ch * E, ra, rb);
+            *pa = ra;
+            *pb = rb;
+        }
+    }
+    if (!k) return;
+    const int slot = slots ? slots[t] : -1;
+    const size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0;
+    const int off = slot >= 0 ? slot % page_size : 0;
+    for (int u = threadIdx.x; u < KV * chunks; u += blockDim.x) {
+        const int kh = u / chunks, ch = u - kh * chunks;
+        uint4* pa = reinterpret_cast<uint4*>(k + (size_t)t * k_stride + (size_t)kh * hd + ch * E);
+        uint4* pb = reinterpret_cast<uint4*>(k + (size_t)t * k_stride + (size_t)kh * hd + half + ch * E);
+        uint4 ra = *pa, rb = *pb;
+        if (inv_freq) {
+            rotate(*pa, *pb, ch * E, ra, rb);
+            *pa = ra;
+            *pb = rb;
+        }
+        if (slot >= 0) {
+            const size_t base = ((page * KV + kh) * page_size + off) * (size_t)hd;
+            const T* vr = v + (size_t)t * v_stride + (size_t)kh * hd;
+            *reinterpret_cast<uint4*>(kcache + base + ch * E) = ra;
+            *reinterpret_cast<uint4*>(kcache + base + half + ch * E) = rb;
+            *reinterpret_cast<uint4*>(vcache + base + ch * E) = *reinterpret_cast<const uint4*>(vr + ch * E);
+            *reinterpret_cast<uint4*>(vcache + base + half + ch * E) = *reinterpret_cast<const uint4*>(vr + half + ch * E);
+        }
+    }
+}
+
 VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long k_stride, const void* v,
                                  long long v_stride, const int* positions, const int* slots,
                                  const float* inv_freq, void* kcache, void* vcache, int code, int T, int H,
@@ -394,6 +472,15 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
     if (T <= 0) return 0;
     if (hd <= 0 || (hd & 1) || H <= 0 || KV < 0 || page_size <= 0) return VOB_ERR_BAD_ARG;
     if (k && slots && (!kcache || !vcache || !v)) return VOB_ERR_BAD_ARG;
+    const int esz = code == VOB_BF16 ? 2 : 4;
+    auto aligned = [&](const void* p, long long stride) { return !p || (((uintptr_t)p & 15) == 0 && (stride * esz) % 16 == 0); };
+    if (T >= 64 && (hd / 2) % (16 / esz) == 0 && aligned(q, q_stride) && aligned(k, k_stride) && aligned(v, v_stride) &&
+        aligned(kcache, hd) && aligned(vcache, hd)) {
+        // many tokens, 16-byte aligned rows: a block per token, sines and cosines once per token
+        VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_token_vec_kernel<ElemT>, dim3(T), dim3(128), (size_t)hd * sizeof(float),
+            stream, (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
+            (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
+    }
     if (T >= 64 && hd / 2 <= 128) {
         // many tokens: a block per token, sines and cosines shared across heads
         VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_token_kernel<ElemT>, dim3(T), dim3(128), 0, stream,

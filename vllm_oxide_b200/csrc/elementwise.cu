@@ -387,80 +387,94 @@ rope_kv_write_token_kernel(T* __restrict__ q, long long q_stride, T* __restrict_
     }
 }
 
-// The same with 16-byte accesses: the token's sines and cosines go to shared memory once, then
-// every thread rotates 16 bytes of the first half of a head against the 16 bytes of the second
-// half that pair with them (8 bfloat16 or 4 float32 pairs per step). Needs 16-byte aligned rows.
+// The same with 16-byte accesses, ROPE_TOK tokens per block: the tokens' sines and cosines go to
+// shared memory once, then every thread takes 16-byte pieces of heads: it first loads all of its
+// pieces (the first half of a head and the half that pairs with it), then rotates and stores
+// them, so that a block has its whole traffic in flight at once. Needs 16-byte aligned rows.
+constexpr int ROPE_TOK = 4;
+constexpr int ROPE_THREADS = 256;
+constexpr int ROPE_MAX_UNITS = 4;                  // pieces per thread handled in one go
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_write_token_vec_kernel(T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
                                const T* __restrict__ v, long long v_stride, const int* __restrict__ positions,
                                const int* __restrict__ slots, const float* __restrict__ inv_freq, T* __restrict__ kcache,
-                               T* __restrict__ vcache, int H, int KV, int hd, int page_size) {
+                               T* __restrict__ vcache, int T_, int H, int KV, int hd, int page_size) {
     constexpr int E = 16 / sizeof(T);              // elements per 16 bytes
     pdl_launch_dependents();
     pdl_wait(4);
-    extern __shared__ float s_cs[];                // [half] cosines, [half] sines
-    const int t = blockIdx.x;
+    extern __shared__ float s_cs[];                // [ROPE_TOK][half] cosines, then as many sines
+    const int t0 = blockIdx.x * ROPE_TOK;
+    const int ntok = min(ROPE_TOK, T_ - t0);
     const int half = hd >> 1;
     float* sc = s_cs;
-    float* ss = s_cs + half;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float* ss = s_cs + ROPE_TOK * half;
+    for (int u = threadIdx.x; u < ntok * half; u += ROPE_THREADS) {
+        const int tt = u / half, i = u - tt * half;
         float c = 1.f, s = 0.f;
         if (inv_freq) {
-            float theta = (float)positions[t] * inv_freq[i];
+            float theta = (float)positions[t0 + tt] * inv_freq[i];
             c = cosf(theta);
             s = sinf(theta);
         }
-        sc[i] = c;
-        ss[i] = s;
+        sc[u] = c;
+        ss[u] = s;
     }
     __syncthreads();
     const int chunks = half / E;                   // 16-byte pieces per half head
-    auto rotate = [&](const uint4& ua, const uint4& ub, int i0, uint4& ra, uint4& rb) {
-        const T* a = reinterpret_cast<const T*>(&ua);
-        const T* b = reinterpret_cast<const T*>(&ub);
-        T* oa = reinterpret_cast<T*>(&ra);
-        T* ob = reinterpret_cast<T*>(&rb);
+    const int heads = H + (k ? KV : 0);            // q heads, then k heads
+    const int per_tok = heads * chunks;
+    const int total = ntok * per_tok;
+    for (int base = 0; base < total; base += ROPE_THREADS * ROPE_MAX_UNITS) {
+        uint4 ua[ROPE_MAX_UNITS], ub[ROPE_MAX_UNITS];
+        T* pa[ROPE_MAX_UNITS];
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float x = ld_f(a + e), y = ld_f(b + e), c = sc[i0 + e], s = ss[i0 + e];
-            st_f(oa + e, x * c - y * s);
-            st_f(ob + e, y * c + x * s);
+        for (int j = 0; j < ROPE_MAX_UNITS; ++j) {
+            const int u = base + j * ROPE_THREADS + threadIdx.x;
+            pa[j] = nullptr;
+            if (u < total) {
+                const int tt = u / per_tok, r = u - tt * per_tok, head = r / chunks, ch = r - head * chunks;
+                pa[j] = head < H ? q + (size_t)(t0 + tt) * q_stride + (size_t)head * hd + ch * E
+                                 : k + (size_t)(t0 + tt) * k_stride + (size_t)(head - H) * hd + ch * E;
+                ua[j] = *reinterpret_cast<const uint4*>(pa[j]);
+                ub[j] = *reinterpret_cast<const uint4*>(pa[j] + half);
+            }
         }
-    };
-    if (inv_freq) {
-        T* qr = q + (size_t)t * q_stride;
-        for (int u = threadIdx.x; u < H * chunks; u += blockDim.x) {
-            const int head = u / chunks, ch = u - head * chunks;
-            uint4* pa = reinterpret_cast<uint4*>(qr + (size_t)head * hd + ch * E);
-            uint4* pb = reinterpret_cast<uint4*>(qr + (size_t)head * hd + half + ch * E);
-            uint4 ra, rb;
-            rotate(*pa, *pb, ch * E, ra, rb);
-            *pa = ra;
-            *pb = rb;
-        }
-    }
-    if (!k) return;
-    const int slot = slots ? slots[t] : -1;
-    const size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0;
-    const int off = slot >= 0 ? slot % page_size : 0;
-    for (int u = threadIdx.x; u < KV * chunks; u += blockDim.x) {
-        const int kh = u / chunks, ch = u - kh * chunks;
-        uint4* pa = reinterpret_cast<uint4*>(k + (size_t)t * k_stride + (size_t)kh * hd + ch * E);
-        uint4* pb = reinterpret_cast<uint4*>(k + (size_t)t * k_stride + (size_t)kh * hd + half + ch * E);
-        uint4 ra = *pa, rb = *pb;
-        if (inv_freq) {
-            rotate(*pa, *pb, ch * E, ra, rb);
-            *pa = ra;
-            *pb = rb;
-        }
-        if (slot >= 0) {
-            const size_t base = ((page * KV + kh) * page_size + off) * (size_t)hd;
-            const T* vr = v + (size_t)t * v_stride + (size_t)kh * hd;
-            *reinterpret_cast<uint4*>(kcache + base + ch * E) = ra;
-            *reinterpret_cast<uint4*>(kcache + base + half + ch * E) = rb;
-            *reinterpret_cast<uint4*>(vcache + base + ch * E) = *reinterpret_cast<const uint4*>(vr + ch * E);
-            *reinterpret_cast<uint4*>(vcache + base + half + ch * E) = *reinterpret_cast<const uint4*>(vr + half + ch * E);
+#pragma unroll
+        for (int j = 0; j < ROPE_MAX_UNITS; ++j) {
+            const int u = base + j * ROPE_THREADS + threadIdx.x;
+            if (u >= total) continue;
+            const int tt = u / per_tok, r = u - tt * per_tok, head = r / chunks, ch = r - head * chunks;
+            uint4 ra = ua[j], rb = ub[j];
+            if (inv_freq) {
+                const T* a = reinterpret_cast<const T*>(&ua[j]);
+                const T* b = reinterpret_cast<const T*>(&ub[j]);
+                T* oa = reinterpret_cast<T*>(&ra);
+                T* ob = reinterpret_cast<T*>(&rb);
+                const float* c = sc + tt * half + ch * E;
+                const float* sn = ss + tt * half + ch * E;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const float x = ld_f(a + e), y = ld_f(b + e);
+                    st_f(oa + e, x * c[e] - y * sn[e]);
+                    st_f(ob + e, y * c[e] + x * sn[e]);
+                }
+                *reinterpret_cast<uint4*>(pa[j]) = ra;
+                *reinterpret_cast<uint4*>(pa[j] + half) = rb;
+            }
+            if (head >= H) {
+                const int kh = head - H;
+                const int slot = slots ? slots[t0 + tt] : -1;
+                if (slot >= 0) {
+                    const size_t cb = ((((size_t)(slot / page_size)) * KV + kh) * page_size + slot % page_size) * (size_t)hd;
+                    const T* vr = v + (size_t)(t0 + tt) * v_stride + (size_t)kh * hd;
+                    *reinterpret_cast<uint4*>(kcache + cb + ch * E) = ra;
+                    *reinterpret_cast<uint4*>(kcache + cb + half + ch * E) = rb;
+                    *reinterpret_cast<uint4*>(vcache + cb + ch * E) = *reinterpret_cast<const uint4*>(vr + ch * E);
+                    *reinterpret_cast<uint4*>(vcache + cb + half + ch * E) = *reinterpret_cast<const uint4*>(vr + half + ch * E);
+                }
+            }
         }
     }
 }
@@ -476,10 +490,10 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
     auto aligned = [&](const void* p, long long stride) { return !p || (((uintptr_t)p & 15) == 0 && (stride * esz) % 16 == 0); };
     if (T >= 64 && (hd / 2) % (16 / esz) == 0 && aligned(q, q_stride) && aligned(k, k_stride) && aligned(v, v_stride) &&
         aligned(kcache, hd) && aligned(vcache, hd)) {
-        // many tokens, 16-byte aligned rows: a block per token, sines and cosines once per token
-        VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_token_vec_kernel<ElemT>, dim3(T), dim3(128), (size_t)hd * sizeof(float),
-            stream, (ElemT*)q, q_stride, (ElemT*)k, k_stride, (const ElemT*)v, v_stride, positions, slots, inv_freq,
-            (ElemT*)kcache, (ElemT*)vcache, H, KV, hd, page_size));
+        // many tokens, 16-byte aligned rows: sines and cosines once per token, 16-byte accesses
+        VOB_DISPATCH_ELEM(code, return vob_launch(rope_kv_write_token_vec_kernel<ElemT>, dim3((T + ROPE_TOK - 1) / ROPE_TOK),
+            dim3(ROPE_THREADS), (size_t)ROPE_TOK * hd * sizeof(float), stream, (ElemT*)q, q_stride, (ElemT*)k, k_stride,
+            (const ElemT*)v, v_stride, positions, slots, inv_freq, (ElemT*)kcache, (ElemT*)vcache, T, H, KV, hd, page_size));
     }
     if (T >= 64 && hd / 2 <= 128) {
         // many tokens: a block per token, sines and cosines shared across heads

@@ -360,7 +360,8 @@ def test_attn_prefill_mma(H, KV, hd, page, window):
         r += n
 
 
-@pytest.mark.parametrize("H,KV,hd,page", [(8, 2, 64, 16), (3, 3, 64, 8), (16, 2, 64, 32), (32, 8, 64, 64), (2, 1, 64, 128)])
+@pytest.mark.parametrize("H,KV,hd,page", [(8, 2, 64, 16), (3, 3, 64, 8), (16, 2, 64, 32), (32, 8, 64, 64), (2, 1, 64, 128),
+                                          (6, 2, 64, 16), (5, 1, 64, 8), (4, 2, 128, 16), (24, 8, 128, 32), (8, 8, 128, 128), (7, 1, 128, 8)])
 def test_attn_prefill_sm100(H, KV, hd, page):
     """The tcgen05 kernel for prompt portions: portions that start mid-page, at a page edge, at
     zero; single tokens beside them; more than one row tile and more than one key tile; one key far
@@ -405,14 +406,15 @@ def test_attn_prefill_sm100_far_key_and_refusals():
         assert rel(out[r:r + n], want) <= 2 ** -6, (s, c, n)
         r += n
     k.gemm_sm100_check()
-    assert not k.attn_prefill_sm100_supported(6, 2, 64, 16, 64)      # 3 heads per kv head: no power of two
-    assert not k.attn_prefill_sm100_supported(4, 2, 128, 16, 64) and not k.attn_prefill_sm100_supported(4, 2, 64, 24, 64)
+    assert k.attn_prefill_sm100_supported(6, 2, 64, 16, 64) and k.attn_prefill_sm100_supported(4, 2, 128, 16, 64)
+    assert not k.attn_prefill_sm100_supported(4, 2, 48, 16, 64) and not k.attn_prefill_sm100_supported(4, 2, 64, 24, 64)
+    assert not k.attn_prefill_sm100_supported(4, 2, 64, 4, 64) and not k.attn_prefill_sm100_supported(258, 2, 64, 16, 64)
     assert not k.attn_prefill_sm100_supported(4, 2, 64, 16, 1 << 20)  # the page list would not fit shared memory
-    q = torch.zeros(1, 6 * 64, dtype=torch.bfloat16, device=DEV)
-    kc6 = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16, device=DEV)
+    q = torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV)
+    kc6 = torch.zeros(2, 2, 16, 48, dtype=torch.bfloat16, device=DEV)
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
     with pytest.raises(ShapeError, match="not supported"):
-        k.attn_prefill_sm100(q, q.clone(), kc6, kc6, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 6, 2, 64, 1.0)
+        k.attn_prefill_sm100(q, q.clone(), kc6, kc6, torch.zeros(1, 2, dtype=torch.int32, device=DEV), z, z, 1, 1, 4, 2, 48, 1.0)
 
 
 @pytest.mark.parametrize("splits", [1, 3, 8])

@@ -1,5 +1,5 @@
 // Attention for portions of prompts on the 5th-generation tensor cores (bfloat16 engine, head
-// size 64): causal grouped-query attention over the paged cache.
+// size 64 or 128): causal grouped-query attention over the paged cache.
 //
 // Math (as csrc/attention.cu; reference crates/engine/src/backend/cpu/attention.rs:76-128):
 //   s_j = (q . K_j) * scale over keys 0..p, softmax in float32 with a running maximum,
@@ -41,8 +41,13 @@
 // wait is bounded (see sm100.cuh); on expiry the block raises the error flag, frees its tensor
 // memory and returns.
 //
-// Takes head_dim 64, G a power of two up to 128, page sizes 8..128 (powers of two), no window.
-// The launcher refuses anything else and the caller uses another kernel.
+// Head size 128 is the same kernel with every operand tile in two 64-wide halves (two TMA boxes,
+// twice the products per tile), O in 128 columns of tensor memory, Q read from shared memory (no
+// room for it in tensor memory) and a ring of two K and two V tiles freed separately. A group
+// size G that does not divide 128 leaves the last 128 mod G rows of a block unused.
+//
+// Takes head_dim 64 or 128, any G up to 128, page sizes 8..128 (powers of two), no window. The
+// launcher refuses anything else and the caller uses another kernel.
 #include "common.cuh"
 VOB_PDL_SWITCH(attention_sm100)
 #include "sm100.cuh"
@@ -55,7 +60,10 @@ using namespace vob_sm100;
 constexpr int BM = 128;            // rows (token, head) per block
 constexpr int BN = 64;             // keys per tile
 constexpr int NTHREADS = 192;
-constexpr int ST = 4;              // K tiles and V tiles in flight
+// K and V tiles in flight: four of 8 KB each at head size 64, two of 16 KB at 128 (two blocks per SM either way)
+template <int HD> __host__ __device__ constexpr int stages() { return HD == 64 ? 4 : 2; }
+constexpr int HALF_Q = BM * 128;   // bytes of a 64-wide half of the Q tile
+constexpr int HALF_KV = BN * 128;  // bytes of a 64-wide half of a K or V tile
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -73,7 +81,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD> __host__ __device__ constexpr size_t tile_bytes() { return (size_t)BN * HD * 2; }
-template <int HD> constexpr size_t fixed_smem() { return 1024 + (size_t)BM * HD * 2 + 2 * ST * tile_bytes<HD>() + 256; }
+template <int HD> constexpr size_t fixed_smem() { return 1024 + (size_t)BM * HD * 2 + 2 * stages<HD>() * tile_bytes<HD>() + 256; }
 
 template <int HD>
 __global__ void __launch_bounds__(NTHREADS, 2)
@@ -82,7 +90,11 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                           const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                           const int* __restrict__ context_lens, int H, int KV, int page_shift, int num_pages,
                           float scale_log2, int* __restrict__ err_flag) {
-    static_assert(HD == 64, "one 128-byte swizzle span per row");
+    static_assert(HD == 64 || HD == 128, "rows of one or two 128-byte swizzle spans");
+    constexpr int ST = stages<HD>();
+    constexpr int NH = HD / 64;                    // 64-wide halves of the head dimension, each a tile of 128-byte rows
+    constexpr bool Q_TMEM = HD == 64;              // Q as the A operand from tensor memory (there is room at head size 64)
+    constexpr bool SPLIT_FREE = HD == 128;         // K stages are freed by Q K^T, V stages by P V (a ring of two needs that)
     pdl_launch_dependents();
     // The step's metadata was copied before the first kernel of the step started: readable now.
     const int G = H / KV;
@@ -92,7 +104,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const int kvh = blockIdx.x, seq = blockIdx.y;
     const int row0 = seq_starts[seq];
     const int total_rows = (seq_starts[seq + 1] - row0) * G;
-    const int tile_row0 = (gridDim.z - 1 - blockIdx.z) * BM;
+    const int tile_rows = (BM / G) * G;            // whole tokens only: BM when G divides it
+    const int tile_row0 = (gridDim.z - 1 - blockIdx.z) * tile_rows;
     if (tile_row0 >= total_rows) return;
     const int ctx = context_lens[seq];
 
@@ -105,8 +118,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     uint64_t* q_full = bars;                 // [1]
     uint64_t* k_full = bars + 1;             // [ST]
     uint64_t* v_full = k_full + ST;          // [ST]
-    uint64_t* kv_free = v_full + ST;         // [ST] P V of the tile has completed: its K and V stage are free, O holds it
-    uint64_t* s_full = kv_free + ST;         // [2] S of a tile is complete (one barrier per S buffer)
+    uint64_t* kv_free = v_full + ST;         // [ST] P V of the tile has completed: its V (and K) stage is free, O holds it
+    uint64_t* k_free = kv_free + ST;         // [ST] Q K^T of the tile has completed (used when K stages are freed on their own)
+    uint64_t* s_full = k_free + ST;          // [2] S of a tile is complete (one barrier per S buffer)
     uint64_t* p_ready = s_full + 2;          // [2] 128 rows have read S and written P over it
     uint64_t* q_ready = p_ready + 2;         // [1] Q has been copied to tensor memory
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(q_ready + 1);
@@ -114,17 +128,18 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     int* s_pages = reinterpret_cast<int*>(bars) + 64;         // [page_end], behind 256 bytes of barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int last_rr = min(tile_row0 + BM, total_rows) - 1;
+    const int last_rr = min(tile_row0 + tile_rows, total_rows) - 1;
     const int hi = ctx + last_rr / G + 1;                     // keys any row of the block reads: [0, hi)
     const int first_tok_pos = ctx + tile_row0 / G;
     const int n_tiles = (hi + BN - 1) / BN;
     const int page_end = ((hi - 1) >> page_shift) + 1;
-    constexpr int TMEM_COLS = 256;                            // S0 64 | S1 64 | O 64 | Q 32 (P lies over the first half of its S)
+    constexpr int TMEM_COLS = 256;                            // S0 64 | S1 64 | O HD | Q 32 at head size 64 (P lies over the first half of its S)
     constexpr uint32_t COL_O = 2 * BN, COL_Q = 2 * BN + HD;
+    static_assert(COL_O + HD + (Q_TMEM ? HD / 2 : 0) <= TMEM_COLS, "tensor memory layout");
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < ST; ++s) { mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(kv_free + s, 1); }
+        for (int s = 0; s < ST; ++s) { mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(kv_free + s, 1); mbar_init(k_free + s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(s_full + b, 1); mbar_init(p_ready + b, 128); }
         mbar_init(q_ready, 128);
         *abort_flag = 0;
@@ -150,10 +165,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const int page_size = 1 << page_shift;
         const int box_rows = min(page_size, BN);
         const int ppt = BN / box_rows;                        // boxes per tile
-        const uint32_t box_bytes = (uint32_t)box_rows * HD * 2;
+        const uint32_t box_bytes = (uint32_t)box_rows * 128;  // one 64-wide half of the box
         if (lane == 0) {
-            mbar_expect_tx(q_full, BM * HD * 2);
-            tma_load_3d(sQ, &map_q, 0, kvh * G, row0 + tile_row0 / G, q_full);
+            mbar_expect_tx(q_full, (uint32_t)tile_rows * 128 * NH);
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+                tma_load_3d(sQ + h * HALF_Q, &map_q, h * 64, kvh * G, row0 + tile_row0 / G, q_full);
         }
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j % ST;
@@ -164,24 +181,38 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             const int y = key0 & (page_size - 1);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(kv_free + s, ph ^ 1, abort_flag, err_flag, 11) ? 1 : 0;
+                ok = mbar_wait(SPLIT_FREE ? k_free + s : kv_free + s, ph ^ 1, abort_flag, err_flag, 11) ? 1 : 0;
                 if (ok) {
                     mbar_expect_tx(k_full + s, tile_bytes<HD>());
-                    mbar_expect_tx(v_full + s, tile_bytes<HD>());
+                    if (!SPLIT_FREE) mbar_expect_tx(v_full + s, tile_bytes<HD>());
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             if (lane < ppt) {
-                tma_load_4d(sK + s * tile_bytes<HD>() + lane * box_bytes, &map_k, 0, y, kvh, phys, k_full + s);
-                tma_load_4d(sV + s * tile_bytes<HD>() + lane * box_bytes, &map_v, 0, y, kvh, phys, v_full + s);
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+                    tma_load_4d(sK + s * tile_bytes<HD>() + h * HALF_KV + lane * box_bytes, &map_k, h * 64, y, kvh, phys, k_full + s);
+            }
+            if (SPLIT_FREE) {
+                if (lane == 0) {
+                    ok = mbar_wait(kv_free + s, ph ^ 1, abort_flag, err_flag, 12) ? 1 : 0;
+                    if (ok) mbar_expect_tx(v_full + s, tile_bytes<HD>());
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            }
+            if (lane < ppt) {
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+                    tma_load_4d(sV + s * tile_bytes<HD>() + h * HALF_KV + lane * box_bytes, &map_v, h * 64, y, kvh, phys, v_full + s);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
-            constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, HD, true);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, 64, true);          // one 64-wide half of O at a time
             const uint32_t tO = tmem_base + COL_O;
             const uint32_t tQ = tmem_base + COL_Q;
             // S[j & 1] = Q K_j^T; tcgen05.mma of one thread run in issue order, so a product may be
@@ -190,14 +221,22 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 const int s = j % ST;
                 if (!mbar_wait(k_full + s, (j / ST) & 1, abort_flag, err_flag, 14)) return false;
                 tcgen05_fence_after();
-                const uint64_t kdesc = umma_desc_sw128(sK + s * tile_bytes<HD>());
                 const uint32_t tS = tmem_base + (uint32_t)(j & 1) * BN;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) umma_bf16_ts(tS, tQ + 8 * k, kdesc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                for (int h = 0; h < NH; ++h) {
+                    const uint64_t kdesc = umma_desc_sw128(sK + s * tile_bytes<HD>() + h * HALF_KV);
+                    const uint64_t qdesc = umma_desc_sw128(sQ + h * HALF_Q);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (Q_TMEM) umma_bf16_ts(tS, tQ + 8 * k, kdesc + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                        else umma_bf16(tS, qdesc + 2 * k, kdesc + 2 * k, idesc_qk, (h > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                if (SPLIT_FREE) umma_commit(k_free + s);
                 umma_commit(s_full + (j & 1));
                 return true;
             };
-            bool ok = mbar_wait(q_ready, 0, abort_flag, err_flag, 13);
+            bool ok = mbar_wait(Q_TMEM ? q_ready : q_full, 0, abort_flag, err_flag, 13);
             if (ok) { tcgen05_fence_after(); ok = issue_qk(0); }
             if (ok && n_tiles > 1) ok = issue_qk(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
@@ -205,12 +244,15 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 if (!mbar_wait(p_ready + (j & 1), (j >> 1) & 1, abort_flag, err_flag, 15)) break;       // S read, P written
                 if (!mbar_wait(v_full + s, (j / ST) & 1, abort_flag, err_flag, 17)) break;
                 tcgen05_fence_after();
-                const uint64_t vdesc = umma_desc_sw128(sV + s * tile_bytes<HD>());
                 const uint32_t tP = tmem_base + (uint32_t)(j & 1) * BN;
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)          // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
-                    umma_bf16_ts(tO, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(kv_free + s);                   // K and V of the tile may be overwritten; O holds the tile
+                for (int h = 0; h < NH; ++h) {
+                    const uint64_t vdesc = umma_desc_sw128(sV + s * tile_bytes<HD>() + h * HALF_KV);
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k)      // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
+                        umma_bf16_ts(tO + h * 64, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(kv_free + s);                   // V (and K) of the tile may be overwritten; O holds the tile
                 if (j + 2 < n_tiles) ok = issue_qk(j + 2);
             }
         }
@@ -219,7 +261,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const int quad = warp & 3;
         const int r = quad * 32 + lane;                       // row of the tile = lane of tensor memory
         const int rr = tile_row0 + r;
-        const bool row_valid = rr < total_rows;
+        const bool row_valid = r < tile_rows && rr < total_rows;
         const int pos = row_valid ? ctx + rr / G : -1;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         float m_ref = -INFINITY, l = 0.f;
@@ -231,20 +273,22 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         // Q goes to tensor memory once: as the A operand of every Q K^T it is then read from there
         // and not from shared memory again (16 KB per tile of keys less for the tensor cores to
         // fetch). Row r of the swizzled tile: 16-byte chunk c lies at chunk position c ^ (r & 7).
-        if (wait_all(q_full, 0, 22)) {
-            uint32_t qv[32];
-            const uint4* qrow = reinterpret_cast<const uint4*>(sQ + (size_t)r * HD * 2);
+        if (Q_TMEM) {
+            if (wait_all(q_full, 0, 22)) {
+                uint32_t qv[32];
+                const uint4* qrow = reinterpret_cast<const uint4*>(sQ + (size_t)r * 128);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint4 x = qrow[c ^ (r & 7)];
-                qv[4 * c] = x.x; qv[4 * c + 1] = x.y; qv[4 * c + 2] = x.z; qv[4 * c + 3] = x.w;
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 x = qrow[c ^ (r & 7)];
+                    qv[4 * c] = x.x; qv[4 * c + 1] = x.y; qv[4 * c + 2] = x.z; qv[4 * c + 3] = x.w;
+                }
+                tmem_st32(lane_addr + COL_Q, qv);
+                tmem_wait_st();
+                tcgen05_fence_before();
+                mbar_arrive(q_ready);
+            } else {
+                ok = false;
             }
-            tmem_st32(lane_addr + COL_Q, qv);
-            tmem_wait_st();
-            tcgen05_fence_before();
-            mbar_arrive(q_ready);
-        } else {
-            ok = false;
         }
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int kbase = j * BN;
@@ -313,9 +357,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 const int s = j % ST;
                 if (!wait_all(v_full + s, (j / ST) & 1, 20)) { ok = false; break; }
                 if (kbase + r >= hi) {
-                    uint4* row = reinterpret_cast<uint4*>(sV + s * tile_bytes<HD>() + (size_t)r * HD * 2);
 #pragma unroll
-                    for (int i = 0; i < HD * 2 / 16; ++i) row[i] = make_uint4(0, 0, 0, 0);
+                    for (int h = 0; h < NH; ++h) {
+                        uint4* row = reinterpret_cast<uint4*>(sV + s * tile_bytes<HD>() + h * HALF_KV + (size_t)r * 128);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
+                    }
                     fence_proxy_async_smem();
                 }
                 __syncwarp();
@@ -389,9 +436,9 @@ inline int log2_exact(int v) {
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {
-    if (hd != 64 || KV <= 0 || H <= 0 || H % KV != 0) return false;
+    if ((hd != 64 && hd != 128) || KV <= 0 || H <= 0 || H % KV != 0) return false;
     int G = H / KV;
-    if (G > BM || log2_exact(G) < 0) return false;
+    if (G > BM) return false;
     if (page_size < 8 || page_size > 128 || log2_exact(page_size) < 0) return false;
     return true;
 }
@@ -400,7 +447,8 @@ bool sizes_ok(int H, int KV, int hd, int page_size) {
 
 VOB_EXPORT int vob_attn_prefill_sm100_supported(int H, int KV, int hd, int page_size, int max_pages) {
     if (!sizes_ok(H, KV, hd, page_size)) return 0;
-    return fixed_smem<64>() + (size_t)max_pages * sizeof(int) <= 110 * 1024 ? 1 : 0;       // two blocks per SM
+    const size_t fixed = hd == 64 ? fixed_smem<64>() : fixed_smem<128>();
+    return fixed + (size_t)max_pages * sizeof(int) <= 110 * 1024 ? 1 : 0;                  // two blocks per SM
 }
 
 // q [q_rows, H*hd] (row stride q_stride elements), out likewise; kcache / vcache [num_pages, KV,
@@ -434,17 +482,30 @@ VOB_EXPORT int vob_attn_prefill_sm100(const void* q, long long q_rows, long long
         e = make_map(&mv, vcache, 4, dims, strides, box);
         if (e) return e;
     }
+    const long long tok_per_tile = BM / G;
+    const long long row_tiles = ((long long)max_new + tok_per_tile - 1) / tok_per_tile;
+    if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
+    dim3 grid(KV, S, (unsigned)row_tiles);
+    if (hd == 64) {
+        static size_t configured = 0;
+        size_t smem = fixed_smem<64>() + (size_t)max_pages * sizeof(int);
+        if (smem > configured) {
+            cudaError_t e = cudaFuncSetAttribute(attn_prefill_sm100_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = smem;
+        }
+        return vob_launch(attn_prefill_sm100_kernel<64>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                          out_stride, block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size),
+                          (int)num_pages, scale * 1.4426950408889634f, err_flag);
+    }
     static size_t configured = 0;
-    size_t smem = fixed_smem<64>() + (size_t)max_pages * sizeof(int);
+    size_t smem = fixed_smem<128>() + (size_t)max_pages * sizeof(int);
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_sm100_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_sm100_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const long long row_tiles = ((long long)max_new * G + BM - 1) / BM;
-    if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
-    dim3 grid(KV, S, (unsigned)row_tiles);
-    return vob_launch(attn_prefill_sm100_kernel<64>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride,
-                      block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size), (int)num_pages,
-                      scale * 1.4426950408889634f, err_flag);
+    return vob_launch(attn_prefill_sm100_kernel<128>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                      out_stride, block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size),
+                      (int)num_pages, scale * 1.4426950408889634f, err_flag);
 }

@@ -761,7 +761,7 @@ def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: in
 def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
                        num_heads: int, num_kv_heads: int, head_dim: int, scale: float) -> None:
     """Attention for portions of prompts and mixed batches on the tcgen05 tensor cores (bfloat16,
-    head_dim 64, no window): Q, K and V tiles by TMA straight from the pages of the cache, scores
+    head_dim 64 or 128, no window): Q, K and V tiles by TMA straight from the pages of the cache, scores
     and output in tensor memory. Arguments as `attn_prefill_mma`."""
     op = "attn_prefill_sm100"
     if not scale > 0:
@@ -787,8 +787,8 @@ def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context
             raise ShapeError(op, f"{name} rows must be 16-byte aligned")
     if not attn_prefill_sm100_supported(num_heads, num_kv_heads, head_dim, kcache.shape[2], block_tables.shape[1]):
         raise ShapeError(op, f"sizes not supported: heads {num_heads}/{num_kv_heads}, head_dim {head_dim}, page "
-                             f"{kcache.shape[2]}, {block_tables.shape[1]} pages per request (head_dim 64, heads per kv head "
-                             "a power of two, page size a power of two from 8 to 128)")
+                             f"{kcache.shape[2]}, {block_tables.shape[1]} pages per request (head_dim 64 or 128, at most 128 "
+                             "heads per kv head, page size a power of two from 8 to 128)")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(context_lens, num_seqs, op, "context_lens")
     f = _fn("attention_sm100", "vob_attn_prefill_sm100",

@@ -634,3 +634,60 @@ def test_gemm_fused_residual_and_folded_norm(T, N, Kd, splits):
     out = torch.empty(T, N, device=DEV)
     k.gemm_fused(xn.to(DEV), w.to(DEV), out, EPI_STORE, N, ssq_in=ssq.to(DEV), eps=eps, splits=splits)
     assert rel(out, want_delta) <= max(2e-6, 2.0 ** -22 * math.sqrt(Kd)) * 4
+
+
+# ----------------------------------------------------------------------------- tcgen05 product on pairs of SMs
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32], ids=["bf16out", "f32out"])
+@pytest.mark.parametrize("T,N,Kd", [(1, 8, 64), (256, 256, 64), (300, 520, 264), (129, 1000, 1032), (700, 384, 96), (1030, 2048, 512)])
+def test_gemm_sm100_pair(T, N, Kd, odt):
+    """The two-SM product (tcgen05.mma.cta_group::2) against float64: rows and features that are no
+    multiple of a tile, K that is no multiple of 64, one tile and many, both output types."""
+    g = torch.Generator().manual_seed(T * 5 + N)
+    a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, N), 7.0, dtype=odt, device=DEV)
+    k = K()
+    k.gemm_sm100_pair(a, w, out)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    want = plain.linear(a.double().cpu(), w.double().cpu())
+    tol = (2.0 ** -8) if odt == torch.bfloat16 else max(2e-6, 2.0 ** -22 * math.sqrt(Kd))
+    assert rel(out, want) <= tol
+    out2 = torch.zeros_like(out)
+    k.gemm_sm100_pair(a, w, out2)                                # nothing needs resetting between launches
+    assert torch.equal(out2, out)
+    # a row's value does not depend on the rows beside it
+    if T > 2:
+        sub = torch.empty((2, N), dtype=odt, device=DEV)
+        k.gemm_sm100_pair(a[T - 2:].contiguous(), w, sub)
+        assert torch.equal(sub, out[T - 2:])
+
+
+def test_gemm_sm100_pair_narrow_output_rows():
+    """An output whose rows are not 16-byte aligned takes the element-wise store path."""
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(200, 128, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(100, 128, generator=g).to(torch.bfloat16).to(DEV)
+    wide = torch.full((200, 101), 7.0, dtype=torch.bfloat16, device=DEV)
+    k = K()
+    k.gemm_sm100_pair(a, w, wide[:, :100])
+    assert rel(wide[:, :100], plain.linear(a.double().cpu(), w.double().cpu())) <= 2 ** -8
+    assert float((wide[:, 100].float() - 7.0).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("T,I,Kd", [(1, 64, 64), (256, 128, 64), (300, 300, 264), (700, 224, 96), (1100, 1000, 256)])
+def test_gemm_pair_swiglu(T, I, Kd):
+    g = torch.Generator().manual_seed(T + I)
+    a = torch.randn(T, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, Kd, generator=g) / math.sqrt(Kd) * 2).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    k = K()
+    k.gemm_pair_swiglu(a, w, out)
+    torch.cuda.synchronize()
+    k.gemm_sm100_check()
+    gate = plain.linear(a.double().cpu(), w[:I].double().cpu())
+    up = plain.linear(a.double().cpu(), w[I:].double().cpu())
+    assert rel(out, plain.swiglu(gate, up)) <= 2 ** -8
+    out2 = torch.zeros_like(out)
+    k.gemm_pair_swiglu(a, w, out2)
+    assert torch.equal(out, out2)

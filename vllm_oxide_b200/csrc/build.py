@@ -31,7 +31,7 @@ if os.environ.get("VOB_TIMELINE") == "1":      # per-kernel timeline recording (
     _NVCC_FLAGS = _NVCC_FLAGS + ["-DVOB_TIMELINE"]
 _CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
-CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "attention_mma", "attention_sm100", "sampling", "gemm_sm100")
+CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "attention_mma", "attention_sm100", "sampling", "gemm_sm100", "gemm_sm100_pair")
 _lock = threading.Lock()
 _loaded: Dict[str, object] = {}
 

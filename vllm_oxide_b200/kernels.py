@@ -87,7 +87,7 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 
 _fn_cache = {}
-_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "attention", "attention_mma", "attention_sm100", "sampling")
+_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -160,7 +160,7 @@ def modules_for(dtype) -> tuple:
     first start."""
     if dtype == torch.float32:
         return ("elementwise", "gemm_f32", "attention", "sampling")
-    return ("elementwise", "gemm_sm100", "attention", "attention_mma", "attention_sm100", "sampling")
+    return ("elementwise", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling")
 
 
 def preload(modules=_MODULES) -> None:
@@ -419,12 +419,54 @@ def gemm_sm100(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Opti
              _ptr(sc.err), _stream()), op)
 
 
+@_timed
+def gemm_sm100_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[T, N] = a[T, K] @ w[N, K]^T for many rows, on pairs of SMs: tcgen05.mma with cta_group::2
+    (256 weight rows x 256 tokens per instruction, operands split over the two blocks' shared
+    memory), persistent over output tiles, accumulators double buffered in tensor memory. bfloat16
+    operands, bfloat16 or float32 out."""
+    op = "gemm_sm100_pair"
+    _cuda(op, a, w, out)
+    if not gemm_sm100_supported(a, w):
+        raise ShapeError(op, f"operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows, got "
+                             f"{a.dtype} {list(a.shape)} strides {list(a.stride())} and {w.dtype} {list(w.shape)}")
+    T, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N) or out.stride(1) != 1:
+        raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
+    f = _fn("gemm_sm100_pair", "vob_gemm_sm100_pair", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out, op), T, N, K,
+             _ptr(_scratch_for(a.device).err), _stream()), op)
+
+
+@_timed
+def gemm_pair_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16) for many rows:
+    the two-SM tcgen05 product whose epilogue applies the activation (gate and up never go to memory)."""
+    op = "gemm_pair_swiglu"
+    _cuda(op, a, w_gate_up, out)
+    if not gemm_sm100_supported(a, w_gate_up):
+        raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    T, K = a.shape
+    if w_gate_up.shape[0] % 2 != 0 or w_gate_up.shape[1] != K:
+        raise ShapeError(op, f"w_gate_up must be [2I, {K}], got {list(w_gate_up.shape)}")
+    I = w_gate_up.shape[0] // 2
+    if out.shape != (T, I) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ShapeError(op, f"out must be bfloat16 [{T}, {I}], got {out.dtype} {list(out.shape)}")
+    f = _fn("gemm_sm100_pair", "vob_gemm_sm100_pair_swiglu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w_gate_up), w_gate_up.stride(0), _ptr(out), out.stride(0), T, I, K,
+             _ptr(_scratch_for(a.device).err), _stream()), op)
+
+
 def _pick_splits(T: int, N: int, K: int, device) -> int:
     f = _fn("gemm_sm100", "vob_gemm_sm100_pick_splits", [_I, _I, _I, _I])
     return int(f(T, N, K, _scratch_for(device).num_sms))
 
 
 FUSED_GEMM_MAX_ROWS = 64      # what the fused kernels take
+PAIR_GEMM_FROM_ROWS = 1024    # from here the two-SM product with the SwiGLU epilogue beats the library product plus the activation kernel
 FUSED_GEMM_BEST_ROWS = 32     # up to here they beat the library product plus separate kernels (measured at 64 rows: 25 % slower)
 
 

@@ -47,6 +47,11 @@ class SwiGLU(FeedForward):
                 and kernels.gemm_sm100_supported(x, self.w_gate_up)):
             # few rows: one kernel, the activation applied in the product's epilogue
             kernels.gemm_swiglu(x, self.w_gate_up, act)
+        elif (self.dtype == torch.bfloat16 and T >= kernels.PAIR_GEMM_FROM_ROWS and self.fused
+                and kernels.gemm_sm100_supported(x, self.w_gate_up)):
+            # many rows: the two-SM product with the activation in its epilogue (gate and up never
+            # go to memory)
+            kernels.gemm_pair_swiglu(x, self.w_gate_up, act)
         else:
             gate_up = matmul(x, self.w_gate_up, ctx.alloc((T, 2 * self.inter)))
             kernels.swiglu(gate_up, act)

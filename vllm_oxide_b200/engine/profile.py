@@ -32,6 +32,8 @@ def profile_decode_step(runner, prompt, steps: int = 4):
 # ------------------------------------------------------------------------------------------------
 # Single kernels on synthetic operands, for profilers:
 #   python -m vllm_oxide_b200.engine.profile gemm --rows 8 --out 16384 --in 2048 [--copies 6] [--iters 3]
+#   python -m vllm_oxide_b200.engine.profile gemm_pair --rows 2048 --out 16384 --in 2048      (the two-SM product)
+#   python -m vllm_oxide_b200.engine.profile gemm_pair_swiglu --rows 2048 --out 16384 --in 2048
 #   python -m vllm_oxide_b200.engine.profile attn_decode --batch 8 --context 2200
 #   python -m vllm_oxide_b200.engine.profile attn_prefill --tokens 2048 [--impl sm100|mma]
 # Each launch works on operands of its own (several copies, together larger than L2), so that DRAM
@@ -42,7 +44,7 @@ def _kernel_cases(argv):
     import math
     import torch
     ap = argparse.ArgumentParser(prog="vllm_oxide_b200.engine.profile")
-    ap.add_argument("kernel", choices=["gemm", "attn_decode", "attn_prefill"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_pair", "gemm_pair_swiglu", "gemm_library", "attn_decode", "attn_prefill"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--out", type=int, default=16384)
     ap.add_argument("--in", dest="inner", type=int, default=2048)
@@ -55,18 +57,27 @@ def _kernel_cases(argv):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--copies", type=int, default=6)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="time the launches back to back, replayed from one CUDA graph")
     ap.add_argument("--impl", default="sm100", choices=["sm100", "mma"], help="attn_prefill: the tcgen05 or the mma.sync kernel")
     a = ap.parse_args(argv)
     dev = "cuda:0"
     bf = torch.bfloat16
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s: torch.randn(*s, generator=g, device=dev).to(bf)
-    if a.kernel == "gemm":
+    if a.kernel in ("gemm", "gemm_pair", "gemm_pair_swiglu", "gemm_library"):
         x = rnd(a.rows, a.inner)
         ws = [rnd(a.out, a.inner) for _ in range(a.copies)]
-        out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
-        launches = [lambda w=w: kernels.gemm_sm100(x, w, out) for w in ws]
-        nbytes = a.out * a.inner * 2 + a.rows * (a.inner + a.out) * 2
+        if a.kernel == "gemm_pair_swiglu":          # --out counts the rows of [Wg; Wu]
+            out = torch.empty(a.rows, a.out // 2, dtype=bf, device=dev)
+            launches = [lambda w=w: kernels.gemm_pair_swiglu(x, w, out) for w in ws]
+        else:
+            out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
+            if a.kernel == "gemm_library":           # the library product the engine uses above 32 rows, for comparison
+                launches = [lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]
+            else:
+                fn = kernels.gemm_sm100 if a.kernel == "gemm" else kernels.gemm_sm100_pair
+                launches = [lambda w=w: fn(x, w, out) for w in ws]
+        nbytes = a.out * a.inner * 2 + a.rows * a.inner * 2 + out.numel() * 2
         flops = 2.0 * a.rows * a.out * a.inner
     else:
         H, KV, hd, page = a.heads, a.kv_heads, a.head_dim, a.page
@@ -102,6 +113,27 @@ def _kernel_cases(argv):
     for f in launches:
         f()
     torch.cuda.synchronize()
+    if a.graph:
+        kernels.set_pdl(True)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(2):
+                for f in launches:
+                    f()
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(max(a.iters, 3)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / (2 * len(launches)))
+        us = sorted(times)[len(times) // 2]
+        print(f"{a.kernel}: {us:.1f} us per launch (events around a CUDA graph of {2 * len(launches)} launches back to back); "
+              f"{nbytes / us / 1e3:.0f} GB/s of the bytes it must read; {flops / us / 1e6:.1f} TFLOP/s")
+        return
     times = []
     for _ in range(a.iters):
         for f in launches:

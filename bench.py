@@ -2,13 +2,16 @@
 """Decode and prefill throughput of the engine at Llama 3.2 1B sizes with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+                    [--sizes 1b|3b|8b] [--prompt-len P] [--gen-len G] [--context C]
 
 A "step" is one decode step of `--batch` requests, each with a 2,048-token prompt already in the
 cache. `value` is decoded tokens per second timed on the device (CUDA events around K steps, each
 step uploading its own metadata and replaying the step's kernels); `e2e` is the same number
 through the Python entry point (`LLM.add_request` / `LLM.step`), host tokens in and out. The same
 line carries the 2,048-token prefill, the decode step's HBM roofline, and decode at batch 1 and 64.
-Prints ONE JSON line. One GPU only.
+Prints ONE JSON line. One GPU only. The defaults are the benchmark's configuration (Llama 3.2 1B
+sizes, batch 8, 2,048-token prompts, 256 generated); --sizes / --prompt-len / --gen-len / --context
+run the same measurements at the other layer sizes and context lengths.
 """
 from __future__ import annotations
 
@@ -26,6 +29,12 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Llama 3.2 1B)"
 PROMPT_LEN = 2048
 GEN_LEN = 256
+# Layer sizes of the three Llama models the reference's plan names (config.json values).
+SIZES = {
+    "1b": dict(name="llama-3.2-1b-sizes", layers=16, hidden=2048, heads=32, head_dim=64, inter=8192, rope_factor=32.0, tied=True),
+    "3b": dict(name="llama-3.2-3b-sizes", layers=28, hidden=3072, heads=24, head_dim=128, inter=8192, rope_factor=32.0, tied=True),
+    "8b": dict(name="llama-3.1-8b-sizes", layers=32, hidden=4096, heads=32, head_dim=128, inter=14336, rope_factor=8.0, tied=False),
+}
 
 
 def load_peaks():
@@ -97,13 +106,25 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sizes", default="1b", choices=sorted(SIZES), help="layer sizes (Llama 3.2 1B / 3.2 3B / 3.1 8B)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--gen-len", type=int, default=GEN_LEN)
+    ap.add_argument("--context", type=int, default=8192, help="max_model_len of the engine")
     a = ap.parse_args()
+    prompt_len, gen_len = a.prompt_len, a.gen_len
+    # requests that finish their prompt early decode while the others still prefill, and the timed
+    # steps come on top: no request may run out of tokens before the measurement ends
+    max_b_guard = max(a.batch, 1 if a.no_points else 64)
+    gen_len = max(gen_len, max_b_guard * prompt_len // 2048 + max(a.warmup, 3) + a.steps + 16)
     if a.impl == "reference":
         return reference_arm()
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    if prompt_len + gen_len + 16 > a.context:
+        print(f"bench.py: --context {a.context} is too short for prompts of {prompt_len} plus {gen_len} generated tokens")
+        return 2
 
     import torch
     from vllm_oxide_b200 import models  # noqa: F401
@@ -113,16 +134,18 @@ def main():
     from vllm_oxide_b200.weights import random_tensors
     from vllm_oxide_b200 import kernels
 
-    full_layers = 16
+    sz = SIZES[a.sizes]
+    full_layers = sz["layers"]
     layers = a.layers or full_layers
-    cfg = LlamaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=layers, num_attention_heads=32,
-                      num_key_value_heads=8, head_dim=64, vocab_size=128256, max_position_embeddings=131072,
-                      rms_norm_eps=1e-5, rope_theta=500000.0, rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192),
-                      tie_word_embeddings=True, bos_token_id=128000, eos_token_ids=(128001,))
-    context_len = 8192
+    cfg = LlamaConfig(hidden_size=sz["hidden"], intermediate_size=sz["inter"], num_hidden_layers=layers,
+                      num_attention_heads=sz["heads"], num_key_value_heads=8, head_dim=sz["head_dim"], vocab_size=128256,
+                      max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      rope_scaling=RopeScaling(sz["rope_factor"], 1.0, 4.0, 8192), tie_word_embeddings=sz["tied"],
+                      bos_token_id=128000, eos_token_ids=(128001,))
+    context_len = a.context
     max_b = 64 if not a.no_points else max(a.batch, 1)
     max_b = max(max_b, a.batch)
-    pages_per_req = -(-(PROMPT_LEN + GEN_LEN + 16) // 16)
+    pages_per_req = -(-(prompt_len + gen_len + 16) // 16)
     engine = EngineConfig(max_batch_tokens=2048, max_seqs=max_b, max_model_len=context_len, block_size=16,
                           num_pages=max_b * pages_per_req + 8, dtype="bfloat16", cuda_graphs=not a.no_graphs)
     dev = "cuda:0"
@@ -132,8 +155,9 @@ def main():
     llm = LLM(runner)
     peaks = load_peaks()
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(max_b)]
-    never_stop = SamplingParams(max_new_tokens=GEN_LEN, temperature=0.0, stop_token_ids=())
+    prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(max_b)]
+    never_stop = SamplingParams(max_new_tokens=gen_len, temperature=0.0, stop_token_ids=())
+    PREFILL = min(2048, prompt_len)          # the timed prefill is one step of this many tokens
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
@@ -142,8 +166,8 @@ def main():
     rt = runner.rt
     def prefill_once(rid):
         runner.admit(rid)
-        runner.manager.reserve(rid, PROMPT_LEN)
-        arrays = runner.build_arrays([rt.StepEntry(rid, prompts[0], [PROMPT_LEN - 1])])
+        runner.manager.reserve(rid, PREFILL)
+        arrays = runner.build_arrays([rt.StepEntry(rid, prompts[0][:PREFILL], [PREFILL - 1])])
         e0, e1 = ev(), ev()
         e0.record()
         runner.step(arrays)
@@ -158,15 +182,15 @@ def main():
     pre_ms = sorted(prefill_once(900100 + i) for i in range(5))[2]
     lin_params = layers * (cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size
                            + 3 * cfg.hidden_size * cfg.intermediate_size)
-    pre_flops = 2.0 * lin_params * PROMPT_LEN + layers * 2.0 * 2.0 * cfg.q_dim * PROMPT_LEN * (PROMPT_LEN + 1) / 2 \
+    pre_flops = 2.0 * lin_params * PREFILL + layers * 2.0 * 2.0 * cfg.q_dim * PREFILL * (PREFILL + 1) / 2 \
         + 2.0 * cfg.vocab_size * cfg.hidden_size
-    prefill = {"value": PROMPT_LEN / (pre_ms / 1e3), "tokens": PROMPT_LEN, "ms": pre_ms,
+    prefill = {"value": PREFILL / (pre_ms / 1e3), "tokens": PREFILL, "ms": pre_ms,
                "frac": pre_flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
 
     def prefill_all(ids):
         """Step until every request has its first token (none may finish on the way: GEN_LEN is
         far above the number of steps that takes)."""
-        for _ in range(4 * len(ids) + 16):
+        for _ in range(2 * (len(ids) * prompt_len // 2048 + len(ids)) + 32):
             if all(llm._generated.get(r, 0) >= 1 for r in ids):
                 return
             llm.step()
@@ -220,7 +244,7 @@ def main():
         for r in ids:
             llm.abort(r)
         return B * steps / dt
-    e2e_steps = min(a.steps, GEN_LEN - a.warmup - 2)
+    e2e_steps = max(1, min(a.steps, gen_len - a.warmup - 2))
     e2e_val = decode_e2e(a.batch, e2e_steps, a.warmup)
     e2e = {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": runner.last_upload_bytes,
            "d2h_bytes_per_step": 4 * a.batch}
@@ -233,13 +257,13 @@ def main():
     clocks = sampler.stop()
 
     out = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "metric": METRIC if a.sizes == "1b" else METRIC.replace("Llama 3.2 1B", sz["name"]), "value": value, "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), seeded uniform token ids",
-        "config": {"model": "llama-3.2-1b-sizes", "layers": layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
+        "config": {"model": sz["name"], "layers": layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": a.batch,
-                   "seq_len": context_len, "prompt_len": PROMPT_LEN, "generated": GEN_LEN, "page_size": 16,
+                   "seq_len": context_len, "prompt_len": prompt_len, "generated": gen_len, "page_size": 16,
                    "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights 2.5 GB per step)",
                    "cuda_graphs": bool(runner.graphs_enabled)},
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,

@@ -237,3 +237,22 @@ def test_running_ahead_changes_no_token_and_sees_stop_tokens(tmp_path_factory, d
     assert [o.token_ids for o in ahead.generate(prompts, free)] == full or dtype == "bfloat16"
     assert ahead.runner.manager.check_invariants() == ""
     assert ahead.runner.manager.num_free_pages(0) == ahead.runner.manager.num_pages(0)
+
+
+def test_generation_crosses_into_long_contexts(tmp_path_factory):
+    """A request grows past the length from which decode steps count as long-context ones: the
+    replayed graphs change kind on the way, and the tokens are those of steps launched one by one."""
+    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    cfg, _, page = TINY["DL"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "DL")
+    prompts = [random_tokens(LONG_CONTEXT_KEYS - 6, cfg.vocab_size, 41), random_tokens(40, cfg.vocab_size, 42)]
+    params = sp(max_new_tokens=16, stop_token_ids=())
+    kw = dict(max_model_len=LONG_CONTEXT_KEYS + 64, max_batch_tokens=2048, num_pages=(LONG_CONTEXT_KEYS + 256) // page + 8)
+    plain_steps = llm_for(d, "bfloat16", page, cuda_graphs=False, run_ahead=False, **kw)
+    want = plain_steps.generate(prompts, params)
+    graphs = llm_for(d, "bfloat16", page, cuda_graphs=True, run_ahead=True, **kw)
+    got = graphs.generate(prompts, params)
+    kinds = {key[2] for key in graphs.runner._graphs}
+    assert kinds == {False, True}, kinds
+    for g, w, p in zip(got, want, prompts):
+        assert_same_or_near_tie(d, p, g.token_ids, w.token_ids, params, TOL[torch.bfloat16])

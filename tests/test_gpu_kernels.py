@@ -439,6 +439,41 @@ def test_attn_decode_mma(H, KV, hd, page, window, splits):
     assert float(out[len(seqs)].float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("H,KV,hd,page,window,splits", [(8, 2, 64, 16, 0, 37), (6, 2, 128, 32, 0, 64), (4, 4, 64, 8, 300, 19),
+                                                        (8, 2, 64, 64, 0, 9)])
+def test_attn_decode_mma_merge_through_global_memory(H, KV, hd, page, window, splits):
+    """Up to 64 blocks per request without a cluster: long and short requests in one launch (a
+    short one uses one block and the others leave), a far key that decides the result, a padding
+    row; and a second launch on the same counters, which the first must have left at zero."""
+    dt = torch.bfloat16
+    seqs = [(5000, 1), (0, 1), (130, 1), (700, 1), (64 * splits * 2 - 1, 1)]
+    sk = (lambda L: max(L - 1 - window, 0)) if window else (lambda L: min(3, L - 1))
+    qrows, kc, vc, bt, row_seq, pos, qs, ks, vs = _paged_case(dt, H, KV, hd, page, seqs, seed=hd + H + page + splits, scale_key=sk)
+    qrows = torch.cat([qrows, torch.randn(1, H * hd).to(dt)])
+    pos = torch.cat([pos, torch.tensor([-1], dtype=torch.int32)])
+    bt = torch.cat([bt, bt[:1]])
+    k = K()
+    S = qrows.shape[0]
+    partials = torch.full((k.attn_decode_partial_floats(S, KV, hd, splits),), float("nan"), device=DEV)
+    arrived = torch.zeros(S * KV, dtype=torch.int32, device=DEV)
+    args = (kc.to(DEV), vc.to(DEV), bt.to(DEV), pos.to(DEV), H, KV, hd, 1.0 / math.sqrt(hd), window, splits, partials, arrived)
+    for _ in range(2):
+        out = torch.full_like(qrows, 7.0).to(DEV)
+        k.attn_decode_mma(qrows.to(DEV), out, *args)
+        for s, (c, n) in enumerate(seqs):
+            want = plain.causal_attention(qs[s].double(), ks[s].double(), vs[s].double(), H, KV, hd, window=window or None)[c:]
+            assert rel(out[s:s + 1], want) <= 2 ** -6, (s, c)
+        assert float(out[len(seqs)].float().abs().max()) == 0.0
+        assert int(arrived.abs().max()) == 0
+    from vllm_oxide_b200.errors import ShapeError
+    with pytest.raises(ShapeError, match="splits must be"):
+        k.attn_decode_mma(qrows.to(DEV), out, *args[:9], 65, partials, arrived)
+    with pytest.raises(ShapeError, match="splits must be"):
+        k.attn_decode_mma(qrows.to(DEV), out, *args[:9], 9)
+    with pytest.raises(ShapeError, match="partials must be"):
+        k.attn_decode_mma(qrows.to(DEV), out, *args[:10], partials[:100], arrived)
+
+
 def test_attn_mma_refusals():
     from vllm_oxide_b200.errors import ShapeError
     k = K()

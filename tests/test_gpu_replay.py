@@ -193,6 +193,35 @@ def test_four_ways_at_the_benchmark_layer_sizes(tmp_path_factory, dtype):
     print(f"1B sizes {dtype}: worst rel diff whole {w1:.2e} bulk+tail {w2:.2e} portions {w3:.2e} mixed {w4:.2e}")
 
 
+def test_long_context_beside_a_short_one(tmp_path_factory):
+    """Decode steps of a request of more than 6,144 keys beside a short one: the decode attention
+    then shares a request's keys over up to 64 blocks that merge through global memory, and the
+    short request uses only as many of them as it has keys for."""
+    dtype = torch.bfloat16
+    cfg, _, page = TINY["DL"]
+    model_dir = make_model_dir(tmp_path_factory.getbasetemp(), "DL")
+    reqs = _requests(cfg.vocab_size, [6300, 150], 900)
+    s = _session(model_dir, dtype, 6336 + 192, page)
+    steps, n = [], 0
+    long_toks, short_toks = reqs["r0"], reqs["r1"]
+    for lo in range(0, 6280, 2048):
+        hi = min(lo + 2048, 6280)
+        steps.append({"step": n, "entries": [{"id": "r0", "tokens": long_toks[lo:hi], "want": [hi - lo - 1]}], "end": []})
+        n += 1
+    steps.append({"step": n, "entries": [{"id": "r1", "tokens": short_toks[:130], "want": [129]}], "end": []})
+    n += 1
+    for i in range(20):
+        steps.append({"step": n, "entries": [{"id": "r0", "tokens": [long_toks[6280 + i]], "want": [0]},
+                                             {"id": "r1", "tokens": [short_toks[130 + i]], "want": [0]}],
+                      "end": ["r0", "r1"] if i == 19 else []})
+        n += 1
+    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    assert LONG_CONTEXT_KEYS < 6280
+    worst = check(run_trace(s, steps), model_dir, reqs, dtype, "long beside short")
+    assert s.runner.manager.num_free_pages(0) == s.runner.manager.num_pages(0)
+    print(f"long context: worst rel diff {worst:.2e}")
+
+
 def test_f32_cuts_agree_closely(tmp_path_factory):
     """In 32-bit, the same position computed whole, token by token and in portions agrees far
     inside the tolerance against the oracle: the reference's bound between two of its own paths

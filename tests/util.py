@@ -1,6 +1,7 @@
 """Shared helpers of the tests: the two tiny configurations, model folders, comparisons."""
 from __future__ import annotations
 
+import dataclasses
 import os
 import random
 
@@ -40,8 +41,11 @@ LAYERS_1B = LlamaConfig(
     head_dim=64, vocab_size=128256, max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
     rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192), tie_word_embeddings=True)
 
+# TINY_D for contexts of thousands of keys (the decode kernels choose by context length)
+TINY_D_LONG = dataclasses.replace(TINY_D, max_position_embeddings=16384)
+
 TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16),
-        "1B": (LAYERS_1B, 0.02, 16)}   # config, std, page size
+        "DL": (TINY_D_LONG, 0.05, 16), "1B": (LAYERS_1B, 0.02, 16)}   # config, std, page size
 
 
 def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:

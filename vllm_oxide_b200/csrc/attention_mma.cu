@@ -315,6 +315,60 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     }
 }
 
+constexpr int DEC_MIN_TILES = 2;
+constexpr int DEC_MAX_SPLITS_WIDE = 64;
+
+// The block of a request and kv head that arrives last adds the partials of all `splits` blocks
+// up (merge through global memory). Everything is fetched with independent loads: first every
+// partial's maxima and sums, from which each row's weights follow; then the values, a thread
+// taking four neighbouring dims over one half of the partials, in rank order. `scratch` is the
+// block's shared memory behind q; `out` points at the group's first head. Not inlined: the
+// kernel's main path keeps its registers.
+template <int HD>
+__device__ __noinline__ void merge_partials(const float* __restrict__ all, int splits, int G, float* scratch,
+                                            __nv_bfloat16* __restrict__ out) {
+    constexpr int PART = 16 * HD + 32;
+    float* ml = scratch;                                    // [splits][32]: 16 maxima, 16 sums
+    float* fk = ml + DEC_MAX_SPLITS_WIDE * 32;              // [splits][16]: weight of partial k in row r
+    float* hs = fk + DEC_MAX_SPLITS_WIDE * 16;              // [2][16 * HD]: the two halves' sums
+    float* Lrow = hs + 2 * 16 * HD;                         // [16]
+    static_assert(DEC_MAX_SPLITS_WIDE * 48 + 2 * 16 * HD + 16 <= 128 + 4 * 16 * HD + 16 * HD + 32, "merge scratch exceeds the combine area");
+    for (int i = threadIdx.x; i < splits * 32; i += NTHREADS) ml[i] = __ldcg(all + (size_t)(i >> 5) * PART + 16 * HD + (i & 31));
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int r = threadIdx.x;
+        float M = -INFINITY;
+        for (int k = 0; k < splits; ++k) M = fmaxf(M, ml[k * 32 + r]);
+        const float Ms = M == -INFINITY ? 0.f : M;
+        float L = 0.f;
+        for (int k = 0; k < splits; ++k) {
+            const float f = exp2f(ml[k * 32 + r] - Ms);
+            fk[k * 16 + r] = f;
+            L += f * ml[k * 32 + 16 + r];
+        }
+        Lrow[r] = L;
+    }
+    __syncthreads();
+    const int items = G * HD / 4, k_half = splits / 2;
+    for (int it = threadIdx.x; it < 2 * items; it += NTHREADS) {
+        const int second = it >= items, e = (it - second * items) * 4, r = e / HD;
+        const int k0 = second ? k_half : 0, k1 = second ? splits : k_half;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int k = k0; k < k1; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(all + (size_t)k * PART + e));
+            const float f = fk[k * 16 + r];
+            acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+        }
+        *reinterpret_cast<float4*>(hs + second * 16 * HD + e) = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * HD; e += NTHREADS) {
+        const float L = Lrow[e / HD];
+        out[e] = __float2bfloat16_rn(L > 0.f ? (hs[e] + hs[16 * HD + e]) / L : 0.f);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Steps of single decoded tokens. Grid (requests, kv heads, splits): a block reads its share of
 // the request's key tiles once for all G heads of the group; its 4 warps split every tile's 64
@@ -325,16 +379,26 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
 // memory in rank order (a fixed order, so the result does not depend on timing). K/V tiles go
 // through a cp.async ring of three stages (two when the grid is so large that the smaller
 // footprint lets one more block live on an SM). Bound: the K/V reads (memory).
+//
+// Few requests with long contexts would leave most SMs idle with 8 blocks each. For them the
+// grid has up to 64 splits and no cluster (`partials` is given): a request uses as many of its
+// blocks as it has tiles for (at least DEC_MIN_TILES each; the others leave at once), every
+// block writes its partial to global memory and counts itself in, and the block that arrives
+// last adds the partials up in rank order and puts the counter back to zero. Nobody waits.
 // ---------------------------------------------------------------------------------------------
+
 template <int HD, int DEC_STAGES>
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
-                       int H, int KV, int page_shift, int window, float scale_log2) {
+                       int H, int KV, int page_shift, int window, float scale_log2, float* __restrict__ partials,
+                       int* __restrict__ arrived) {
     constexpr int LD = HD + 8;
+    constexpr int PART = 16 * HD + 32;                                          // floats of one block's partial
     pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_last;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
     __nv_bfloat16* sK0 = sQ + 16 * LD;                                          // DEC_STAGES x BN x LD
     __nv_bfloat16* sV0 = sK0 + DEC_STAGES * BN * LD;
@@ -344,7 +408,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     // every key but the newest was written by earlier steps: all of that may be read before the
     // wait, while the kernel in front (which writes the newest key and this step's q) still runs.
     const int G = H / KV;
-    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    int splits = gridDim.z;
     const int p = positions[seq];                 // one row per request: row index == request index
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_tables + (size_t)seq * max_pages;
@@ -352,6 +417,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     const int lo_key = (p >= 0 && window > 0) ? max(0, p + 1 - window) : 0;
     const int t_first = lo_key / BN;
     const int n_tiles = p >= 0 ? (hi + BN - 1) / BN - t_first : 0;
+    if (partials) {
+        splits = max(1, min(splits, n_tiles / DEC_MIN_TILES));
+        const int share = max(1, (n_tiles + splits - 1) / splits);
+        splits = max(1, (n_tiles + share - 1) / share);      // no block without a tile
+        if (split >= splits) return;                  // the whole block: this request has no tiles for it
+    }
     const int per = (n_tiles + splits - 1) / splits;
     const int t_begin = t_first + split * per;
     const int t_end = min(t_first + n_tiles, t_begin + per);
@@ -472,7 +543,21 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             if (d == 0) { fin[16 * HD + r] = M; fin[16 * HD + 16 + r] = L; }
         }
     }
-    if (splits > 1) {
+    if (splits > 1 && partials) {
+        float* mine = partials + ((size_t)(seq * KV + kvh) * gridDim.z + split) * PART;
+        __syncthreads();
+        for (int e = threadIdx.x; e < G * HD; e += NTHREADS) mine[e] = fin[e];
+        if (threadIdx.x < 32) mine[16 * HD + threadIdx.x] = fin[16 * HD + threadIdx.x];
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(arrived + seq * KV + kvh, 1) == splits - 1;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        merge_partials<HD>(partials + (size_t)(seq * KV + kvh) * gridDim.z * PART, splits, G, reinterpret_cast<float*>(sK0),
+                           out + (size_t)seq * out_stride + (size_t)kvh * G * HD);
+        if (threadIdx.x == 0) arrived[seq * KV + kvh] = 0;      // ready for the next launch
+    } else if (splits > 1) {
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         const uint32_t fin_local = smem_u32(fin);
         const int total = G * HD;
@@ -556,11 +641,14 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
 template <int HD, int ST>
 int launch_decode_st(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                      const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                     float scale, int splits, cudaStream_t stream) {
+                     float scale, int splits, float* partials, int* arrived, cudaStream_t stream) {
     static size_t configured = 0;
     // a block's page list: its share of the tiles of the longest request the block table can hold
+    // (a request with few tiles uses fewer blocks, but then the tiles are few)
     long long tiles_max = ((long long)max_pages * page_size + BN - 1) / BN;
-    long long pages_cta = ((tiles_max + splits - 1) / splits) * (BN / page_size) + 1;
+    long long per_max = (tiles_max + splits - 1) / splits;
+    if (partials && per_max < 2 * DEC_MIN_TILES) per_max = 2 * DEC_MIN_TILES;
+    long long pages_cta = per_max * (BN / page_size) + 1;
     size_t smem = decode_smem<HD, ST>() + (size_t)pages_cta * sizeof(int);
     int e = ensure_smem(attn_decode_mma_kernel<HD, ST>, smem, &configured);
     if (e) return e;
@@ -573,21 +661,21 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = splits;            // the blocks that share one (request, kv head)
+    attr[0].val.clusterDim.z = partials ? 1 : splits;      // the blocks that share one (request, kv head)
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
     cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                         out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
-                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f);
+                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f, partials, arrived);
     return ce != cudaSuccess ? (int)ce : vob_launch_status();
 }
 
 template <int HD>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                   const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                  float scale, int splits, cudaStream_t stream) {
+                  float scale, int splits, float* partials, int* arrived, cudaStream_t stream) {
     static int num_sms = 0;
     if (!num_sms) {
         int dev = 0;
@@ -600,9 +688,9 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>() + 2048));
     if (blocks <= fit3)
         return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                       window, scale, splits, stream);
+                                       window, scale, splits, partials, arrived, stream);
     return launch_decode_st<HD, 2>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                   window, scale, splits, stream);
+                                   window, scale, splits, partials, arrived, stream);
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {
@@ -631,16 +719,19 @@ VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out
                                context_lens, S, max_new, H, KV, page_size, window, scale, stream);
 }
 
-// `splits` (1..8) blocks share each (request, kv head) as one cluster.
+// `splits` (1..8) blocks share each (request, kv head) as one cluster. With `partials` (float32
+// [S * KV * splits * (16 * hd + 32)]) and `arrived` (int32 [S * KV], zero; left zero) up to 64 blocks
+// share it without a cluster and merge through global memory.
 VOB_EXPORT int vob_attn_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                                    const void* vcache, const int* block_tables, int max_pages, const int* positions, int S,
                                    int H, int KV, int hd, int page_size, int window, float scale, int splits,
-                                   cudaStream_t stream) {
+                                   void* partials, int* arrived, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
-    if (q_stride % 8 != 0 || splits < 1 || splits > 8 || KV > 65535) return VOB_ERR_BAD_ARG;
+    if ((partials == nullptr) != (arrived == nullptr)) return VOB_ERR_BAD_ARG;
+    if (q_stride % 8 != 0 || splits < 1 || splits > (partials ? DEC_MAX_SPLITS_WIDE : 8) || KV > 65535) return VOB_ERR_BAD_ARG;
     if (hd == 64) return launch_decode<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
-                                          H, KV, page_size, window, scale, splits, stream);
+                                          H, KV, page_size, window, scale, splits, (float*)partials, arrived, stream);
     return launch_decode<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
-                              page_size, window, scale, splits, stream);
+                              page_size, window, scale, splits, (float*)partials, arrived, stream);
 }

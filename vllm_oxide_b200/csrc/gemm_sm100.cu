@@ -14,7 +14,7 @@
 // memory and (one lane) issues tcgen05.mma, committing each stage back to the producer with
 // tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld (each warp its own 32 lanes) and
 // write C: lane = output feature, so one store instruction of a warp covers 32 consecutive
-// features of one token.
+// features of one token. The kernel for few tokens has one more warp with a second issuing thread.
 //
 // Few tokens leave most SMs without a tile, so the K range can be split over blockIdx.z. The
 // blocks of one tile form a thread-block cluster (up to 8): each leaves its float32 partial tile
@@ -38,6 +38,8 @@ constexpr int BM = 128;           // weight rows (output features) per block
 constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
+constexpr int ISSUERS = 2;          // MMA-issuing threads of the kernel for few tokens (warps 1, 6, 7, ...)
+constexpr int NTHREADS_FEW = 192 + 32 * (ISSUERS - 1);
 // kind::f16 instruction descriptor of this file's products: M = 128 weight rows, N = n tokens, both K-major.
 __host__ __device__ constexpr uint32_t umma_idesc(int n) { return umma_idesc_bf16(BM, n, false); }
 
@@ -89,7 +91,8 @@ typedef EpiArgs QkvArgs;
 
 template <int BT, int EPI> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
 template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage_bytes<BT, EPI_STORE>(); }
-template <int BT, int EPI> __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
+// two accumulators of BT columns each (one per issuing thread) for few tokens
+template <int BT, int EPI> __host__ __device__ constexpr int tmem_cols() { return ISSUERS * BT < 32 ? 32 : ISSUERS * BT; }
 template <int BT> __host__ __device__ constexpr int tmem_cols() { return tmem_cols<BT, EPI_STORE>(); }
 
 // One finished element of column `col` of the block's tile; `row` points at the 128 finished
@@ -152,8 +155,22 @@ __device__ __forceinline__ void finish_element(OutT* __restrict__ C, long long l
     }
 }
 
+// 16 columns of this thread's lane, summed over the issuers' accumulators in a fixed order.
+template <int BT> __device__ __forceinline__ void load_acc(uint32_t taddr, float* r) {
+    uint32_t a[ISSUERS][16];
+#pragma unroll
+    for (int w = 0; w < ISSUERS; ++w) tmem_ld16(taddr + w * BT, a[w]);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (ISSUERS == 4) r[j] = (__uint_as_float(a[0][j]) + __uint_as_float(a[1][j])) + (__uint_as_float(a[2][j]) + __uint_as_float(a[3][j]));
+        else if (ISSUERS == 2) r[j] = __uint_as_float(a[0][j]) + __uint_as_float(a[1][j]);
+        else r[j] = __uint_as_float(a[0][j]);
+    }
+}
+
 template <int BT, int STAGES, typename OutT, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS_FEW, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ C,
                   long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag, int up_row0,
                   const QkvArgs qa) {
@@ -180,8 +197,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int nkb = kb1 - kb0;                    // >= 1 by the launcher's choice of splits
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
-        mbar_init(acc_bar, 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, ISSUERS); }
+        mbar_init(acc_bar, ISSUERS);                     // both issuing threads commit to these
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -227,9 +244,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + s);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp >= 6) {
+        // ISSUERS issuing threads. One thread gets a tcgen05.mma through about every 125 clocks
+        // whatever its size, and an instruction of 128 x 16 x 16 consumes only 4 KB of weights: a
+        // single issuer just about keeps pace with HBM, and its chain is what a block with few
+        // k-blocks waits for. Each thread takes its share of every stage's K steps into an
+        // accumulator of its own; the epilogue adds them in a fixed order. (Measured on a decode
+        // step of 8 rows: two issuers +2.5 %, four +2.7 %.)
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BT);
+            constexpr int KSTEPS = BK / UMMA_K / ISSUERS;
+            const int w = warp >= 6 ? warp - 5 : 0;
+            const uint32_t acc = tmem_base + (uint32_t)(w * BT);
             bool ok = true;
             for (int i = 0; i < nkb && ok; ++i) {
                 int s = i % STAGES;
@@ -241,15 +267,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 uint64_t adesc = umma_desc_sw128(a);
                 uint64_t bdesc = umma_desc_sw128(a + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
+                for (int kk = 0; kk < KSTEPS; ++kk) {
                     // 16 K elements = 32 bytes = 2 units of the descriptor's start address
-                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    const int k = w * KSTEPS + kk;
+                    umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(empty_bar + s);       // the stage is free once these MMAs have read it
+                umma_commit(empty_bar + s);       // the stage is free once both threads' MMAs have read it
             }
             if (ok) umma_commit(acc_bar);         // the accumulator is complete
         }
-    } else {
+    } else if (warp < 6) {
         // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) ... + 31
         const int quad = warp & 3;
         const int col = quad * 32 + lane;
@@ -309,13 +336,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (ok && splits == 1 && EPI == EPI_STORE) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(taddr + c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float r[16];
+                load_acc<BT>(taddr + c, r);
                 if (f < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, __uint_as_float(r[j]) * sc[c + j]);
+                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, r[j] * sc[c + j]);
                 }
             }
         } else if (ok) {
@@ -324,11 +350,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // without a split, the finished tile in which partners of a fused epilogue find each other
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(taddr + c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float r[16];
+                load_acc<BT>(taddr + c, r);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = __uint_as_float(r[j]) * sc[c + j];
+                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = r[j] * sc[c + j];
             }
             if (splits == 1) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -380,7 +405,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
     }
-    if (splits > 1 && warp < 2) {
+    if (splits > 1 && (warp < 2 || warp >= 6)) {
         // the producer and MMA warps take part in the cluster's two barriers as well
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -563,6 +588,10 @@ template <int BT, int STAGES, int EPI = EPI_STORE> constexpr size_t smem_bytes()
 template <int BT, int STAGES, typename OutT, int EPI>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int splits, int kb_per,
            int* err_flag, int up_row0, const QkvArgs& qa, cudaStream_t stream) {
+    // Blocks of a cluster wait for one another, and tcgen05.alloc waits for columns: the blocks that
+    // fit one SM by shared memory must all get their tensor memory, or two clusters could wait for
+    // each other for ever.
+    static_assert((227 * 1024 / smem_bytes<BT, STAGES, EPI>()) * tmem_cols<BT, EPI>() <= 512, "tensor memory oversubscribed");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BT, STAGES, OutT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -573,7 +602,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     cudaLaunchConfig_t cfg = {};
     constexpr int FEATURES_PER_TILE = EPI == EPI_SWIGLU ? BM / 2 : BM;
     cfg.gridDim = dim3((N + FEATURES_PER_TILE - 1) / FEATURES_PER_TILE, (T + BT - 1) / BT, splits);
-    cfg.blockDim = dim3(NTHREADS);
+    cfg.blockDim = dim3(NTHREADS_FEW);
     cfg.dynamicSmemBytes = smem_bytes<BT, STAGES, EPI>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];

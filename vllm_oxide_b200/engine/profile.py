@@ -3,6 +3,7 @@ crates/engine/examples/generate.rs:56-67)."""
 from __future__ import annotations
 
 from .. import kernels
+from ..parts.base import LONG_CONTEXT_KEYS
 
 
 def profile_decode_step(runner, prompt, steps: int = 4):
@@ -58,6 +59,8 @@ def _kernel_cases(argv):
     ap.add_argument("--copies", type=int, default=6)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--graph", action="store_true", help="time the launches back to back, replayed from one CUDA graph")
+    ap.add_argument("--merge", default="auto", choices=["auto", "cluster", "global"],
+                    help="attn_decode: how the blocks of a request merge (auto: the engine's choice)")
     ap.add_argument("--impl", default="sm100", choices=["sm100", "mma"], help="attn_prefill: the tcgen05 or the mma.sync kernel")
     a = ap.parse_args(argv)
     dev = "cuda:0"
@@ -94,8 +97,15 @@ def _kernel_cases(argv):
         scale = 1.0 / math.sqrt(hd)
         if a.kernel == "attn_decode":
             pos = torch.full((S,), L - 1, dtype=torch.int32, device=dev)
-            splits = max(1, min(8, -(-2 * torch.cuda.get_device_properties(dev).multi_processor_count // (S * KV))))
-            launches = [lambda kc=kc, vc=vc: kernels.attn_decode_mma(q, out, kc, vc, bt, pos, H, KV, hd, scale, 0, splits)
+            # the engine's choice (parts/attention.py decode_splits): a cluster of up to 8 blocks per
+            # request and kv head, or, for one few requests with long contexts, up to 64 that merge through global memory
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            wide = 3 * sms // (S * KV) >= 4 and (ctx > LONG_CONTEXT_KEYS if a.merge == "auto" else a.merge == "global")
+            splits = max(1, min(64, 3 * sms // (S * KV))) if wide else max(1, min(8, -(-2 * sms // (S * KV))))
+            partials = torch.empty(kernels.attn_decode_partial_floats(S, KV, hd, splits), device=dev) if wide else None
+            arrived = torch.zeros(S * KV, dtype=torch.int32, device=dev) if wide else None
+            launches = [lambda kc=kc, vc=vc: kernels.attn_decode_mma(q, out, kc, vc, bt, pos, H, KV, hd, scale, 0, splits,
+                                                                     partials, arrived)
                         for kc, vc in caches]
             nbytes = 2 * S * L * KV * hd * 2
             flops = 4.0 * S * H * hd * L

@@ -25,7 +25,7 @@ from ..cache.pools import CachePools
 from ..config import EngineConfig, architecture_for, read_config_json
 from ..csrc.build import runtime_module
 from ..errors import CapacityError, KernelError, ShapeError
-from ..parts.base import FOLD_ROWS, ModelSpec, StepContext, Workspace
+from ..parts.base import FOLD_ROWS, LONG_CONTEXT_KEYS, ModelSpec, StepContext, Workspace
 from ..weights import load_safetensors_weights, weights_from_tensors
 
 
@@ -157,7 +157,8 @@ class ModelRunner:
             workspace=self.workspace,
             max_new=arrays.max_new if arrays is not None else 0,
             max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays,
-            decode_only=bool(arrays is not None and arrays.max_new == 1 and arrays.rows == arrays.seqs))
+            decode_only=bool(arrays is not None and arrays.max_new == 1 and arrays.rows == arrays.seqs),
+            long_context=bool(arrays is not None and arrays.max_seq_len > LONG_CONTEXT_KEYS))
 
     def upload(self, arrays) -> None:
         """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
@@ -274,7 +275,8 @@ class ModelRunner:
     def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True, parity: int = 0):
         """A step in which every request brings exactly one token. Its kernels are the same as any
         step's, but their launches are replayed from a CUDA graph captured once per batch-size
-        class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing), because
+        class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing) and per
+        kind of context (long or not: parts may pick other kernels for long contexts), because
         at small batches launching ~10 kernels per layer costs more than running them
         (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51).
         The picked tokens land in pinned host buffer `parity`. With `read` the call waits and
@@ -290,17 +292,18 @@ class ModelRunner:
             # runs ahead without reading them back; request order must not have changed)
             self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
         b = self._bucket(S)
-        key = (b, parity)
+        long_context = bool(arrays.max_seq_len > LONG_CONTEXT_KEYS)
+        key = (b, parity, long_context)
         graph = self._graphs.get(key)
         if graph is None:
             # first step of this class: run it eagerly (that is this step's result), then record
             # the same launches for the steps to come
-            self._decode_eager(b, parity)
+            self._decode_eager(b, parity, long_context)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = kernels.launch_count()
             with torch.cuda.graph(g, pool=self._graph_pool):
-                self._decode_eager(b, parity)
+                self._decode_eager(b, parity, long_context)
             self._graph_launches[key] = kernels.launch_count() - n0
             kernels.count_launches(-self._graph_launches[key])      # recorded, not run
             self._graphs[key] = g
@@ -322,11 +325,11 @@ class ModelRunner:
         event.synchronize()
         return self.sampled_host_np[parity, :count].tolist()
 
-    def _decode_eager(self, b: int, parity: int = 0) -> None:
+    def _decode_eager(self, b: int, parity: int = 0, long_context: bool = False) -> None:
         L = self.decode_layout
         self.workspace.reset()
         ctx = self.context(b, b, None, L)
-        ctx.decode_only, ctx.max_new = True, 1
+        ctx.decode_only, ctx.max_new, ctx.long_context = True, 1, long_context
         resid, pending = self._forward(ctx)
         self._head(resid, pending, ctx, b, None, L)
         self.sampled_host[parity, :b].copy_(self.sampled[:b], non_blocking=True)

@@ -842,10 +842,13 @@ def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context
 
 @_timed
 def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int = 0, splits: int = 1) -> None:
+                    scale: float, window: int = 0, splits: int = 1, partials=None, arrived=None) -> None:
     """Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
     With splits > 1 (at most 8) each request's keys are shared out over the blocks of a cluster,
-    which merge their partial results through distributed shared memory."""
+    which merge their partial results through distributed shared memory. With `partials` (float32,
+    `attn_decode_partial_floats` elements) and `arrived` (int32 zeros, one per request and kv head;
+    the kernel leaves them zero) up to 64 blocks share a request without a cluster and merge
+    through global memory: for few requests with long contexts."""
     op = "attn_decode_mma"
     if not scale > 0:
         raise ShapeError(op, f"the score scale must be positive, got {scale}")
@@ -857,13 +860,28 @@ def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: 
         raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {S} requests")
     if num_heads // num_kv_heads > 16:
         raise ShapeError(op, f"{num_heads // num_kv_heads} heads per kv head: the decode kernel takes at most 16")
-    if not 1 <= splits <= 8:
-        raise ShapeError(op, f"splits must be 1..8, got {splits}")
+    if (partials is None) != (arrived is None):
+        raise ShapeError(op, "partials and arrived go together")
+    most = 8 if partials is None else 64
+    if not 1 <= splits <= most:
+        raise ShapeError(op, f"splits must be 1..{most}, got {splits}")
+    if partials is not None:
+        _cuda(op, partials, arrived)
+        need = attn_decode_partial_floats(S, num_kv_heads, head_dim, splits)
+        if partials.dtype != torch.float32 or not partials.is_contiguous() or partials.numel() < need or partials.data_ptr() % 16:
+            raise ShapeError(op, f"partials must be contiguous float32, 16-byte aligned, with at least {need} elements")
+        if arrived.dtype != torch.int32 or not arrived.is_contiguous() or arrived.numel() < S * num_kv_heads:
+            raise ShapeError(op, f"arrived must be contiguous int32 with at least {S * num_kv_heads} elements")
     f = _fn("attention_mma", "vob_attn_decode_mma",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P])
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
              block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
-             float(scale), int(splits), _stream()), op)
+             float(scale), int(splits), _ptr(partials), _ptr(arrived), _stream()), op)
+
+
+def attn_decode_partial_floats(num_seqs: int, num_kv_heads: int, head_dim: int, splits: int) -> int:
+    """Elements of the float32 scratch that `attn_decode_mma` needs for its merge through global memory."""
+    return num_seqs * num_kv_heads * splits * (16 * head_dim + 32)
 
 
 # ------------------------------------------------------------------------------------ sampling

@@ -54,6 +54,10 @@ class Attention(Mixer):
         self.impl = "auto"            # "general" forces the general attention kernel, "mma" the mma.sync kernels (tests)
         self.fused = True             # False forces the separate projection / rotary / cache-write kernels
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+        # scratch of the decode kernel's merge through global memory (one or two requests with long
+        # contexts): made at the first such step, kept; the counters are zero between launches
+        self._partials = None
+        self._arrived = None
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return CacheSpec(self.KV, self.hd, "window" if self.window else "full", self.window)
@@ -122,8 +126,13 @@ class Attention(Mixer):
         bt = ctx.block_tables[cache.group]
         if self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0:
             if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
-                kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd,
-                                        self.scale, self.window, self.decode_splits(ctx.rows))
+                splits, wide = self.decode_splits(ctx.rows, ctx.long_context)
+                if wide and self._partials is None:
+                    floats = kernels.attn_decode_partial_floats(1, 1, self.hd, 3 * self.num_sms)    # requests x kv heads x splits <= 3 SMs
+                    self._partials = torch.empty(floats, dtype=torch.float32, device=q.device)
+                    self._arrived = torch.zeros(self.num_sms, dtype=torch.int32, device=q.device)
+                kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd, self.scale,
+                                        self.window, splits, self._partials if wide else None, self._arrived if wide else None)
                 return
             if (not ctx.decode_only and ctx.max_new > 0 and self.window == 0 and self.impl != "mma"
                     and kernels.attn_prefill_sm100_supported(self.H, self.KV, self.hd, page, bt.shape[1])):
@@ -137,8 +146,16 @@ class Attention(Mixer):
         kernels.paged_attention(q, out, cache.k, cache.v, bt, ctx.row_seq, ctx.positions, self.H, self.KV, self.hd,
                                 self.scale, self.window)
 
-    def decode_splits(self, num_seqs: int) -> int:
-        """How many blocks share one request's keys in a decode step: enough that the grid fills
-        the GPU twice over, at most 8 (the blocks of one request form a cluster)."""
+    def decode_splits(self, num_seqs: int, long_context: bool = False):
+        """(splits, wide): how many blocks share one request's keys in a decode step. Up to 8 blocks
+        form a cluster and merge through shared memory: enough that the grid fills the GPU twice
+        over. With long contexts and few requests (at least 4 blocks per request and kv head at
+        three blocks per SM, which is what fits with the three-stage ring), up to 64 blocks merge
+        through global memory instead (`wide`), and a request uses as many of them as its length
+        is worth. Measured with 8 kv heads of 64: one request of 131,072 keys 175 us in clusters
+        of 8, 51 us wide; 8 requests of 32,768 keys 107 / 94 us; below some 6,000 keys the cluster
+        is faster."""
         blocks = max(1, num_seqs * self.KV)
-        return max(1, min(8, -(-2 * self.num_sms // blocks)))
+        if long_context and 3 * self.num_sms // blocks >= 4:
+            return min(64, 3 * self.num_sms // blocks), True
+        return max(1, min(8, -(-2 * self.num_sms // blocks))), False

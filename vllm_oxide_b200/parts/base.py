@@ -120,6 +120,8 @@ class StepContext:
     max_new: int = 0                # longest portion in the batch (host fact)
     max_seq_len: int = 0            # longest context after the step (host fact)
     decode_only: bool = False       # every request brings exactly one token and row i is request i
+    long_context: bool = False      # some request is longer than LONG_CONTEXT_KEYS (host fact; a replayed
+                                    # step was recorded with the same value)
     host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them
 
     def alloc(self, shape, dtype=None) -> torch.Tensor:
@@ -139,6 +141,7 @@ class FoldedState:
 
 
 FOLD_ROWS = 32              # most rows a step may have for the folded form
+LONG_CONTEXT_KEYS = 6144    # beyond this a step counts as one of long contexts (parts may pick other kernels)
 
 
 # ------------------------------------------------------------------------------ part interfaces

@@ -95,66 +95,6 @@ template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage
 template <int BT, int EPI> __host__ __device__ constexpr int tmem_cols() { return ISSUERS * BT < 32 ? 32 : ISSUERS * BT; }
 template <int BT> __host__ __device__ constexpr int tmem_cols() { return tmem_cols<BT, EPI_STORE>(); }
 
-// One finished element of column `col` of the block's tile; `row` points at the 128 finished
-// values of the same token in shared memory (partners of a rotation, the "up" half of SwiGLU).
-// With `pre` the rotation's cosine, sine and the cache slot were worked out ahead of time.
-template <int EPI, typename OutT>
-__device__ __forceinline__ void finish_element(OutT* __restrict__ C, long long ldc, int t, int f, int col, float v,
-                                               const float* row, int m_tile, int N, const QkvArgs& qa, bool pre, float pc,
-                                               float ps, int pslot) {
-    if (EPI == EPI_STORE) {
-        if (f < N) store_out<OutT>(C + (size_t)t * ldc + f, v);
-    } else if (EPI == EPI_RESID) {
-        // all 128 threads of the tile come here together: `row` is scratch for the sum of squares
-        float sq = 0.f;
-        if (f < N) {
-            const float r_new = (pre ? pc : qa.resid[(size_t)t * qa.ld_resid + f]) + v;
-            qa.resid[(size_t)t * qa.ld_resid + f] = r_new;
-            qa.xn_out[(size_t)t * qa.ld_xn + f] = __float2bfloat16_rn(r_new * ps);
-            sq = r_new * r_new;
-        }
-        sq = warp_sum(sq);
-        float* red = const_cast<float*>(row);
-        if ((col & 31) == 0) red[col >> 5] = sq;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (col == 0) qa.ssq_out[(size_t)m_tile * qa.ld_ssq + t] = (red[0] + red[1]) + (red[2] + red[3]);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-    } else if (EPI == EPI_SWIGLU) {
-        // columns 0..63: gate of feature m_tile * 64 + col; columns 64..127: up of the same features
-        const int fo = m_tile * (BM / 2) + col;
-        if (col < BM / 2 && fo < N) store_out<OutT>(C + (size_t)t * ldc + fo, v / (1.0f + expf(-v)) * row[col + BM / 2]);
-    } else {
-        if (f >= N) return;
-        const int hd = qa.hd, half = hd >> 1;
-        const bool is_q = f < qa.q_dim, is_k = !is_q && f < qa.q_dim + qa.kv_dim;
-        float outv = v;
-        if ((is_q || is_k) && qa.inv_freq) {
-            const int i = f % hd;
-            const float partner = row[i < half ? col + half : col - half];
-            float c = pc, s = ps;
-            if (!pre) {
-                const float theta = (float)qa.positions[t] * qa.inv_freq[i < half ? i : i - half];
-                c = cosf(theta);
-                s = sinf(theta);
-            }
-            outv = i < half ? v * c - partner * s : v * c + partner * s;
-        }
-        if (is_q) {
-            store_out<OutT>(C + (size_t)t * ldc + f, outv);
-        } else {
-            const int slot = pre ? pslot : (qa.slots ? qa.slots[t] : -1);
-            if (slot >= 0) {
-                const int g = is_k ? f - qa.q_dim : f - qa.q_dim - qa.kv_dim;
-                const int kh = g / hd, d = g - kh * hd;
-                const size_t page = (size_t)(slot / qa.page_size);
-                const int off = slot % qa.page_size;
-                const size_t idx = ((page * qa.KV + kh) * qa.page_size + off) * (size_t)hd + d;
-                (is_k ? qa.kcache : qa.vcache)[idx] = __float2bfloat16_rn(outv);
-            }
-        }
-    }
-}
-
 // 16 columns of this thread's lane, summed over the issuers' accumulators in a fixed order.
 template <int BT> __device__ __forceinline__ void load_acc(uint32_t taddr, float* r) {
     uint32_t a[ISSUERS][16];
@@ -176,7 +116,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                   const QkvArgs qa) {
     constexpr int SB = stage_bytes<BT, EPI>();
     constexpr int A_BYTES = BM * BK * 2;
-    constexpr int PRE = 4;                         // tokens per block whose rotation is worked out ahead
+    constexpr int PRE = BT >= 64 ? 12 : (BT >= 32 ? 8 : 4);   // tokens per block whose rotation is worked out ahead
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -282,31 +222,37 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int col = quad * 32 + lane;
         const int f = m_tile * BM + col;                       // this thread's output feature
         const int t0 = n_tile * BT;
-        // Rotary positions: what this thread will need for the tokens its block finishes (cosine,
-        // sine, cache slot) depends only on data that was on the device before the step began, so
-        // it is worked out now, while the weights stream, not after the accumulator is done.
+        // The tokens this block finishes: its whole tile without a split, else every splits-th
+        // token (number k is token tok_first + k * splits of the tile).
+        const int tok_first = splits > 1 ? split : 0;
+        const int tok_end = min(BT, T - t0);
+        const int nk = tok_end > tok_first ? (tok_end - tok_first + splits - 1) / splits : 0;
+        // Rotary positions: what this thread will need for the first tokens its block finishes
+        // (cosine, sine, cache slot) depends only on data that was on the device before the step
+        // began, so it is worked out now, while the weights stream, not after the accumulator is done.
         float pc[PRE], ps[PRE];
         int pslot[PRE];
-        if (EPI == EPI_QKV && splits > 1) {
+        bool rot = false;
+        float inv = 0.f;
+        if (EPI == EPI_QKV) {
             const int hd = qa.hd, half = hd >> 1, i = f % hd;
-            const bool rot = qa.inv_freq && f < qa.q_dim + qa.kv_dim;
-            const float inv = rot ? qa.inv_freq[i < half ? i : i - half] : 0.f;
+            rot = qa.inv_freq && f < qa.q_dim + qa.kv_dim;
+            inv = rot ? qa.inv_freq[i < half ? i : i - half] : 0.f;
 #pragma unroll
             for (int k = 0; k < PRE; ++k) {
-                const int j = split + k * splits;
                 pc[k] = 1.f; ps[k] = 0.f; pslot[k] = -1;
-                if (j < BT && t0 + j < T) {
-                    const float theta = (float)qa.positions[t0 + j] * inv;
+                if (k < nk) {
+                    const int t = t0 + tok_first + k * splits;
+                    const float theta = (float)qa.positions[t] * inv;
                     pc[k] = cosf(theta);
                     ps[k] = sinf(theta);
-                    pslot[k] = qa.slots ? qa.slots[t0 + j] : -1;
+                    pslot[k] = qa.slots ? qa.slots[t] : -1;
                 }
             }
         }
         pdl_wait();
-        // per-token scale of the accumulator (the folded RMSNorm of this product's input) and, for a
-        // residual epilogue, the old residual of the tokens this block finishes: both come from
-        // kernels in front, so they are fetched after the wait, while the product itself runs
+        // per-token scale of the accumulator (the folded RMSNorm of this product's input): it comes
+        // from kernels in front, so it is fetched after the wait, while the product itself runs
         {
             // 128 threads = BT tokens x (128 / BT) lanes: lane l adds the tiles l, l + L, ... of its
             // token, then the lanes' sums are added pairwise in a fixed tree (one L2 round trip
@@ -320,19 +266,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             for (int o = L / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             if (ln == 0) sc[tk] = (qa.ssq_in && t0 + tk < T) ? 1.0f / sqrtf(part * qa.inv_h + qa.eps) : 1.f;
         }
-        if (EPI == EPI_RESID) ps[0] = f < N ? qa.next_w[f] : 0.f;       // the next norm's weight of this feature
-        if (EPI == EPI_RESID && splits > 1) {
-#pragma unroll
-            for (int k = 0; k < PRE; ++k) {
-                const int j = split + k * splits;
-                pc[k] = (j < BT && t0 + j < T && f < N) ? qa.resid[(size_t)(t0 + j) * qa.ld_resid + f] : 0.f;
-            }
-        }
+        float next_w = 0.f;
+        if (EPI == EPI_RESID) next_w = f < N ? qa.next_w[f] : 0.f;      // the next norm's weight of this feature
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
+        const bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        float* tile = reinterpret_cast<float*>(tiles);         // [token][128] float32 over the operand stages
+        // Shared memory over the operand stages (every MMA that read them has completed once acc_bar
+        // has flipped): `tile` [BT][128] is this block's tile (a partial one under a split, which
+        // peers read); `fin` [nk][128] the finished values of the tokens this block completes, in
+        // which partners of a fused epilogue find each other; `red` [nk][4] sums of squares by warp.
+        float* tile = reinterpret_cast<float*>(tiles);
+        float* fin = splits > 1 ? tile + BT * BM : tile;
+        float* red = fin + (splits > 1 ? (BT / 2) * BM : BT * BM);
         if (ok && splits == 1 && EPI == EPI_STORE) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
@@ -345,9 +291,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         } else if (ok) {
-            // the tile to this block's shared memory (every MMA that read the operand stages has
-            // completed once acc_bar has flipped): a partial tile for the cluster to add up, or,
-            // without a split, the finished tile in which partners of a fused epilogue find each other
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 float r[16];
@@ -355,51 +298,124 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = r[j] * sc[c + j];
             }
-            if (splits == 1) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                for (int j = 0; j < BT && t0 + j < T; ++j)
-                    finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, tile[j * BM + col], EPI == EPI_RESID ? xch : tile + j * BM, m_tile, N,
-                                              qa, false, 0.f, EPI == EPI_RESID ? ps[0] : 0.f, -1);
-            }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         if (splits > 1) {
             // every thread of every block of the cluster: partials are written, peers may read them
             __syncwarp();
             asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-            if (!*abort_flag) {
-                const uint32_t local = smem_u32(tile + col);
-                // this block adds up the tokens j with j % splits == its rank
-                int k = 0;
-                for (int j = split; j < BT && t0 + j < T; j += splits, ++k) {
+        } else {
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        // the same answer in all 128 threads (a wait that gave up has raised the block's flag)
+        const bool go = !*abort_flag && !(splits == 1 && EPI == EPI_STORE);
+        if (go) {
+            // Step one, all tokens at once (independent loads): under a split, add the peers'
+            // partials up through distributed shared memory in rank order; a residual epilogue adds
+            // the old residual. Only then do the tokens meet their partners, with no barrier per token.
+            if (splits > 1) {
+                uint32_t remote[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[p]) : "r"(smem_u32(tile + col)), "r"(p < splits ? p : 0));
+#pragma unroll 2
+                for (int k = 0; k < nk; ++k) {
+                    const int j = tok_first + k * splits;
                     float part[8];
 #pragma unroll
                     for (int p = 0; p < 8; ++p) {
                         part[p] = 0.f;
-                        if (p < splits) {
-                            uint32_t remote;
-                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local + (uint32_t)(j * BM * 4)), "r"(p));
-                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[p]) : "r"(remote) : "memory");
-                        }
+                        if (p < splits)
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[p]) : "r"(remote[p] + (uint32_t)(j * BM * 4)) : "memory");
                     }
+                    float old = 0.f;
+                    if (EPI == EPI_RESID && f < N) old = qa.resid[(size_t)(t0 + j) * qa.ld_resid + f];
                     float acc = 0.f;
 #pragma unroll
                     for (int p = 0; p < 8; ++p) acc += part[p];       // rank order, zeros beyond the last rank
                     if (EPI == EPI_STORE) {
                         if (f < N) store_out<OutT>(C + (size_t)(t0 + j) * ldc + f, acc);
-                    } else if (EPI == EPI_RESID) {
-                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, k < PRE, pc[k < PRE ? k : 0], ps[0], -1);
                     } else {
-                        // partners meet in a row of shared memory
-                        xch[col] = acc;
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        const bool pre = EPI == EPI_QKV && k < PRE;
-                        finish_element<EPI, OutT>(C, ldc, t0 + j, f, col, acc, xch, m_tile, N, qa, pre, pre ? pc[k < PRE ? k : 0] : 0.f,
-                                                  pre ? ps[k < PRE ? k : 0] : 0.f, pre ? pslot[k < PRE ? k : 0] : -1);
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        fin[k * BM + col] = old + acc;
                     }
                 }
+            } else if (EPI == EPI_RESID) {
+#pragma unroll 4
+                for (int k = 0; k < nk; ++k) {
+                    const float old = f < N ? qa.resid[(size_t)(t0 + k) * qa.ld_resid + f] : 0.f;
+                    fin[k * BM + col] = old + fin[k * BM + col];
+                }
             }
+            if (EPI != EPI_STORE && (splits > 1 || EPI == EPI_RESID)) asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (EPI == EPI_SWIGLU) {
+                // columns 0..63: gate of feature m_tile * 64 + col; columns 64..127: up of the same
+                // features. The two halves of the threads take alternate tokens.
+                const int c = col & (BM / 2 - 1);
+                const int fo = m_tile * (BM / 2) + c;
+                if (fo < N) {
+                    for (int k = col / (BM / 2); k < nk; k += 2) {
+                        const float g = fin[k * BM + c], u = fin[k * BM + c + BM / 2];
+                        store_out<OutT>(C + (size_t)(t0 + tok_first + k * splits) * ldc + fo, g / (1.0f + expf(-g)) * u);
+                    }
+                }
+            } else if (EPI == EPI_QKV) {
+                const int hd = qa.hd, half = hd >> 1, i = f % hd;
+                const bool is_q = f < qa.q_dim, is_k = !is_q && f < qa.q_dim + qa.kv_dim;
+                const int pcol = i < half ? col + half : col - half;           // the rotation's partner
+                const int g = is_q ? 0 : (is_k ? f - qa.q_dim : f - qa.q_dim - qa.kv_dim);
+                const int kh = g / hd, d = g - kh * hd;
+                auto finish = [&](int k, float c, float s_, int slot) {
+                    const int t = t0 + tok_first + k * splits;
+                    const float v = fin[k * BM + col];
+                    float outv = v;
+                    if (rot) {
+                        const float partner = fin[k * BM + pcol];
+                        outv = i < half ? v * c - partner * s_ : v * c + partner * s_;
+                    }
+                    if (is_q) {
+                        store_out<OutT>(C + (size_t)t * ldc + f, outv);
+                    } else if (slot >= 0) {
+                        const size_t page = (size_t)(slot / qa.page_size);
+                        const int off = slot % qa.page_size;
+                        const size_t idx = ((page * qa.KV + kh) * qa.page_size + off) * (size_t)hd + d;
+                        (is_k ? qa.kcache : qa.vcache)[idx] = __float2bfloat16_rn(outv);
+                    }
+                };
+                if (f < N) {
+#pragma unroll
+                    for (int k = 0; k < PRE; ++k)
+                        if (k < nk) finish(k, pc[k], ps[k], pslot[k]);
+                    for (int k = PRE; k < nk; ++k) {
+                        const int t = t0 + tok_first + k * splits;
+                        float c = 1.f, s_ = 0.f;
+                        if (rot) {
+                            const float theta = (float)qa.positions[t] * inv;
+                            c = cosf(theta);
+                            s_ = sinf(theta);
+                        }
+                        finish(k, c, s_, is_q ? -1 : (qa.slots ? qa.slots[t] : -1));
+                    }
+                }
+            } else if (EPI == EPI_RESID) {
+                for (int k = 0; k < nk; ++k) {
+                    const int t = t0 + tok_first + k * splits;
+                    float sq = 0.f;
+                    if (f < N) {
+                        const float r_new = fin[k * BM + col];
+                        qa.resid[(size_t)t * qa.ld_resid + f] = r_new;
+                        qa.xn_out[(size_t)t * qa.ld_xn + f] = __float2bfloat16_rn(r_new * next_w);
+                        sq = r_new * r_new;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) red[k * 4 + quad] = sq;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int k = col; k < nk; k += 128)
+                    qa.ssq_out[(size_t)m_tile * qa.ld_ssq + t0 + tok_first + k * splits] =
+                        (red[k * 4] + red[k * 4 + 1]) + (red[k * 4 + 2] + red[k * 4 + 3]);
+            }
+        }
+        if (splits > 1) {
             // nobody leaves (and frees its shared memory) while a peer may still be reading it
             __syncwarp();
             asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -640,6 +656,12 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, lon
                       mw, mx, (OutT*)C, ldc, T, N, K, err_flag);
 }
 
+// Stages of the ring for few tokens: as many as let two blocks share an SM (about 110 KB each).
+// With one block per SM the next kernel's blocks (and their clusters, which need all their SMs
+// free at one time) cannot move in beside this kernel's: its prefetch before the wait is lost and
+// it runs in waves (measured at 32 rows: a QKV product of 8 us in block 0 took 19 us as a grid).
+constexpr int few_stages(int bt) { return bt <= 16 ? 6 : bt <= 32 ? 5 : 4; }
+
 int pick_bt(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 }  // namespace
@@ -694,9 +716,9 @@ VOB_EXPORT int vob_gemm_sm100(const void* X, long long ldx, const void* W, long 
                ? launch<BT, ST, float, EPI_STORE>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, 0, QkvArgs{}, stream)      \
                : launch<BT, ST, __nv_bfloat16, EPI_STORE>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, 0, QkvArgs{}, stream)
     switch (bt) {
-        case 16: GO(16, 6);
-        case 32: GO(32, 6);
-        case 64: GO(64, 4);
+        case 16: GO(16, few_stages(16));
+        case 32: GO(32, few_stages(32));
+        case 64: GO(64, few_stages(64));
         default: break;
     }
 #undef GO
@@ -745,7 +767,7 @@ VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, lo
     if (e) return e;
     e = make_map(&mx, X, T, K, ldx, bt);
     if (e) return e;
-#define GOX(BT_, OUT_, EPI_) return launch<BT_, 6, OUT_, EPI_>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, mode == EPI_SWIGLU ? N : 0, *ea, stream)
+#define GOX(BT_, OUT_, EPI_) return launch<BT_, few_stages(BT_), OUT_, EPI_>(mw, mx, C, ldc, T, N, K, splits, kb_per, err_flag, mode == EPI_SWIGLU ? N : 0, *ea, stream)
     switch (mode) {
         case EPI_STORE:
             if (ldc < N) return VOB_ERR_BAD_ARG;

@@ -467,7 +467,7 @@ def _pick_splits(T: int, N: int, K: int, device) -> int:
 
 FUSED_GEMM_MAX_ROWS = 64      # what the fused kernels take
 PAIR_GEMM_FROM_ROWS = 1024    # from here the two-SM product with the SwiGLU epilogue beats the library product plus the activation kernel
-FUSED_GEMM_BEST_ROWS = 32     # up to here they beat the library product plus separate kernels (measured at 64 rows: 25 % slower)
+FUSED_GEMM_BEST_ROWS = 32     # up to here they beat the library product plus separate kernels (a decode step of 64 rows: 15 % slower)
 
 
 @_timed

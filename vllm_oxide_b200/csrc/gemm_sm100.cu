@@ -124,10 +124,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * SB);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    uint64_t* done_bar = acc_bar + 1;              // under a split: every block of the cluster has read this block's partials
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(done_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-    float* xch = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);      // 128 floats: partners meet here
-    float* sc = xch + 128;                                                        // BT floats: per-token scales
+    float* sc = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);       // BT floats: per-token scales
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -139,6 +139,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, ISSUERS); }
         mbar_init(acc_bar, ISSUERS);                     // both issuing threads commit to these
+        mbar_init(done_bar, splits);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -346,7 +347,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     fin[k * BM + col] = old + fin[k * BM + col];
                 }
             }
-            if (EPI != EPI_STORE && (splits > 1 || EPI == EPI_RESID)) asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (splits > 1 || EPI == EPI_RESID) asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (splits > 1 && col < splits) {
+            // this block has read what it needs of every peer's partials: tell each of them (a block
+            // may leave, and free its shared memory, once all have said so; no second meeting)
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(done_bar)), "r"(col));
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+        }
+        if (go) {
             if (EPI == EPI_SWIGLU) {
                 // columns 0..63: gate of feature m_tile * 64 + col; columns 64..127: up of the same
                 // features. The two halves of the threads take alternate tokens.
@@ -415,16 +425,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         (red[k * 4] + red[k * 4 + 1]) + (red[k * 4 + 2] + red[k * 4 + 3]);
             }
         }
+        // nobody leaves (and frees its shared memory) while a peer may still be reading it; by now
+        // the peers' notices have usually come in
         if (splits > 1) {
-            // nobody leaves (and frees its shared memory) while a peer may still be reading it
-            __syncwarp();
-            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            volatile int never = 0;          // this wait does not give up early: peers may be reading
+            mbar_wait(done_bar, 0, &never, err_flag, 4);
         }
     }
     if (splits > 1 && (warp < 2 || warp >= 6)) {
-        // the producer and MMA warps take part in the cluster's two barriers as well
-        __syncwarp();
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // the producer and MMA warps take part in the cluster's barrier as well
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
@@ -598,7 +607,7 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, 
 }
 
 template <int BT, int STAGES, int EPI = EPI_STORE> constexpr size_t smem_bytes() {
-    return (size_t)STAGES * stage_bytes<BT, EPI>() + 1024 + 1024;       // tiles + alignment slack + barriers and exchange row
+    return (size_t)STAGES * stage_bytes<BT, EPI>() + 1024 + 1024;       // tiles + alignment slack + barriers and per-token scales
 }
 
 template <int BT, int STAGES, typename OutT, int EPI>

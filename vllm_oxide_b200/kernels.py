@@ -664,8 +664,8 @@ def gemm_sm100_check() -> None:
         code = int(sc.err.item())
         if code:
             sc.err.zero_()
-            raise KernelError(f"a bounded wait expired inside a tensor-core kernel (code {code}: 1-3 = matrix product: TMA "
-                              "producer, MMA issuer, epilogue; 11-21 = attention: 11-12 TMA producer, 13-17 MMA issuer, "
+            raise KernelError(f"a bounded wait expired inside a tensor-core kernel (code {code}: 1-4 = matrix product: TMA "
+                              "producer, MMA issuer, epilogue, peers of a split; 11-21 = attention: 11-12 TMA producer, 13-17 MMA issuer, "
                               "18-21 softmax rows); its result is not valid")
 
 

@@ -96,6 +96,38 @@ def reference_arm():
     return 0
 
 
+def serve_run(a, llm, cfg, sz, layers, full_layers, gen_len, params):
+    """Many requests of different lengths at once through the public entry point: the scheduler
+    cuts prompts into portions under the token budget and mixes them with the decoding of the
+    requests that are through. Wall-clock time of generate(), host token ids in and out."""
+    import time
+    import torch
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(a.serve_min, a.serve_max + 1, (a.serve,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    llm.generate([p[:64] for p in prompts[:4]], params.__class__(max_new_tokens=8, temperature=0.0, stop_token_ids=()))  # warm-up
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    steps0 = llm.runner.steps_run
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, params)
+    torch.cuda.synchronize()
+    secs = time.perf_counter() - t0
+    clocks = sampler.stop()
+    generated = sum(len(o.token_ids) for o in outs)
+    print(json.dumps({
+        "metric": f"serving run through LLM.generate ({sz['name']}): generated tok/s", "value": generated / secs, "unit": "tok/s",
+        "total_tok_s": (sum(lens) + generated) / secs, "seconds": secs, "engine_steps": llm.runner.steps_run - steps0,
+        "preemptions": llm.stats.get("preemptions", 0), "n_gpus": 1, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), seeded uniform token ids and prompt lengths",
+        "config": {"model": sz["name"], "layers": layers, "layers_full": full_layers, "requests": a.serve,
+                   "prompt_len_min": a.serve_min, "prompt_len_max": a.serve_max, "prompt_tokens": sum(lens),
+                   "generated_per_request": gen_len, "max_batch_tokens": 2048, "page_size": 16},
+        "clocks": clocks, "impl": "ours"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -110,18 +142,27 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--gen-len", type=int, default=GEN_LEN)
     ap.add_argument("--context", type=int, default=8192, help="max_model_len of the engine")
+    ap.add_argument("--serve", type=int, default=0, metavar="N",
+                    help="instead of the step measurements: N requests with prompts of seeded uniform lengths in "
+                         "[--serve-min, --serve-max], --gen-len tokens each, all handed to LLM.generate at once "
+                         "(chunked prefill mixed with decoding); prints one line with total tokens a second")
+    ap.add_argument("--serve-min", type=int, default=128)
+    ap.add_argument("--serve-max", type=int, default=4096)
     a = ap.parse_args()
     prompt_len, gen_len = a.prompt_len, a.gen_len
     # requests that finish their prompt early decode while the others still prefill, and the timed
     # steps come on top: no request may run out of tokens before the measurement ends
     max_b_guard = max(a.batch, 1 if a.no_points else 64)
-    gen_len = max(gen_len, max_b_guard * prompt_len // 2048 + max(a.warmup, 3) + a.steps + 16)
+    if not a.serve:
+        gen_len = max(gen_len, max_b_guard * prompt_len // 2048 + max(a.warmup, 3) + a.steps + 16)
     if a.impl == "reference":
         return reference_arm()
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.serve:
+        prompt_len = a.serve_max
     if prompt_len + gen_len + 16 > a.context:
         print(f"bench.py: --context {a.context} is too short for prompts of {prompt_len} plus {gen_len} generated tokens")
         return 2
@@ -145,6 +186,8 @@ def main():
     context_len = a.context
     max_b = 64 if not a.no_points else max(a.batch, 1)
     max_b = max(max_b, a.batch)
+    if a.serve:
+        max_b = a.serve
     pages_per_req = -(-(prompt_len + gen_len + 16) // 16)
     engine = EngineConfig(max_batch_tokens=2048, max_seqs=max_b, max_model_len=context_len, block_size=16,
                           num_pages=max_b * pages_per_req + 8, dtype="bfloat16", cuda_graphs=not a.no_graphs)
@@ -157,6 +200,8 @@ def main():
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(max_b)]
     never_stop = SamplingParams(max_new_tokens=gen_len, temperature=0.0, stop_token_ids=())
+    if a.serve:
+        return serve_run(a, llm, cfg, sz, layers, full_layers, gen_len, never_stop)
     PREFILL = min(2048, prompt_len)          # the timed prefill is one step of this many tokens
 
     def ev():

@@ -105,7 +105,7 @@ def serve_run(a, llm, cfg, sz, layers, full_layers, gen_len, params):
     g = torch.Generator().manual_seed(7)
     lens = torch.randint(a.serve_min, a.serve_max + 1, (a.serve,), generator=g).tolist()
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
-    llm.generate([p[:64] for p in prompts[:4]], params.__class__(max_new_tokens=8, temperature=0.0, stop_token_ids=()))  # warm-up
+    llm.generate(prompts, params)       # warm-up: the same run once (library handles, graphs of every batch class)
     torch.cuda.synchronize()
     sampler = ClockSampler()
     sampler.start()

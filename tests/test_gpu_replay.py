@@ -193,6 +193,39 @@ def test_four_ways_at_the_benchmark_layer_sizes(tmp_path_factory, dtype):
     print(f"1B sizes {dtype}: worst rel diff whole {w1:.2e} bulk+tail {w2:.2e} portions {w3:.2e} mixed {w4:.2e}")
 
 
+def test_mixed_step_sends_leading_single_tokens_to_the_decode_kernel(tmp_path_factory, monkeypatch):
+    """A mixed step whose first requests bring one token each: those rows go to the decode
+    attention kernel, the portions behind them (and a single token that follows a portion) to the
+    portion kernel. Same logits as the plain implementation either way."""
+    from vllm_oxide_b200 import kernels
+    dtype = torch.bfloat16
+    cfg, _, page = TINY["D"]
+    model_dir = make_model_dir(tmp_path_factory.getbasetemp(), "D")
+    reqs = _requests(cfg.vocab_size, [90, 70, 100, 40, 33], 500)
+    t = reqs
+    calls = []
+    real = kernels.attn_decode_mma
+    monkeypatch.setattr(kernels, "attn_decode_mma", lambda q, *a, **k: (calls.append(q.shape[0]), real(q, *a, **k))[1])
+    for split in (True, False):
+        s = _session(model_dir, dtype, 448, page)
+        for blk in s.runner.spec.blocks:
+            blk.mixer.split_mixed = split
+        steps = [
+            {"step": 0, "entries": [{"id": "r0", "tokens": t["r0"][:80], "want": [79]}, {"id": "r1", "tokens": t["r1"][:69], "want": []},
+                                    {"id": "r3", "tokens": t["r3"][:30], "want": [29]}], "end": []},
+            {"step": 1, "entries": [{"id": "r0", "tokens": t["r0"][80:81], "want": [0]}, {"id": "r1", "tokens": t["r1"][69:70], "want": [0]},
+                                    {"id": "r2", "tokens": t["r2"][:57], "want": [0, 56]}, {"id": "r3", "tokens": t["r3"][30:31], "want": [0]},
+                                    {"id": "r4", "tokens": t["r4"], "want": [32]}], "end": ["r1", "r4"]},
+            {"step": 2, "entries": [{"id": "r0", "tokens": t["r0"][81:82], "want": [0]}, {"id": "r3", "tokens": t["r3"][31:32], "want": [0]},
+                                    {"id": "r2", "tokens": t["r2"][57:], "want": [42]}], "end": ["r0", "r2", "r3"]},
+        ]
+        calls.clear()
+        check(run_trace(s, steps), model_dir, reqs, dtype, f"leading single tokens, split={split}")
+        layers = cfg.num_hidden_layers
+        assert calls == ([2] * layers + [2] * layers if split else []), calls
+        assert s.runner.manager.num_free_pages(0) == s.runner.manager.num_pages(0)
+
+
 def test_long_context_beside_a_short_one(tmp_path_factory):
     """Decode steps of a request of more than 6,144 keys beside a short one: the decode attention
     then shares a request's keys over up to 64 blocks that merge through global memory, and the

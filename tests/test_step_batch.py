@@ -44,6 +44,22 @@ def test_two_portions_flatten_like_the_reference():
     assert sec(a, "seeds", 4) == [0, 0, 9, 5] and sec(a, "sample_steps", 2) == [0, 3]
 
 
+def test_leading_single_tokens_are_counted():
+    """`lead_single`: how many requests at the front of the batch bring exactly one token (a
+    mixed step hands their rows to the decode attention kernel); one behind a portion does not count."""
+    c = rt.CacheManager(4, [rt.GroupSpec(rt.FULL, 0, 32)], 8)
+    for r in (1, 2, 3, 4):
+        c.admit(r)
+    for r in (1, 2, 4):
+        c.reserve(r, 5), c.commit(r, 5)
+    for r, n in ((1, 1), (2, 1), (3, 6), (4, 1)):
+        c.reserve(r, n)
+    e = [rt.StepEntry(1, [7], [0]), rt.StepEntry(2, [8], [0]), rt.StepEntry(3, [1, 2, 3, 4, 5, 6], [5]), rt.StepEntry(4, [9], [0])]
+    assert rt.build_step(c, e, 16, 8, 16, 8, 100).lead_single == 2
+    assert rt.build_step(c, e[2:], 16, 8, 16, 8, 100).lead_single == 0
+    assert rt.build_step(c, [e[0], e[1], e[3]], 16, 8, 16, 8, 100).lead_single == 3
+
+
 def test_refusals():
     c = rt.CacheManager(4, [rt.GroupSpec(rt.FULL, 0, 8)], 4)
     c.admit(1)

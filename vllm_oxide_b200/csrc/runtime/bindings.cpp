@@ -70,6 +70,7 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def_readonly("seqs", &StepArrays::seqs)
         .def_readonly("logit_count", &StepArrays::logit_count)
         .def_readonly("max_new", &StepArrays::max_new)
+        .def_readonly("lead_single", &StepArrays::lead_single)
         .def_readonly("max_seq_len", &StepArrays::max_seq_len)
         .def_readonly("any_sampling", &StepArrays::any_sampling)
         .def_readonly("ids", &StepArrays::ids)

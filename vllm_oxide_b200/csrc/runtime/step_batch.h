@@ -63,6 +63,7 @@ struct StepArrays {
     std::vector<int32_t> data;      // layout.total ints
     int rows = 0, seqs = 0, logit_count = 0;
     int max_new = 0;                // longest portion in the batch
+    int lead_single = 0;            // leading requests that bring exactly one token (rows 0 .. lead_single - 1)
     int64_t max_seq_len = 0;        // longest context after this step
     bool any_sampling = false;      // some row has temperature > 0
     std::vector<int64_t> ids;       // request of each sequence, in batch order
@@ -143,6 +144,7 @@ inline StepArrays build_step(const CacheManager& cache, const std::vector<StepEn
             ++lr;
         }
         A.max_new = std::max(A.max_new, n);
+        if (n == 1 && A.lead_single == (int)A.ids.size()) ++A.lead_single;
         A.max_seq_len = std::max<int64_t>(A.max_seq_len, ctx + n);
         A.ids.push_back(e.id);
         A.new_counts.push_back(n);

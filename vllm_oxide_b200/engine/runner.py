@@ -158,7 +158,8 @@ class ModelRunner:
             max_new=arrays.max_new if arrays is not None else 0,
             max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays,
             decode_only=bool(arrays is not None and arrays.max_new == 1 and arrays.rows == arrays.seqs),
-            long_context=bool(arrays is not None and arrays.max_seq_len > LONG_CONTEXT_KEYS))
+            long_context=bool(arrays is not None and arrays.max_seq_len > LONG_CONTEXT_KEYS),
+            lead_single=int(arrays.lead_single) if arrays is not None else 0)
 
     def upload(self, arrays) -> None:
         """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""

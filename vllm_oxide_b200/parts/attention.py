@@ -53,6 +53,7 @@ class Attention(Mixer):
         self.dtype = dtype
         self.impl = "auto"            # "general" forces the general attention kernel, "mma" the mma.sync kernels (tests)
         self.fused = True             # False forces the separate projection / rotary / cache-write kernels
+        self.split_mixed = True       # False sends a mixed step's single tokens through the portion kernel too (tests)
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
         # scratch of the decode kernel's merge through global memory (one or two requests with long
         # contexts): made at the first such step, kept; the counters are zero between launches
@@ -120,31 +121,46 @@ class Attention(Mixer):
 
     def attend(self, q, out, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with sizes the tensor-core kernels take: the decode kernel for steps of single
-        tokens; for everything else the tcgen05 kernel (head size 64, no window) or the mma.sync
-        portion kernel. Otherwise (float32, other head sizes) the general kernel."""
+        tokens; for everything else the tcgen05 kernel (head size 64 or 128, no window) or the
+        mma.sync portion kernel. In a mixed step the leading requests that bring one token each go
+        to the decode kernel and the portions behind them to the portion kernel (a single token is
+        a poor portion: one block would walk all its keys for four rows of a 128-row tile).
+        Otherwise (float32, other head sizes) the general kernel."""
         page = cache.k.shape[2]
         bt = ctx.block_tables[cache.group]
         if self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0:
-            if ctx.decode_only and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True):
-                splits, wide = self.decode_splits(ctx.rows, ctx.long_context)
-                if wide and self._partials is None:
-                    floats = kernels.attn_decode_partial_floats(1, 1, self.hd, 3 * self.num_sms)    # requests x kv heads x splits <= 3 SMs
-                    self._partials = torch.empty(floats, dtype=torch.float32, device=q.device)
-                    self._arrived = torch.zeros(self.num_sms, dtype=torch.int32, device=q.device)
-                kernels.attn_decode_mma(q, out, cache.k, cache.v, bt, ctx.positions, self.H, self.KV, self.hd, self.scale,
-                                        self.window, splits, self._partials if wide else None, self._arrived if wide else None)
+            decode_ok = kernels.attn_mma_supported(self.H, self.KV, self.hd, page, True)
+            if ctx.decode_only and decode_ok:
+                self._attend_single(q, out, ctx, cache, bt, ctx.rows)
                 return
+            lead = 0
+            if not ctx.decode_only and decode_ok and self.split_mixed and 0 < ctx.lead_single < ctx.seqs:
+                lead = ctx.lead_single
             if (not ctx.decode_only and ctx.max_new > 0 and self.window == 0 and self.impl != "mma"
                     and kernels.attn_prefill_sm100_supported(self.H, self.KV, self.hd, page, bt.shape[1])):
-                kernels.attn_prefill_sm100(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,
-                                           ctx.max_new, self.H, self.KV, self.hd, self.scale)
+                if lead:
+                    self._attend_single(q, out, ctx, cache, bt, lead)
+                kernels.attn_prefill_sm100(q, out, cache.k, cache.v, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:],
+                                           ctx.seqs - lead, ctx.max_new, self.H, self.KV, self.hd, self.scale)
                 return
             if not ctx.decode_only and ctx.max_new > 0 and kernels.attn_mma_supported(self.H, self.KV, self.hd, page, False):
-                kernels.attn_prefill_mma(q, out, cache.k, cache.v, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs,
-                                         ctx.max_new, self.H, self.KV, self.hd, self.scale, self.window)
+                if lead:
+                    self._attend_single(q, out, ctx, cache, bt, lead)
+                kernels.attn_prefill_mma(q, out, cache.k, cache.v, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:],
+                                         ctx.seqs - lead, ctx.max_new, self.H, self.KV, self.hd, self.scale, self.window)
                 return
         kernels.paged_attention(q, out, cache.k, cache.v, bt, ctx.row_seq, ctx.positions, self.H, self.KV, self.hd,
                                 self.scale, self.window)
+
+    def _attend_single(self, q, out, ctx: StepContext, cache: LayerCache, bt, count: int) -> None:
+        """The decode kernel on the first `count` rows, row i belonging to request i."""
+        splits, wide = self.decode_splits(count, ctx.long_context)
+        if wide and self._partials is None:
+            floats = kernels.attn_decode_partial_floats(1, 1, self.hd, 3 * self.num_sms)    # requests x kv heads x splits <= 3 SMs
+            self._partials = torch.empty(floats, dtype=torch.float32, device=q.device)
+            self._arrived = torch.zeros(self.num_sms, dtype=torch.int32, device=q.device)
+        kernels.attn_decode_mma(q[:count], out[:count], cache.k, cache.v, bt, ctx.positions[:count], self.H, self.KV, self.hd,
+                                self.scale, self.window, splits, self._partials if wide else None, self._arrived if wide else None)
 
     def decode_splits(self, num_seqs: int, long_context: bool = False):
         """(splits, wide): how many blocks share one request's keys in a decode step. Up to 8 blocks

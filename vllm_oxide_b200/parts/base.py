@@ -120,6 +120,8 @@ class StepContext:
     max_new: int = 0                # longest portion in the batch (host fact)
     max_seq_len: int = 0            # longest context after the step (host fact)
     decode_only: bool = False       # every request brings exactly one token and row i is request i
+    lead_single: int = 0            # the first so many requests bring exactly one token each (host fact):
+                                    # rows 0 .. lead_single - 1 are theirs, row i belonging to request i
     long_context: bool = False      # some request is longer than LONG_CONTEXT_KEYS (host fact; a replayed
                                     # step was recorded with the same value)
     host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them

@@ -105,7 +105,8 @@ def serve_run(a, llm, cfg, sz, layers, full_layers, gen_len, params):
     g = torch.Generator().manual_seed(7)
     lens = torch.randint(a.serve_min, a.serve_max + 1, (a.serve,), generator=g).tolist()
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
-    llm.generate(prompts, params)       # warm-up: the same run once (library handles, graphs of every batch class)
+    for _ in range(2):                  # warm-up: the same run twice (library handles; a step's shape class is
+        llm.generate(prompts, params)   # recorded as a CUDA graph when it comes the second time)
     torch.cuda.synchronize()
     sampler = ClockSampler()
     sampler.start()

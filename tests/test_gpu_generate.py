@@ -256,3 +256,25 @@ def test_generation_crosses_into_long_contexts(tmp_path_factory):
     assert kinds == {False, True}, kinds
     for g, w, p in zip(got, want, prompts):
         assert_same_or_near_tie(d, p, g.token_ids, w.token_ids, params, TOL[torch.bfloat16])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_replayed_from_graphs_give_the_same_tokens(tmp_path_factory, dtype):
+    """Steps that are no decode steps (portions of prompts, mixed batches) are recorded as CUDA
+    graphs when their shape class comes again, rows padded up to the class; the tokens are those of
+    steps launched one by one."""
+    name = "B" if dtype == "float32" else "D"
+    cfg, _, page = TINY[name]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), name)
+    # prompts of 130..150 tokens cut into portions of 48: every request brings portions of 48, 48
+    # and a rest that falls into one class of rows
+    prompts = [random_tokens(130 + 3 * i, cfg.vocab_size, 60 + i) for i in range(6)]
+    params = sp(max_new_tokens=6, stop_token_ids=())
+    kw = dict(max_batch_tokens=48, max_seqs=4, max_model_len=256, num_pages=4 * 256 // page)
+    want = [o.token_ids for o in llm_for(d, dtype, page, step_graphs=0, **kw).generate(prompts, params)]
+    llm = llm_for(d, dtype, page, step_graphs=2, **kw)
+    got = [o.token_ids for o in llm.generate(prompts, params)]
+    assert llm.runner.step_graph_replays > 4 and len(llm.runner._step_graphs) >= 1
+    for g, w, p in zip(got, want, prompts):
+        assert_same_or_near_tie(d, p, g, w, params, 0.0 if dtype == "float32" else TOL[torch.bfloat16])
+    assert llm.runner.manager.num_free_pages(0) == llm.runner.manager.num_pages(0)

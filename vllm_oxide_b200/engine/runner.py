@@ -13,6 +13,7 @@ residual; then the final norm and the head on the wanted rows only (:335-344).
 """
 from __future__ import annotations
 
+import collections
 import os
 from dataclasses import dataclass
 from typing import List, Optional
@@ -109,6 +110,10 @@ class ModelRunner:
         self.graphs_enabled = bool(engine.cuda_graphs)
         self.decode_layout = self.rt.step_layout(self.seqs_cap, self.seqs_cap, self.seqs_cap, G, self.max_pages)
         self._graphs = {}
+        self._step_graphs = collections.OrderedDict()    # shape class -> (graph, launches); least recently replayed first
+        self._step_seen = {}
+        self.step_graph_after = int(getattr(engine, "step_graphs", 0))
+        self.step_graph_replays = 0
         self._foldable = None
         self._folded = None
         self._graph_launches = {}
@@ -258,13 +263,66 @@ class ModelRunner:
                                        or logits_out.shape[1] != self.spec.vocab_size or logits_out.dtype != torch.float32):
             raise ShapeError("step", f"logits_out must be float32 [>={R}, {self.spec.vocab_size}]")
         self.upload(arrays)
+        shape = self._step_shape(arrays) if logits_out is None else None
+        if shape is not None:
+            entry = self._step_graphs.get(shape)
+            if entry is not None:
+                self._step_graphs.move_to_end(shape)
+                entry[0].replay()
+                kernels.count_launches(entry[1])
+                self.steps_run += 1
+                self.step_graph_replays += 1
+                return StepResult(self.sampled, None, R)
         self.workspace.reset()
         ctx = self.context(T, S, arrays)
         resid, pending = self._forward(ctx)
         if R:
             self._head(resid, pending, ctx, R, logits_out)
         self.steps_run += 1
+        if shape is not None:
+            seen = self._step_seen.get(shape, 0) + 1
+            self._step_seen[shape] = seen
+            if seen >= self.step_graph_after:
+                self._record_step(shape)
         return StepResult(self.sampled, logits_out, R)
+
+    # ------------------------------------------------------------------ other steps as CUDA graphs
+    STEP_GRAPHS_KEPT = 256
+
+    def _step_shape(self, arrays):
+        """The shape class of a step that is no decode step: everything its launches depend on
+        besides what lies in the step's device buffers. Rows are rounded up (the rows added are
+        padding: position -1, they attend to nothing and write nothing, as in a decode step's
+        graph) and so is the longest portion (kernels take it as an upper bound). None: this step
+        is not replayed (graphs off, a decode step, no logits wanted)."""
+        if not (self.graphs_enabled and self.step_graph_after > 0) or arrays.logit_count == 0:
+            return None
+        T, S = arrays.rows, arrays.seqs
+        if arrays.max_new == 1 and T == S:
+            return None
+        rows = min(16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else -(-T // 128) * 128, self.rows_cap)
+        longest = min(-(-arrays.max_new // 64) * 64, rows)
+        return (rows, S, arrays.logit_count, longest, int(arrays.lead_single), bool(arrays.max_seq_len > LONG_CONTEXT_KEYS))
+
+    def _record_step(self, shape) -> None:
+        """Record the launches of a step of this shape class (nothing runs while recording: the
+        step that asked for it has run already)."""
+        rows, S, R, longest, lead, long_context = shape
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = kernels.launch_count()
+        with torch.cuda.graph(g, pool=self._graph_pool):
+            self.workspace.reset()
+            ctx = self.context(rows, S, None)
+            ctx.max_new, ctx.lead_single, ctx.long_context = longest, lead, long_context
+            resid, pending = self._forward(ctx)
+            self._head(resid, pending, ctx, R, None)
+        launches = kernels.launch_count() - n0
+        kernels.count_launches(-launches)           # recorded, not run
+        self._graph_pool = self._graph_pool or g.pool()
+        self._step_graphs[shape] = (g, launches)
+        while len(self._step_graphs) > self.STEP_GRAPHS_KEPT:
+            self._step_graphs.popitem(last=False)   # the one replayed longest ago
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _bucket(self, n: int) -> int:

@@ -56,6 +56,10 @@ class LayerCache:
 
 
 # ------------------------------------------------------------------------------ per-step facts
+_ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8, torch.uint8: 1,
+                 torch.int8: 1, torch.float64: 8}
+
+
 class Workspace:
     """A bump allocator over one device buffer: a step's activations live here, so that a step
     allocates nothing and its tensors sit at the same addresses every time. The reference's
@@ -70,7 +74,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * _ELEMENT_SIZE[dtype]
         start = (self.top + 255) & ~255
         if start + nbytes > self.buf.numel():
             from ..errors import CapacityError

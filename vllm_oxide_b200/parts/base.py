@@ -106,7 +106,13 @@ class Workspace:
 class StepContext:
     """Everything a part may read about the current step. Device tensors are views into the
     step's packed int32 buffer; they hold `rows_cap` / `seqs_cap` entries of which the first
-    `rows` / `seqs` are real (the rest is padding that attends to nothing and writes nothing)."""
+    `rows` / `seqs` are real (the rest is padding that attends to nothing and writes nothing).
+
+    Steps are recorded as CUDA graphs and replayed for later steps of the same shape class, so
+    what a part launches may depend only on the host facts below that make up the class (`rows`,
+    `seqs`, `max_new` as an upper bound, `decode_only`, `lead_single`, `long_context`) and on its
+    own constants; everything else must be read on the device, from the tensors. `max_seq_len`
+    and `host` are there for checks and debugging only (a recording is made with neither)."""
     rows: int                       # rows the kernels run over (real rows, or the padded count)
     seqs: int
     dtype: torch.dtype              # compute dtype of activations and cache

@@ -18,7 +18,6 @@ import os
 from dataclasses import dataclass
 from typing import List, Optional
 
-import numpy as np
 import torch
 
 from .. import kernels

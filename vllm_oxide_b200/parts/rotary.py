@@ -10,7 +10,6 @@ is computed in float64 and rounded. The rotation (rotate-half pairing, angle = f
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import numpy as np
 import torch

@@ -9,7 +9,7 @@ crates/engine/src/generate.rs:46-47).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
 

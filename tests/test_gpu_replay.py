@@ -193,6 +193,22 @@ def test_four_ways_at_the_benchmark_layer_sizes(tmp_path_factory, dtype):
     print(f"1B sizes {dtype}: worst rel diff whole {w1:.2e} bulk+tail {w2:.2e} portions {w3:.2e} mixed {w4:.2e}")
 
 
+def test_four_ways_at_head_size_128(tmp_path_factory):
+    """Head size 128 with three heads per kv head at a real width (hidden 3072): the tcgen05
+    portion kernel's second instantiation and the decode kernel's, inside the engine, cut four ways."""
+    dtype = torch.bfloat16
+    cfg, _, page = TINY["HD128"]
+    model_dir = make_model_dir(tmp_path_factory.getbasetemp(), "HD128")
+    reqs = _requests(cfg.vocab_size, [170, 45], 31)
+    s = _session(model_dir, dtype, 320, page)
+    w1 = check(run_trace(s, whole_steps(reqs)), model_dir, reqs, dtype, "whole")
+    w2 = check(run_trace(s, bulk_tail_steps(reqs)), model_dir, reqs, dtype, "bulk+tail")
+    w3 = check(run_trace(s, portion_steps(reqs, sizes=(64, 7, 2, 33, 3, 16, 2, 1, 40))), model_dir, reqs, dtype, "portions")
+    w4 = check(run_trace(s, mixed_steps(reqs, seed=5)), model_dir, reqs, dtype, "mixed")
+    assert s.runner.manager.num_free_pages(0) == s.runner.manager.num_pages(0)
+    print(f"head size 128: worst rel diff whole {w1:.2e} bulk+tail {w2:.2e} portions {w3:.2e} mixed {w4:.2e}")
+
+
 def test_mixed_step_sends_leading_single_tokens_to_the_decode_kernel(tmp_path_factory, monkeypatch):
     """A mixed step whose first requests bring one token each: those rows go to the decode
     attention kernel, the portions behind them (and a single token that follows a portion) to the

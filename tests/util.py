@@ -44,7 +44,14 @@ LAYERS_1B = LlamaConfig(
 # TINY_D for contexts of thousands of keys (the decode kernels choose by context length)
 TINY_D_LONG = dataclasses.replace(TINY_D, max_position_embeddings=16384)
 
-TINY = {"A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16),
+# Two layers of a wider model with head size 128 and three heads per kv head (Llama 3.2 3B's
+# attention sizes; vocabulary and feed-forward kept small for the plain implementation), untied head
+LAYERS_HD128 = LlamaConfig(
+    hidden_size=3072, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=24, num_key_value_heads=8,
+    head_dim=128, vocab_size=1000, max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192), tie_word_embeddings=False)
+
+TINY = {"HD128": (LAYERS_HD128, 0.02, 16), "A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16),
         "DL": (TINY_D_LONG, 0.05, 16), "1B": (LAYERS_1B, 0.02, 16)}   # config, std, page size
 
 
@@ -54,7 +61,7 @@ def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:
     if not os.path.exists(os.path.join(d, "model.safetensors")):
         # larger weights than a checkpoint's so that attention is far from uniform and a wrong
         # key or a stale page changes the logits visibly; norm weights away from 1
-        write_random_model(d, cfg, seed, std=(std if std is not None else (s if name == "1B" else max(s, 0.08))), norm_jitter=0.3)
+        write_random_model(d, cfg, seed, std=(std if std is not None else (s if name in ("1B", "HD128") else max(s, 0.08))), norm_jitter=0.3)
     return d
 
 

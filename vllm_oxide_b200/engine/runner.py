@@ -279,6 +279,8 @@ class ModelRunner:
             self._head(resid, pending, ctx, R, logits_out)
         self.steps_run += 1
         if shape is not None:
+            if len(self._step_seen) > 4096:
+                self._step_seen.clear()                 # a count per shape class ever seen: keep it bounded
             seen = self._step_seen.get(shape, 0) + 1
             self._step_seen[shape] = seen
             if seen >= self.step_graph_after:

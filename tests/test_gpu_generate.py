@@ -278,3 +278,34 @@ def test_steps_replayed_from_graphs_give_the_same_tokens(tmp_path_factory, dtype
     for g, w, p in zip(got, want, prompts):
         assert_same_or_near_tie(d, p, g, w, params, 0.0 if dtype == "float32" else TOL[torch.bfloat16])
     assert llm.runner.manager.num_free_pages(0) == llm.runner.manager.num_pages(0)
+
+
+def test_tight_pool_and_replayed_steps_change_no_token_in_f32():
+    """Forty requests of 5 to 700 tokens, greedy and with temperature, once with room for all and
+    steps launched one by one, once with a pool so tight that requests are preempted and
+    recomputed, a smaller token budget, and every step that is no decode step recorded as a CUDA
+    graph at its first sighting: in float32 the tokens are the same to the last one, nothing leaks."""
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import EngineConfig, LlamaConfig
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    cfg = LlamaConfig(hidden_size=192, intermediate_size=320, num_hidden_layers=3, num_attention_heads=6,
+                      num_key_value_heads=2, head_dim=32, vocab_size=1000, max_position_embeddings=4096,
+                      rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None, tie_word_embeddings=False)
+    tensors = random_tensors(models.llama_manifest(cfg), 0, 0.08, torch.float32, "cuda:0")
+    n = 40
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(5, 700, (n,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (k,), generator=g).tolist() for k in lens]
+    params = [sp(max_new_tokens=40 + i % 30, temperature=0.0 if i % 3 else 0.8, seed=i, stop_token_ids=()) for i in range(n)]
+    outs = []
+    for pages, graphs_after, budget in ((n * 64, 0, 512), (300, 1, 256)):
+        eng = EngineConfig(max_batch_tokens=budget, max_seqs=16, max_model_len=1024, num_pages=pages, step_graphs=graphs_after,
+                           dtype="float32")
+        llm = LLM(ModelRunner(cfg, tensors, eng))
+        outs.append([o.token_ids for o in llm.generate(prompts, params)])
+        r = llm.runner
+        assert r.manager.check_invariants() == "" and r.manager.num_free_pages(0) == r.manager.num_pages(0)
+        if graphs_after:
+            assert llm.stats["preemptions"] > 0 and r.step_graph_replays > 0
+    assert outs[0] == outs[1]

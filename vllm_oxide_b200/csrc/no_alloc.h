@@ -34,7 +34,7 @@
 #include <stdint.h>
 
 #define VOB_PICK_STATIC_MAX_ROWS 64
-#define VOB_PICK_STATIC_MAX_SPLITS 64
+#define VOB_PICK_STATIC_MAX_SPLITS 256
 // per row and split one float and one int, plus one int per row for the NaN mark
 #define VOB_PICK_STATIC_BYTES (VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 8 + VOB_PICK_STATIC_MAX_ROWS * 4)
 #define VOB_ERR_STATIC_TOO_LARGE 2003

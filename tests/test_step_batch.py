@@ -87,3 +87,19 @@ def test_layout_is_a_function_of_the_capacities():
     offs = [a["tokens"], a["positions"], a["row_seq"], a["seq_starts"], a["context_lens"], a["seq_lens"],
             a["state_slots"], a["logit_rows"], a["temperature"], a["seeds"], a["sample_steps"]] + a["slot_mapping"] + a["block_tables"]
     assert len(set(offs)) == len(offs) and all(o % 4 == 0 and o < a["total"] for o in offs)
+
+
+def test_shape_class_of_a_step():
+    """What a recorded step is replayed for: rows are padded up, the longest portion is an upper
+    bound, requests / wanted rows / leading single tokens are exact; decode steps have their own graphs."""
+    from vllm_oxide_b200.engine.runner import step_shape_class
+    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    assert step_shape_class(8, 8, 8, 1, 8, 300, 2048) is None                 # a decode step
+    assert step_shape_class(100, 2, 0, 60, 0, 300, 2048) is None              # no logits wanted
+    assert step_shape_class(1, 1, 1, 1, 1, 5, 2048) is None
+    assert step_shape_class(9, 2, 2, 8, 1, 40, 2048) == (16, 2, 2, 16, 1, False)
+    assert step_shape_class(33, 3, 3, 20, 2, 40, 2048) == (64, 3, 3, 64, 2, False)
+    assert step_shape_class(2048, 1, 1, 2048, 0, 2048, 2048) == (2048, 1, 1, 2048, 0, False)
+    assert step_shape_class(1999, 5, 4, 1930, 3, LONG_CONTEXT_KEYS + 1, 2048) == (2048, 5, 4, 1984, 3, True)
+    assert step_shape_class(130, 2, 2, 129, 0, 500, 192) == (192, 2, 2, 192, 0, False)    # never beyond the engine's rows
+    assert step_shape_class(40, 4, 4, 37, 0, 90, 48) == (48, 4, 4, 48, 0, False)

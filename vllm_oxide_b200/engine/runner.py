@@ -40,6 +40,19 @@ class StepResult:
         return self.sampled[:self.num_logit_rows].tolist()
 
 
+def step_shape_class(rows: int, seqs: int, logit_count: int, max_new: int, lead_single: int, max_seq_len: int,
+                     rows_cap: int):
+    """The shape class under which a step that is no decode step is recorded and replayed:
+    (rows rounded up to 16 / 32 / 64 / a multiple of 128, never beyond `rows_cap`; requests; wanted
+    rows; the longest portion rounded up to 64, never beyond the rows; leading single tokens; long
+    contexts or not). None for a decode step and for a step that wants no logits."""
+    if logit_count == 0 or (max_new == 1 and rows == seqs):
+        return None
+    padded = min(16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else -(-rows // 128) * 128, rows_cap)
+    longest = min(-(-max_new // 64) * 64, padded)
+    return (padded, seqs, logit_count, longest, int(lead_single), bool(max_seq_len > LONG_CONTEXT_KEYS))
+
+
 def _require_cuda(device: str) -> None:
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device is available; this engine has no CPU path")
@@ -296,14 +309,10 @@ class ModelRunner:
         padding: position -1, they attend to nothing and write nothing, as in a decode step's
         graph) and so is the longest portion (kernels take it as an upper bound). None: this step
         is not replayed (graphs off, a decode step, no logits wanted)."""
-        if not (self.graphs_enabled and self.step_graph_after > 0) or arrays.logit_count == 0:
+        if not (self.graphs_enabled and self.step_graph_after > 0):
             return None
-        T, S = arrays.rows, arrays.seqs
-        if arrays.max_new == 1 and T == S:
-            return None
-        rows = min(16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else -(-T // 128) * 128, self.rows_cap)
-        longest = min(-(-arrays.max_new // 64) * 64, rows)
-        return (rows, S, arrays.logit_count, longest, int(arrays.lead_single), bool(arrays.max_seq_len > LONG_CONTEXT_KEYS))
+        return step_shape_class(arrays.rows, arrays.seqs, arrays.logit_count, arrays.max_new, arrays.lead_single,
+                                arrays.max_seq_len, self.rows_cap)
 
     def _record_step(self, shape) -> None:
         """Record the launches of a step of this shape class (nothing runs while recording: the

@@ -309,3 +309,23 @@ def test_tight_pool_and_replayed_steps_change_no_token_in_f32():
         if graphs_after:
             assert llm.stats["preemptions"] > 0 and r.step_graph_replays > 0
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_tokens_are_reported_as_they_are_read(tmp_path_factory, run_ahead):
+    """`on_token`: every generated token once, in order, the stop token included, nothing that was
+    computed past a stop token; with and without steps launched ahead."""
+    cfg, _, page = TINY["B"]
+    d = make_model_dir(tmp_path_factory.getbasetemp(), "B")
+    prompts = [random_tokens(L, cfg.vocab_size, 800 + i) for i, L in enumerate([4, 13, 30, 9])]
+    base = llm_for(d, "float32", page, run_ahead=False)
+    full = [o.token_ids for o in base.generate(prompts, sp(max_new_tokens=24, stop_token_ids=()))]
+    params = [sp(max_new_tokens=24, stop_token_ids=(full[i][5 + 4 * i],)) if i < 3 else sp(max_new_tokens=24, stop_token_ids=())
+              for i in range(4)]
+    llm = llm_for(d, "float32", page, run_ahead=run_ahead)
+    seen = {i: [] for i in range(4)}
+    outs = llm.generate(prompts, params, on_token=lambda i, tok: seen[i].append(tok))
+    assert [o.finish_reason for o in outs] == ["stop", "stop", "stop", "length"]
+    assert [seen[i] for i in range(4)] == [o.token_ids for o in outs]
+    assert llm.on_token is None
+    assert (llm.stats["ahead_steps"] > 0) == run_ahead

@@ -60,6 +60,9 @@ class LLM:
         self._generated: Dict[int, int] = {}
         self._preempt: Dict[int, int] = {}
         self._tokenizer = None
+        # called as on_token(request id, token) for every generated token as soon as the host has read
+        # it, in generation order per request (a token computed past a stop token is never reported)
+        self.on_token = None
         self._logit_buf = None
         self._inflight = None            # a decode step launched but not read yet: (plan, ids, parity, event)
         self._late: List[RequestOutput] = []
@@ -170,6 +173,10 @@ class LLM:
         sampled = self.runner.read_decode(event, len(ids), parity)
         if min(sampled, default=0) < 0:
             raise NaNError("pick_tokens")            # crates/engine/src/backend/cpu/mod.rs:377-379
+        if self.on_token is not None:
+            for rid, tok in zip(ids, sampled):
+                if rid in self._params:              # not one that ended on a stop token a step earlier
+                    self.on_token(rid, tok)
         return self._outputs(self.scheduler.resolve(plan, sampled, ahead))
 
     def _finish_inflight(self) -> None:
@@ -216,6 +223,9 @@ class LLM:
             gen = self._generated
             for rid in sampling:
                 gen[rid] += 1
+            if self.on_token is not None:
+                for rid, tok in zip(sampling, sampled):
+                    self.on_token(rid, tok)
             done = sched.update(plan, sampled)
         else:
             done = sched.take_done()
@@ -270,8 +280,10 @@ class LLM:
             d.pop(rid, None)
 
     # ------------------------------------------------------------------ whole jobs
-    def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:
-        """Run every prompt to its end; outputs come back in the order of `prompts`."""
+    def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 on_token=None) -> List[RequestOutput]:
+        """Run every prompt to its end; outputs come back in the order of `prompts`. `on_token(index
+        of the prompt, token)` is called for every generated token as soon as the host has read it."""
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         if sampling_params is None:
@@ -281,9 +293,15 @@ class LLM:
             raise ShapeError("generate", f"{len(prompts)} prompts but {len(plist)} sampling parameter sets")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         results: Dict[int, RequestOutput] = {}
-        while self.has_unfinished():
-            for out in self.step():
-                results[out.request_id] = out
+        mine, before = {rid: i for i, rid in enumerate(ids)}, self.on_token
+        if on_token is not None:
+            self.on_token = lambda rid, tok: on_token(mine[rid], tok) if rid in mine else None
+        try:
+            while self.has_unfinished():
+                for out in self.step():
+                    results[out.request_id] = out
+        finally:
+            self.on_token = before
         self.runner.check_kernels()
         return [results[i] for i in ids]
 

@@ -80,9 +80,11 @@ class ModelRunner:
         else:
             weights = weights_from_tensors(tensors_or_dir, manifest)
         kernels.set_pdl(bool(engine.pdl))
-        kernels.preload(kernels.modules_for(self.dtype))
         self.spec: ModelSpec = arch.build(config, weights, BuildContext(dtype=self.dtype, device=self.device))
         del weights
+        # what this model needs is compiled now, side by side (a fresh checkout has nothing built)
+        head_dims = {getattr(b.mixer, "hd", 0) for b in self.spec.blocks if hasattr(b, "mixer")}
+        kernels.preload(kernels.modules_for(self.dtype, head_dims, engine.max_batch_tokens))
         # As in the reference, the longest sequence is the engine's limit, not config.json's
         # max_position_embeddings (crates/engine/src/backend/cpu/mod.rs:49-54): rotation angles are
         # computed from the position itself, so no table length binds them.

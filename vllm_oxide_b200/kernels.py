@@ -157,12 +157,21 @@ def _fn(module: str, name: str, argtypes):
 _pdl_on = False
 
 
-def modules_for(dtype) -> tuple:
-    """The kernel modules an engine of this compute dtype uses: only these are compiled at its
-    first start."""
+TENSOR_CORE_HEAD_DIMS = (64, 128)       # head sizes the tensor-core attention kernels are built for
+
+
+def modules_for(dtype, head_dims=(), max_rows: Optional[int] = None) -> tuple:
+    """The kernel modules an engine uses, by its compute dtype, the head sizes of its attention
+    mixers and the most rows a step may have: only these are compiled (side by side) at its first
+    start. Anything else a step turns out to need is still built when it is first called."""
     if dtype == torch.float32:
         return ("elementwise", "gemm_f32", "attention", "sampling")
-    return ("elementwise", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling")
+    mods = ["elementwise", "gemm_sm100", "attention", "sampling"]
+    if max_rows is None or max_rows >= PAIR_GEMM_FROM_ROWS:
+        mods.append("gemm_sm100_pair")
+    if any(hd in TENSOR_CORE_HEAD_DIMS for hd in head_dims):
+        mods += ["attention_mma", "attention_sm100"]
+    return tuple(mods)
 
 
 def preload(modules=_MODULES) -> None:
@@ -747,6 +756,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
 
 def attn_mma_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, decode: bool) -> bool:
     """Whether the tensor-core attention kernels take these sizes (bfloat16 only)."""
+    if head_dim not in TENSOR_CORE_HEAD_DIMS:
+        return False                      # answered here: a model of another head size never builds the module
     f = _fn("attention_mma", "vob_attn_mma_supported", [_I, _I, _I, _I, _I])
     return bool(f(num_heads, num_kv_heads, head_dim, page_size, int(decode)))
 
@@ -797,6 +808,8 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
 
 def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:
     """Whether the tcgen05 attention kernel for prompt portions takes these sizes (bfloat16, no window)."""
+    if head_dim not in TENSOR_CORE_HEAD_DIMS:
+        return False
     f = _fn("attention_sm100", "vob_attn_prefill_sm100_supported", [_I, _I, _I, _I, _I])
     return bool(f(num_heads, num_kv_heads, head_dim, page_size, max_pages))
 

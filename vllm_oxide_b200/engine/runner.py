@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import collections
 import os
+import sys
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -299,7 +300,13 @@ class ModelRunner:
             seen = self._step_seen.get(shape, 0) + 1
             self._step_seen[shape] = seen
             if seen >= self.step_graph_after:
-                self._record_step(shape)
+                try:
+                    self._record_step(shape)
+                except Exception as e:      # a part that cannot be recorded (it reads device data on the host, say)
+                    self.step_graph_after = 0
+                    self._step_graphs.clear()
+                    print(f"[vllm_oxide_b200] steps are not recorded as CUDA graphs from here on: {type(e).__name__}: {e}",
+                          file=sys.stderr, flush=True)
         return StepResult(self.sampled, logits_out, R)
 
     # ------------------------------------------------------------------ other steps as CUDA graphs

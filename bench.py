@@ -92,7 +92,7 @@ def reference_arm():
     # no GPU code; neither pip nor cargo can build it on this machine.
     print(json.dumps({"impl": "reference", "unavailable":
                       "the reference is a CPU-only Rust workspace (no setup.py/pyproject, no cargo/rustc here); "
-                      "pip install of /root/reference fails and it has no GPU path to run"}))
+                      "pip install of its source tree fails and it has no GPU path to run"}))
     return 0
 
 

@@ -304,3 +304,64 @@ def test_steady_decode_is_false_whenever_the_next_step_could_differ():
     s2.add_request(2, [1], sp(6))
     run_step(s2)
     assert c2.num_free_pages(0) == 0 and not s2.steady_decode()      # no free page for every running request
+
+
+def test_admission_watermark_keeps_room_for_the_running_requests():
+    """With a watermark a waiting request is admitted only if so many pages stay free behind its
+    first portion while others run; alone it is admitted anyway; 0 admits whenever a token fits."""
+    c, s = make(pages=8, page=4, budget=64, max_len=64)
+    s.set_admission_watermark(3)
+    assert s.admission_watermark() == 3
+    s.add_request(1, list(range(8)), sp(20))        # 2 pages
+    s.add_request(2, list(range(12)), sp(4))        # 3 pages: 8 - 2 - 3 = 3 would stay free: admitted
+    s.add_request(3, list(range(4)), sp(4))         # 1 page: 3 - 1 = 2 < 3: waits
+    plan, _ = run_step(s)
+    assert plan.admitted == [1, 2] and s.waiting() == [3]
+    assert c.check_invariants() == ""
+    # request 3 comes in once request 2 has finished and given its pages back
+    admitted_at = None
+    for step in range(40):
+        plan, done = run_step(s)
+        if 3 in plan.admitted:
+            admitted_at = step
+            assert 2 not in s.running()
+            break
+    assert admitted_at is not None
+    while s.has_unfinished():
+        run_step(s)
+    assert c.num_free_pages(0) == 8 and c.check_invariants() == ""
+    # nothing runs: the watermark does not hold a request back
+    c2, s2 = make(pages=4, page=4, budget=64, max_len=64)
+    s2.set_admission_watermark(3)
+    s2.add_request(7, list(range(10)), sp(2))       # 3 pages of 4: only 1 would stay free
+    plan, _ = run_step(s2)
+    assert plan.admitted == [7]
+    with pytest.raises(rt.RuntimeFault):
+        s2.set_admission_watermark(-1)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_traces_with_a_watermark_finish_everything_with_fewer_preemptions(seed):
+    def run(watermark):
+        rng = random.Random(seed)
+        c, s = make(pages=24, page=4, slots=5, budget=16, max_seqs=5, max_len=96)
+        s.set_admission_watermark(watermark)
+        want, got, preempted = {}, {}, 0
+        for rid in range(20):
+            n = rng.randrange(4, 20)
+            s.add_request(rid, [rng.randrange(50) for _ in range(rng.randrange(1, 40))], sp(n))
+            want[rid] = n
+        for step in range(4000):
+            if not s.has_unfinished():
+                break
+            plan, done = run_step(s, token=lambda rid, k: rid)
+            preempted += len(plan.preempted)
+            for f in done:
+                got[f.id] = f
+            assert c.check_invariants() == ""
+        assert not s.has_unfinished() and c.num_free_pages(0) == 24
+        assert {i: len(f.output) for i, f in got.items()} == want
+        assert all(f.output == [i] * want[i] for i, f in got.items())
+        return preempted
+    without, with_room = run(0), run(4)
+    assert with_room <= without

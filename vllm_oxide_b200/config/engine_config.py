@@ -44,6 +44,8 @@ class EngineConfig:
     num_pages: Optional[int] = None    # explicit page count per cache group
     dtype: torch.dtype = torch.bfloat16
     prefill_chunk: Optional[int] = None  # most prompt tokens of one request per step
+    admission_watermark_pages: int = 0   # while others run, admit a request only if so many pages stay free behind
+                                         # its first portion (0: whenever a token fits)
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
     pdl: bool = True                   # programmatic dependent launch between the engine's kernels
     fold_norms: bool = True            # steps of few rows: norms and residual adds folded into the products
@@ -64,3 +66,5 @@ class EngineConfig:
             raise ConfigError("engine config: num_pages must be positive")
         if self.prefill_chunk is not None and self.prefill_chunk <= 0:
             raise ConfigError("engine config: prefill_chunk must be positive")
+        if self.admission_watermark_pages < 0:
+            raise ConfigError("engine config: admission_watermark_pages cannot be negative")

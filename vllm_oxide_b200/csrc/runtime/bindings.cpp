@@ -128,6 +128,8 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def(py::init<CacheManager*, int, int, int, int>(), py::arg("cache"), py::arg("max_batch_tokens"),
              py::arg("max_seqs"), py::arg("max_model_len"), py::arg("prefill_chunk") = 0, py::keep_alive<1, 2>())
         .def("add_request", &Scheduler::add_request)
+        .def("set_admission_watermark", &Scheduler::set_admission_watermark)
+        .def("admission_watermark", &Scheduler::admission_watermark)
         .def("has_unfinished", &Scheduler::has_unfinished)
         .def("num_waiting", &Scheduler::num_waiting)
         .def("num_running", &Scheduler::num_running)

@@ -103,6 +103,15 @@ public:
         waiting_.push_back(id);
     }
 
+    // Admission watermark: while other requests run, a waiting request is admitted only if so many
+    // pages of every group stay free behind its first portion (room for the running requests to
+    // grow, so that the newcomer is not preempted again at once). 0: admit whenever a token fits.
+    void set_admission_watermark(int pages) {
+        if (pages < 0) throw CacheError("scheduler: the admission watermark cannot be negative");
+        watermark_pages_ = pages;
+    }
+    int admission_watermark() const { return watermark_pages_; }
+
     bool has_unfinished() const { return !waiting_.empty() || !running_.empty(); }
     size_t num_waiting() const { return waiting_.size(); }
     size_t num_running() const { return running_.size(); }
@@ -161,6 +170,15 @@ public:
                 plan.failed.emplace_back(id, "capacity");
                 requests_.erase(id);
                 continue;
+            }
+            if (watermark_pages_ > 0 && !running_.empty()) {
+                bool room = true;
+                for (int g = 0; g < cache_->num_groups(); ++g)
+                    if (cache_->num_free_pages(g) - cache_->pages_to_add(id, g, n) < watermark_pages_) room = false;
+                if (!room) {
+                    cache_->release(id);
+                    break;                             // wait until the running requests have given pages back
+                }
             }
             cache_->reserve(id, n);
             waiting_.pop_front();
@@ -340,6 +358,7 @@ private:
 
     CacheManager* cache_;
     int max_batch_tokens_, max_seqs_, max_model_len_, prefill_chunk_;
+    int watermark_pages_ = 0;
     std::map<int64_t, Request> requests_;
     std::deque<int64_t> waiting_;
     std::vector<int64_t> running_;

@@ -53,6 +53,7 @@ class LLM:
         e = r.engine
         self.scheduler = r.rt.Scheduler(r.manager, e.max_batch_tokens, e.max_seqs, r.max_model_len,
                                         e.prefill_chunk or 0)
+        self.scheduler.set_admission_watermark(int(getattr(e, "admission_watermark_pages", 0)))
         self._next_id = 0
         self._params: Dict[int, SamplingParams] = {}
         self._prompts: Dict[int, List[int]] = {}

@@ -121,3 +121,40 @@ def test_take_and_finish():
         w.finish()
     with pytest.raises(WeightsError):
         w.take("zzz")
+
+
+def test_checkpoint_in_shards(tmp_path):
+    """A folder without model.safetensors but with model.safetensors.index.json: the shards its
+    weight_map names are read as one checkpoint, and one error still lists everything wrong."""
+    import json
+    from vllm_oxide_b200.weights import write_safetensors
+    manifest = llama_manifest(TINY_A)
+    tensors = random_tensors(manifest, seed=5, std=0.05)
+    names = sorted(tensors)
+    cut = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:cut], "model-00002-of-00002.safetensors": names[cut:]}
+    d = tmp_path / "sharded"
+    d.mkdir()
+    for fn, ns in shards.items():
+        write_safetensors(str(d / fn), {n: tensors[n] for n in ns})
+    (d / "model.safetensors.index.json").write_text(json.dumps(
+        {"metadata": {"total_size": 0}, "weight_map": {n: fn for fn, ns in shards.items() for n in ns}}))
+    ws = load_safetensors_weights(str(d), manifest)
+    for n in names:
+        assert torch.equal(ws.take(n), tensors[n])
+    ws.finish()
+    # a tensor missing from its shard, one left over, and one stored twice
+    gone, extra = shards["model-00002-of-00002.safetensors"][0], "model.layers.9.extra.weight"
+    second = {n: tensors[n] for n in shards["model-00002-of-00002.safetensors"] if n != gone}
+    second[extra] = torch.zeros(2, dtype=torch.bfloat16)
+    write_safetensors(str(d / "model-00002-of-00002.safetensors"), second)
+    with pytest.raises(WeightsError) as e:
+        load_safetensors_weights(str(d), manifest)
+    assert e.value.missing == [gone] and e.value.unexpected == [extra]
+    second[names[0]] = tensors[names[0]]
+    write_safetensors(str(d / "model-00002-of-00002.safetensors"), second)
+    with pytest.raises(WeightsError, match="more than one shard"):
+        load_safetensors_weights(str(d), manifest)
+    (d / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(WeightsFormatError, match="not a shard index"):
+        load_safetensors_weights(str(d), manifest)

@@ -12,13 +12,14 @@ whose dtype differs from the compute dtype is the part's business.
 """
 from __future__ import annotations
 
+import json
 import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, Mapping, Optional, Tuple
 
 import torch
 
-from ..errors import WeightsError
+from ..errors import WeightsError, WeightsFormatError
 from .safetensors_io import SafetensorsFile
 
 _FLOAT_NAMES = ("BF16", "F16", "F32")
@@ -90,23 +91,52 @@ def check_against_manifest(source: str, found: Mapping[str, Tuple[Tuple[int, ...
         raise WeightsError(source, missing, unexpected, wrong_shape, wrong_dtype)
 
 
+def _checkpoint_files(model_dir: str):
+    """The safetensors files of a model folder: `model.safetensors`, or, for a checkpoint in
+    shards, the files that `model.safetensors.index.json` names (its `weight_map` gives the shard
+    of every tensor; the reference reads a single file only, crates/engine/src/weights.rs:139-150).
+    Returns (source name for messages, [paths])."""
+    single = os.path.join(model_dir, "model.safetensors")
+    index = os.path.join(model_dir, "model.safetensors.index.json")
+    if os.path.exists(single) or not os.path.exists(index):
+        return single, [single]
+    try:
+        with open(index) as f:
+            weight_map = json.load(f)["weight_map"]
+        shards = sorted(set(weight_map.values()))
+        if not shards or not all(isinstance(x, str) for x in shards):
+            raise ValueError("empty weight_map")
+    except (OSError, ValueError, KeyError, TypeError, AttributeError) as e:
+        raise WeightsFormatError(f"{index}: not a shard index ({type(e).__name__}: {e})") from None
+    return index, [os.path.join(model_dir, os.path.basename(x)) for x in shards]
+
+
 def load_safetensors_weights(model_dir: str, manifest: Mapping[str, TensorSpec],
                              device: Optional[str] = None) -> WeightSet:
-    """Read <model_dir>/model.safetensors, check it against the manifest, return a WeightSet.
+    """Read <model_dir>/model.safetensors (or the shards its index names), check what was found
+    against the manifest, return a WeightSet.
 
-    With `device`, tensors are copied there (the file mapping is not kept); without, they are
+    With `device`, tensors are copied there (the file mappings are not kept); without, they are
     private CPU copies."""
-    path = os.path.join(model_dir, "model.safetensors")
-    f = SafetensorsFile(path)
-    found = {n: (f.shape(n), f.dtype_name(n)) for n in f.names()}
-    check_against_manifest(path, found, manifest)
+    source, paths = _checkpoint_files(model_dir)
+    files = [SafetensorsFile(p) for p in paths]
+    where, found, twice = {}, {}, []
+    for f in files:
+        for n in f.names():
+            if n in where:
+                twice.append(n)
+            where[n] = f
+            found[n] = (f.shape(n), f.dtype_name(n))
+    if twice:
+        raise WeightsError(source, other=["stored in more than one shard: " + ", ".join(sorted(twice))])
+    check_against_manifest(source, found, manifest)
     out = {}
     for n, spec in manifest.items():
-        t = f.tensor(n)
-        t = _normalise(t, spec.kind)
+        t = _normalise(where[n].tensor(n), spec.kind)
         out[n] = t.to(device) if device is not None else t.clone()
-    f.close()
-    return WeightSet(out, path)
+    for f in files:
+        f.close()
+    return WeightSet(out, source)
 
 
 def weights_from_tensors(tensors: Mapping[str, torch.Tensor], manifest: Mapping[str, TensorSpec],

@@ -69,6 +69,9 @@ def test_missing_required_key(key):
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "llama3"),
     ({"rope_scaling": {"rope_type": "llama3", "factor": 2.0}}, "low_freq_factor"),
     ({"sliding_window": 4096}, "sliding_window"), ({"tie_word_embeddings": "yes"}, "true or false"),
+    ({"sliding_window": 1}, "sliding_window"), ({"attention_dropout": 1}, "attention_dropout"),
+    ({"attention_dropout": 0.1}, "attention_dropout"), ({"pretraining_tp": 2}, "pretraining_tp"),
+    ({"pretraining_tp": 0}, "pretraining_tp"), ({"sliding_window": True}, "sliding_window"),
     ({"eos_token_id": "x"}, "eos_token_id"), ({"architectures": []}, "architectures"),
 ])
 def test_bad_values_are_refused(patch, match):
@@ -76,6 +79,14 @@ def test_bad_values_are_refused(patch, match):
     d.update(patch)
     with pytest.raises(ConfigError, match=match):
         LlamaConfig.from_dict(d)
+
+
+@pytest.mark.parametrize("patch", [{"sliding_window": None}, {"sliding_window": 0}, {"attention_dropout": 0.0},
+                                   {"attention_dropout": 0}, {"pretraining_tp": 1}, {"pretraining_tp": None}])
+def test_off_values_of_unsupported_features_pass(patch):
+    d = dict(LLAMA_1B)
+    d.update(patch)
+    LlamaConfig.from_dict(d)
 
 
 def test_registry():

@@ -726,3 +726,39 @@ def test_gemm_pair_swiglu(T, I, Kd):
     out2 = torch.zeros_like(out)
     k.gemm_pair_swiglu(a, w, out2)
     assert torch.equal(out, out2)
+
+
+def test_a_wait_that_runs_out_raises_the_error_word_and_harms_nothing():
+    """The give-up path of the tensor-core kernels: a one-block launch of the few-token product is
+    told to expect 16 bytes more than its loads bring, with the wait limit lowered to 10 ms. The
+    kernel returns (no hang, no fault), the error word turns into a KernelError, and the next
+    ordinary launch on the same context is correct."""
+    from vllm_oxide_b200 import kernels
+    from vllm_oxide_b200.errors import KernelError
+    g = torch.Generator().manual_seed(90)
+    a = torch.randn(8, 256, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(128, 256, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.zeros(8, 128, dtype=torch.float32, device=DEV)
+    kernels.gemm_sm100(a, w, out, splits=1)
+    torch.cuda.synchronize()
+    kernels.gemm_sm100_check()                                   # nothing wrong so far
+    want = a.double().cpu() @ w.double().cpu().t()
+    assert max_rel_diff(out.cpu(), want) <= 1e-5
+    kernels.gemm_sm100_test_hooks(extra_tx_bytes=16, wait_limit_ms=10.0)
+    try:
+        kernels.gemm_sm100(a, w, torch.zeros_like(out), splits=1)
+        torch.cuda.synchronize()                           # returns after some 10 ms
+    finally:
+        kernels.gemm_sm100_test_hooks(0, 0.0)
+    with pytest.raises(KernelError, match="bounded wait"):
+        kernels.gemm_sm100_check()
+    kernels.gemm_sm100_check()                                   # the word was cleared by the check
+    out2 = torch.zeros_like(out)
+    kernels.gemm_sm100(a, w, out2, splits=1)
+    big = torch.zeros(8, 2048, dtype=torch.float32, device=DEV)
+    w2 = torch.randn(2048, 256, generator=g).to(torch.bfloat16).to(DEV)
+    kernels.gemm_sm100(a, w2, big)                               # and a launch with a cluster split
+    torch.cuda.synchronize()
+    kernels.gemm_sm100_check()
+    assert max_rel_diff(out2.cpu(), want) <= 1e-5
+    assert max_rel_diff(big.cpu(), a.double().cpu() @ w2.double().cpu().t()) <= 1e-5

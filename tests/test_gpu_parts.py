@@ -151,7 +151,7 @@ def test_attention_part_in_portions(dt, window, rope, scale):
     spec = part.cache_spec()
     assert (spec.kind, spec.window) == (("window", window) if window else ("full", 0))
     h = Harness(dt, page=page, groups=((spec.kind, spec.window),), kv=(KV, hd))
-    cache = LayerCache(h.kv[0][0], h.kv[0][1], 0, True)
+    cache = LayerCache((h.kv[0][0], h.kv[0][1]), 0, True)
     T = 45
     x = torch.randn(T, hidden, generator=g).to(dt)
     inv = plain.rope_inv_freq({"head_dim": hd, "hidden_size": hidden, "num_attention_heads": H, "rope_theta": 500000.0,
@@ -189,7 +189,7 @@ def test_block_part_and_bad_sizes(dt):
     pending = torch.randn(T, hidden, generator=g).to(dt).to(DEV)
     x0 = resid.double().cpu() + pending.double().cpu()
     out = ctx.alloc((T, hidden))
-    block.forward(resid, pending, ctx, LayerCache(h.kv[0][0], h.kv[0][1], 0, True), None, out)
+    block.forward(resid, pending, ctx, LayerCache((h.kv[0][0], h.kv[0][1]), 0, True), None, out)
     inv = plain.rope_inv_freq({"head_dim": hd, "hidden_size": hidden, "num_attention_heads": H, "rope_theta": 10000.0})
     x1 = x0 + _plain_attention_block(plain.rms_norm(x0, n1.double(), 1e-5), wq, wk, wv, wo, H, KV, hd, inv)
     ff = plain.feed_forward(plain.rms_norm(x1, n2.double(), 1e-5), wg.double(), wu.double(), wd.double())

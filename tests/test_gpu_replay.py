@@ -17,13 +17,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _session(model_dir, dtype, max_tokens, page):
+def _session(model_dir, dtype, max_tokens, page, max_seqs=8, max_batch_tokens=None, max_model_len=None):
     from vllm_oxide_b200.config import EngineConfig
     from vllm_oxide_b200.engine import ModelRunner
     from vllm_oxide_b200.replay.trace import TraceSession
     pages = -(-max_tokens // page)
-    eng = EngineConfig(max_batch_tokens=pages * page, max_seqs=8, max_model_len=pages * page, block_size=page,
-                       num_pages=pages, dtype=dtype, cuda_graphs=False)
+    eng = EngineConfig(max_batch_tokens=max_batch_tokens or pages * page, max_seqs=max_seqs, max_model_len=max_model_len or pages * page,
+                       block_size=page, num_pages=pages, dtype=dtype, cuda_graphs=False)
     return TraceSession(ModelRunner.from_dir(model_dir, eng))
 
 

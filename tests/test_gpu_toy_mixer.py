@@ -148,5 +148,15 @@ def test_toy_stateful_mixer_runs_through_the_unchanged_framework(tmp_path):
                 assert tok == int(_plain_logits(d, seq)[-1].argmax())
                 seq.append(tok)
         assert runner.manager.num_free_slots() == 3
+        # the same with the engine's defaults (CUDA graphs, steps launched ahead): this mixer reads
+        # device data on the host, so no step of it can be recorded; the engine notices at its
+        # first try, goes on launching steps one by one, and the tokens are the same
+        eng2 = EngineConfig(max_batch_tokens=64, max_seqs=3, max_model_len=64, block_size=8, num_pages=4, dtype="float32")
+        assert eng2.cuda_graphs and eng2.run_ahead
+        llm2 = LLM(ModelRunner.from_dir(d, eng2))
+        outs2 = llm2.generate([reqs["a"][:6], reqs["b"][:9], reqs["a"][3:8], reqs["b"][:2]],
+                              SamplingParams(max_new_tokens=5, stop_token_ids=()))
+        assert [o.token_ids for o in outs2] == [o.token_ids for o in outs]
+        assert not llm2.runner.decode_graphs and not llm2.runner._graphs
     finally:
         unregister_architecture("ToyRunningMean")

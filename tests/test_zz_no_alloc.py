@@ -1,6 +1,6 @@
 """The entry point that allocates nothing (csrc/no_alloc.h), called through its exported C symbol
-as a foreign caller would, against the ordinary entry point: two calls in a row, the second
-finding the first call's leftovers (a NaN mark among them) in the library's fixed array.
+as a foreign caller would, against the ordinary entry point: two calls in a row on the library's
+one fixed array, the second after NaN marks were left in it as by a call that broke off halfway.
 
 For users of the library: `vob_pick_tokens_static` is for callers that cannot obtain scratch
 buffers because they may not allocate device memory at all (all memory already handed to another
@@ -43,13 +43,20 @@ def _reference(logits, temps, seeds, steps):
 
 def test_static_pick_matches_the_ordinary_entry_point_twice_in_a_row():
     f = _static_fn()
+    from vllm_oxide_b200.csrc.build import cuda_library_path
+    leave_marks = ctypes.CDLL(cuda_library_path("sampling")).vob_pick_static_test_leave_marks
+    leave_marks.argtypes, leave_marks.restype = [ctypes.c_int, ctypes.c_void_p], ctypes.c_int
     g = torch.Generator().manual_seed(17)
     V = 128256
     for call in range(2):
         R = 8 if call == 0 else 5
         logits = (torch.randn(R, V, generator=g) * 3).to(DEV)
         if call == 0:
-            logits[3, 77777] = float("nan")           # leaves a mark in the shared array for the next call to find
+            logits[3, 77777] = float("nan")
+        else:
+            # what a call that failed between its two kernels would leave: marks on every row
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            assert leave_marks(64, stream) == 0
         temps = torch.tensor([0.0, 0.7, 0.0, 0.0, 1.3, 0.7, 0.0, 0.2][:R], device=DEV)
         seeds = torch.tensor([[i + 1, 3 * i] for i in range(R)], dtype=torch.int32, device=DEV)
         steps = torch.arange(call * 10, call * 10 + R, dtype=torch.int32, device=DEV)

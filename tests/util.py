@@ -41,6 +41,10 @@ LAYERS_1B = LlamaConfig(
     head_dim=64, vocab_size=128256, max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
     rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192), tie_word_embeddings=True)
 
+# The same layers with a vocabulary of 2,048: steps of dozens of requests and of thousands of rows
+# stay affordable for the plain implementation (the head is the largest product at full vocabulary)
+LAYERS_1B_V2K = dataclasses.replace(LAYERS_1B, vocab_size=2048)
+
 # TINY_D for contexts of thousands of keys (the decode kernels choose by context length)
 TINY_D_LONG = dataclasses.replace(TINY_D, max_position_embeddings=16384)
 
@@ -52,7 +56,7 @@ LAYERS_HD128 = LlamaConfig(
     rope_scaling=RopeScaling(32.0, 1.0, 4.0, 8192), tie_word_embeddings=False)
 
 TINY = {"HD128": (LAYERS_HD128, 0.02, 16), "A": (TINY_A, 0.02, 16), "B": (TINY_B, 0.05, 8), "C": (TINY_C, 0.04, 16), "D": (TINY_D, 0.05, 16),
-        "DL": (TINY_D_LONG, 0.05, 16), "1B": (LAYERS_1B, 0.02, 16)}   # config, std, page size
+        "DL": (TINY_D_LONG, 0.05, 16), "1B": (LAYERS_1B, 0.02, 16), "1Bv": (LAYERS_1B_V2K, 0.02, 16)}   # config, std, page size
 
 
 def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:
@@ -61,7 +65,7 @@ def make_model_dir(tmp_path, name: str, seed: int = 1234, std=None) -> str:
     if not os.path.exists(os.path.join(d, "model.safetensors")):
         # larger weights than a checkpoint's so that attention is far from uniform and a wrong
         # key or a stale page changes the logits visibly; norm weights away from 1
-        write_random_model(d, cfg, seed, std=(std if std is not None else (s if name in ("1B", "HD128") else max(s, 0.08))), norm_jitter=0.3)
+        write_random_model(d, cfg, seed, std=(std if std is not None else (s if name in ("1B", "1Bv", "HD128") else max(s, 0.08))), norm_jitter=0.3)
     return d
 
 

@@ -6,4 +6,4 @@ __version__ = "0.1.0"
 
 from .config import EngineConfig, LlamaConfig, RopeScaling  # noqa: F401
 from .errors import (EngineError, ConfigError, ShapeError, CapacityError, WeightsError,  # noqa: F401
-                     WeightsFormatError, KernelError, NaNError, OutOfPages)
+                     WeightsFormatError, KernelError, NaNError)

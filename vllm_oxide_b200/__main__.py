@@ -7,8 +7,8 @@ is the reference's `generate` example with its positional arguments, defaults an
 default "The capital of France is", max_new default 64, stop at the model's eos, prefill tok/s =
 prompt tokens / prefill time, decode tok/s = tokens after the first / decode time). Options
 beyond the reference's: --prompt-ids / --prompt-len (token ids instead of text, for model folders
-without a tokenizer), --temperature, --seed, --dtype, and the engine limits by their
-`EngineConfig` names.
+without a tokenizer), --random-weights SEED (the folder needs only config.json; weights are drawn
+from the seed), --temperature, --seed, --dtype, and the engine limits by their `EngineConfig` names.
 
     python -m vllm_oxide_b200 load_weights [model_dir]         (crates/engine/examples/load_weights.rs:11-28)
     python -m vllm_oxide_b200 random_weights model_dir --config config.json --seed N [--std S]
@@ -48,15 +48,22 @@ def cmd_generate(argv):
     ap.add_argument("--profile", action="store_true", help="per-kernel device time of one decode step")
     ap.add_argument("--prompt-ids", default=None, help="comma-separated token ids instead of text")
     ap.add_argument("--prompt-len", type=int, default=None, help="a seeded random prompt of this many tokens")
+    ap.add_argument("--max-new", dest="max_new_opt", type=int, default=None, help="same as the positional max_new")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                    help="read only config.json and draw the weights from this seed")
+    ap.add_argument("--random-weights-std", type=float, default=0.02, metavar="S", help="their standard deviation")
     _engine_args(ap)
     a = ap.parse_args(argv)
+    if a.max_new_opt is not None:
+        a.max_new = a.max_new_opt
     import torch
     from .engine import LLM
     from .sampling import SamplingParams
     t = time.perf_counter()
-    llm = LLM(a.model_dir, dtype=a.dtype, **_engine_kwargs(a))
+    llm = LLM(a.model_dir, dtype=a.dtype, random_weights_seed=a.random_weights, random_weights_std=a.random_weights_std,
+              **_engine_kwargs(a))
     print(f"loaded secs={time.perf_counter() - t:.3f}", file=sys.stderr)
     if a.prompt_ids is not None:
         ids = [int(x) for x in a.prompt_ids.split(",") if x.strip()]
@@ -138,7 +145,12 @@ def main(argv=None):
     if not argv or argv[0] not in cmds:
         print(__doc__, file=sys.stderr)
         return 2
-    return cmds[argv[0]](argv[1:])
+    from .errors import EngineError
+    try:
+        return cmds[argv[0]](argv[1:])
+    except EngineError as e:                      # a user's mistake or a limit: one line, no traceback
+        print(f"{argv[0]}: {type(e).__name__}: {e}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":

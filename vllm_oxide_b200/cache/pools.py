@@ -1,12 +1,12 @@
 """Device memory of the cache and its host-side bookkeeping, laid out from a model's parts.
 
-Every call of the model's run order that writes a cache gets pages of its own:
-K and V, each [num_pages, kv_heads, page_size, head_dim] in the compute dtype (inside a page
-the layout is head-major, so one (page, head) is one contiguous page_size x head_dim tile; the
-reference's pool is [slot, kv_heads, head_dim], crates/engine/src/backend/paged.rs:25-27, and
-leaves the layout to the backend, crates/engine/src/backend/mod.rs:10-12). Calls whose mixers
-ask for the same kind of cache (all keys, or a window of w) with the same head sizes form a
-group: one page pool and one block table per request serve all of them, a page number being
+Every call of the model's run order that writes a cache gets pages of its own: the tensors
+its mixer's `CacheSpec` names (by default K and V), each [num_pages, heads, page_size, width]
+in the compute dtype or the one the spec gives (inside a page the layout is head-major, so one
+(page, head) is one contiguous page_size x width tile; the reference's pool is
+[slot, kv_heads, head_dim], crates/engine/src/backend/paged.rs:25-27, and leaves the layout to
+the backend, crates/engine/src/backend/mod.rs:10-12). Calls whose mixers ask for the same kind
+of cache (all keys, or a window of w) with the same tensors form a group: one page pool and one block table per request serve all of them, a page number being
 valid in every layer of its group. Mixers with fixed-size state get a tensor
 [max_seqs, *shape] indexed by the request's state slot. The page bookkeeping itself is the
 native `CacheManager`.
@@ -55,11 +55,14 @@ class CachePools:
                 group_keys.append(key)
             self.cache_group[c] = group_keys.index(key)
         self.group_keys = group_keys
-        es = 2 if dtype == torch.bfloat16 else 4
         # bytes one page costs in each group (over all caches of the group)
         self.page_bytes = [0] * len(group_keys)
         for c, cs in cache_specs.items():
-            self.page_bytes[self.cache_group[c]] += 2 * cs.num_kv_heads * cs.head_dim * page_size * es
+            for t in cs.paged_tensors():
+                if t.heads <= 0 or t.width <= 0:
+                    raise ConfigError(f"cache {c}: a paged tensor needs positive heads and width, got {t}")
+                es = torch.empty((), dtype=t.dtype or dtype).element_size()
+                self.page_bytes[self.cache_group[c]] += t.heads * t.width * page_size * es
         if num_pages is None:
             total = sum(self.page_bytes)
             if not total:
@@ -75,11 +78,15 @@ class CachePools:
         groups = []
         for key in group_keys:
             kind, window = key[0], key[1]
+            if kind not in ("full", "window"):
+                raise ConfigError(f"cache kind {kind!r} is not known (full or window)")
             groups.append(rt.GroupSpec(rt.WINDOW if kind == "window" else rt.FULL, int(window), self.num_pages))
         self.manager = rt.CacheManager(page_size, groups, max_seqs)
-        self.kv: Dict[int, torch.Tensor] = {}
+        # cache number -> its tensors, in the order of the spec (K, V by default)
+        self.kv: Dict[int, tuple] = {}
         for c, cs in cache_specs.items():
-            self.kv[c] = torch.zeros((2, self.num_pages, cs.num_kv_heads, page_size, cs.head_dim), dtype=dtype, device=device)
+            self.kv[c] = tuple(torch.zeros((self.num_pages, t.heads, page_size, t.width), dtype=t.dtype or dtype, device=device)
+                               for t in cs.paged_tensors())
         # fixed-size per-request state, one tensor per call whose mixer asks for it
         self.state: Dict[int, torch.Tensor] = {}
         for idx, call in enumerate(spec.schedule):
@@ -94,8 +101,7 @@ class CachePools:
     def layer_cache(self, cache: Optional[int], write: bool) -> Optional[LayerCache]:
         if cache is None:
             return None
-        kv = self.kv[cache]
-        return LayerCache(k=kv[0], v=kv[1], group=self.cache_group[cache], write=write)
+        return LayerCache(tensors=self.kv[cache], group=self.cache_group[cache], write=write)
 
     def reset_slot(self, slot: int) -> None:
         """A request was admitted to this slot: its state starts from zero."""
@@ -106,4 +112,4 @@ class CachePools:
         return sum(self.page_bytes) // self.page_size
 
     def total_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kv.values())
+        return sum(t.numel() * t.element_size() for ts in self.kv.values() for t in ts)

@@ -138,9 +138,12 @@ class LlamaConfig:
         for k, want in fixed.items():
             if k in d and d[k] != want:
                 raise ConfigError(f"{where}: '{k}' = {d[k]!r} is not supported (only {want!r})")
-        for k in ("sliding_window", "attention_dropout", "pretraining_tp"):
-            if d.get(k) not in (None, 0, 0.0, 1):
-                raise ConfigError(f"{where}: '{k}' = {d[k]!r} is not supported by this architecture")
+        # keys that switch on something this architecture does not compute: only their "off" values pass
+        off_values = {"sliding_window": (None, 0), "attention_dropout": (None, 0, 0.0), "pretraining_tp": (None, 1)}
+        for k, allowed in off_values.items():
+            v = d.get(k)
+            if isinstance(v, bool) or not any(v is a or (a is not None and v == a) for a in allowed):
+                raise ConfigError(f"{where}: '{k}' = {v!r} is not supported by this architecture")
         hidden = _need(d, "hidden_size", int, where)
         heads = _need(d, "num_attention_heads", int, where)
         if heads <= 0:

@@ -244,24 +244,6 @@ VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Residual add alone: resid[t, :] += delta[t, :]  (float32 sum). Used where no norm follows.
-// ---------------------------------------------------------------------------------------------
-template <typename TD>
-__global__ void add_residual_kernel(float* __restrict__ resid, const TD* __restrict__ delta, size_t n) {
-    pdl_launch_dependents();
-    pdl_wait(3);
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) resid[i] += ld_f(delta + i);
-}
-
-VOB_EXPORT int vob_add_residual(float* resid, const void* delta, int delta_code, long long n, cudaStream_t stream) {
-    if (n <= 0) return 0;
-    unsigned blocks = (unsigned)((n + 255) / 256);
-    VOB_DISPATCH_ELEM(delta_code, return vob_launch(add_residual_kernel<ElemT>, dim3(blocks), dim3(256), 0, stream, resid, (const ElemT*)delta, (size_t)n));
-    return 0;
-}
-
-// ---------------------------------------------------------------------------------------------
 // Rotary positions on q and k, and the cache write of k and v, in one pass over a token's
 // q/k/v rows:
 //   theta_i = float(pos) * inv_freq[i]         (float32 product; cosf/sinf precise versions)

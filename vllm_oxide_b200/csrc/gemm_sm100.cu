@@ -113,7 +113,7 @@ template <int BT, int STAGES, typename OutT, int EPI>
 __global__ void __launch_bounds__(NTHREADS_FEW, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ C,
                   long long ldc, int T, int N, int K, int kb_per_split, int* __restrict__ err_flag, int up_row0,
-                  const QkvArgs qa) {
+                  const QkvArgs qa, int test_extra_tx) {
     constexpr int SB = stage_bytes<BT, EPI>();
     constexpr int A_BYTES = BM * BK * 2;
     constexpr int PRE = BT >= 64 ? 12 : (BT >= 32 ? 8 : 4);   // tokens per block whose rotation is worked out ahead
@@ -159,7 +159,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int pre = nkb < STAGES ? nkb : STAGES;
             for (int i = 0; i < pre; ++i) {
                 unsigned char* a = tiles + i * SB;
-                mbar_expect_tx(full_bar + i, SB);
+                // test_extra_tx is 0 except in the test of the give-up path: bytes that never arrive
+                mbar_expect_tx(full_bar + i, SB + (i == 0 ? test_extra_tx : 0));
                 if (EPI == EPI_SWIGLU) {
                     tma_load_2d(a, &map_w, (kb0 + i) * BK, m_tile * (BM / 2), full_bar + i);
                     tma_load_2d(a + (BM / 2) * BK * 2, &map_w, (kb0 + i) * BK, up_row0 + m_tile * (BM / 2), full_bar + i);
@@ -610,6 +611,10 @@ template <int BT, int STAGES, int EPI = EPI_STORE> constexpr size_t smem_bytes()
     return (size_t)STAGES * stage_bytes<BT, EPI>() + 1024 + 1024;       // tiles + alignment slack + barriers and per-token scales
 }
 
+// Test hook (see vob_gemm_sm100_test_hooks): bytes by which the next launches over-declare what
+// their first stage's barrier expects, so that the barrier never completes and the waits run out.
+int g_test_extra_tx = 0;
+
 template <int BT, int STAGES, typename OutT, int EPI>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int splits, int kb_per,
            int* err_flag, int up_row0, const QkvArgs& qa, cudaStream_t stream) {
@@ -639,8 +644,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
+    // the hook applies to a block on its own only (no cluster whose peers would wait for it)
+    const int extra_tx = (splits == 1 && cfg.gridDim.x == 1 && cfg.gridDim.y == 1) ? g_test_extra_tx : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<BT, STAGES, OutT, EPI>, mw, mx, (OutT*)C, ldc, T, N, K, kb_per, err_flag,
-                                       up_row0, qa);
+                                       up_row0, qa, extra_tx);
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }
 
@@ -674,6 +681,20 @@ constexpr int few_stages(int bt) { return bt <= 16 ? 6 : bt <= 32 ? 5 : 4; }
 int pick_bt(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 }  // namespace
+
+// For the test of the give-up path only. `extra_tx_bytes` > 0: launches of ONE block (one tile, no
+// split) declare so many bytes more than their first stage's loads bring, so its barrier never
+// completes; `wait_limit_ns` is the limit after which a wait gives up (the default is two seconds;
+// 0 puts it back). The block then raises the error word, frees its tensor memory and returns:
+// nothing faults and nothing hangs. Call with (0, 0) afterwards.
+VOB_EXPORT int vob_gemm_sm100_test_hooks(int extra_tx_bytes, unsigned long long wait_limit_ns) {
+    if (extra_tx_bytes < 0 || extra_tx_bytes > 1024) return VOB_ERR_BAD_ARG;
+    unsigned long long limit = wait_limit_ns ? wait_limit_ns : WAIT_LIMIT_NS;
+    cudaError_t e = cudaMemcpyToSymbol(g_wait_limit_ns, &limit, sizeof(limit));
+    if (e != cudaSuccess) return (int)e;
+    g_test_extra_tx = extra_tx_bytes;
+    return 0;
+}
 
 // How many splits of K fill `num_sms` SMs for a product with few tokens (1 when the tiles alone do).
 VOB_EXPORT int vob_gemm_sm100_pick_splits(int T, int N, int K, int num_sms) {

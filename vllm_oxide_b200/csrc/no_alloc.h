@@ -25,7 +25,8 @@
 //     that device current) and remembers it; make that first call outside any stream capture;
 //   * every call uses the same array and finds in it whatever the last call left. The words that
 //     must start at zero (the per-row NaN marks) are cleared on the stream at the start of each
-//     call. Two calls whose kernels may run at the same time on one GPU (different streams, no
+//     call. (A call that ran to its end leaves them at zero itself; the clearing matters after a
+//     call whose second kernel was never launched.) Two calls whose kernels may run at the same time on one GPU (different streams, no
 //     ordering between them) would race on the array: order them;
 //   * the function calls no cudaMalloc, cudaFree or any allocating library routine.
 // Returns 0, a cudaError_t value, or one of the VOB_ERR_* codes.
@@ -45,6 +46,10 @@ extern "C" {
 __attribute__((visibility("default")))
 int vob_pick_tokens_static(const float* logits, long long ld, int R, int V, const float* temperature,
                            const uint32_t* seeds, const int* steps, int* out, cudaStream_t stream);
+// Test aid: leaves NaN marks for the first `rows` rows in the fixed array, as a call that broke off
+// between its two kernels would; the next call must not be misled by them.
+__attribute__((visibility("default")))
+int vob_pick_static_test_leave_marks(int rows, cudaStream_t stream);
 #ifdef __cplusplus
 }
 #endif

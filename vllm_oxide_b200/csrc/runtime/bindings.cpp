@@ -46,6 +46,8 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def("admit", &CacheManager::admit)
         .def("reserve", &CacheManager::reserve)
         .def("tokens_that_fit", &CacheManager::tokens_that_fit)
+        .def("max_pages_held", &CacheManager::max_pages_held)
+        .def("first_visible", &CacheManager::first_visible)
         .def("commit", &CacheManager::commit)
         .def("release", &CacheManager::release)
         .def("slot_of", &CacheManager::slot_of)

@@ -28,10 +28,26 @@ namespace vob {
 
 enum GroupKind : int { kFull = 0, kWindow = 1 };
 
+// What a group keeps of a request. The two questions every other piece of the runtime asks of a
+// kind are answered HERE and nowhere else (the cache manager's `commit`, the scheduler's capacity
+// check and `max_pages_held` only call them), so another kind is another case in these two
+// functions.
 struct GroupSpec {
     int kind = kFull;
     int window = 0;      // keys visible to a query, itself included (Window groups)
     int num_pages = 0;
+
+    // First position whose key a query at position `pos` still reads.
+    int64_t first_visible(int64_t pos) const {
+        if (kind == kWindow) return std::max<int64_t>(0, pos + 1 - window);
+        return 0;
+    }
+    // Most tokens whose pages a request of `total` tokens holds at any one time: a window group
+    // holds the window plus the page being filled, a full group everything.
+    int64_t max_live_tokens(int64_t total, int page_size) const {
+        if (kind == kWindow) return std::min<int64_t>(total, (int64_t)window + page_size);
+        return total;
+    }
 };
 
 struct CacheError : std::runtime_error {
@@ -121,10 +137,13 @@ public:
     }
 
     // First position whose key a query at position `pos` still reads in group g.
-    int64_t first_visible(int g, int64_t pos) const {
-        const auto& gs = groups_[g];
-        if (gs.kind == kWindow) return std::max<int64_t>(0, pos + 1 - gs.window);
-        return 0;
+    int64_t first_visible(int g, int64_t pos) const { return groups_.at(g).first_visible(pos); }
+
+    // Pages of group g that a request of `total` tokens holds at most at any one time (what a
+    // pool must have for the request to fit at all).
+    int64_t max_pages_held(int g, int64_t total) const {
+        int64_t live = groups_.at(g).max_live_tokens(total, page_size_);
+        return (live + page_size_ - 1) / page_size_;
     }
 
     // Pages that group g must add so that the request can take n_new more tokens.
@@ -178,9 +197,8 @@ public:
         r.len += n_new;
         std::vector<std::pair<int, int>> released;   // (group, page)
         for (size_t g = 0; g < groups_.size(); ++g) {
-            if (groups_[g].kind != kWindow) continue;
             int64_t first = first_visible((int)g, r.len);        // next query sits at position len
-            int64_t dead_pages = first / page_size_;             // pages wholly below `first`
+            int64_t dead_pages = first / page_size_;             // pages wholly below `first` (none in a full group)
             auto& t = r.tables[g];
             for (int64_t i = 0; i < dead_pages && i < (int64_t)t.size(); ++i) {
                 if (t[i] >= 0) {

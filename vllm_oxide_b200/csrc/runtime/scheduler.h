@@ -89,10 +89,7 @@ public:
         if (total > max_model_len_)
             throw CacheError("capacity: sequence length: need " + std::to_string(total) + ", limit " + std::to_string(max_model_len_));
         for (int g = 0; g < cache_->num_groups(); ++g) {
-            const GroupSpec& gs = cache_->group(g);
-            // a window group holds the window plus the page being filled
-            int64_t live = gs.kind == kWindow ? std::min<int64_t>(total, (int64_t)gs.window + cache_->page_size()) : total;
-            int64_t pages = (live + cache_->page_size() - 1) / cache_->page_size();
+            int64_t pages = cache_->max_pages_held(g, total);      // the group's own rule (all tokens, a window, ...)
             if (pages > cache_->num_pages(g))
                 throw CacheError("capacity: sequence length: need " + std::to_string(pages) + " pages, the pool has " +
                                  std::to_string(cache_->num_pages(g)));

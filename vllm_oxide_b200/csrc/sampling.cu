@@ -178,8 +178,20 @@ int vob_pick_tokens_static(const float* logits, long long ld, int R, int V, cons
     float* part_val = reinterpret_cast<float*>(base);
     int* part_idx = reinterpret_cast<int*>(base + VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 4);
     int* nan_flags = reinterpret_cast<int*>(base + VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 8);
-    // the array keeps what the last call left: the NaN marks must start at zero
+    // the array keeps what the last call left: the NaN marks must start at zero (a call that ran to
+    // its end has put its own marks back; one that failed between its two launches has not)
     cudaError_t e = cudaMemsetAsync(nan_flags, 0, sizeof(int) * R, stream);
     if (e != cudaSuccess) return (int)e;
     return vob_pick_tokens(logits, ld, R, V, temperature, seeds, steps, splits, part_val, part_idx, nan_flags, out, stream);
+}
+
+// For the test of the rule above: sets the NaN marks of the first `rows` rows in the fixed array,
+// as a call that failed between its two launches would leave them.
+int vob_pick_static_test_leave_marks(int rows, cudaStream_t stream) {
+    if (rows < 0 || rows > VOB_PICK_STATIC_MAX_ROWS) return VOB_ERR_BAD_ARG;
+    unsigned char* base = nullptr;
+    int rc = pick_static_scratch_address(&base);
+    if (rc) return rc;
+    int* nan_flags = reinterpret_cast<int*>(base + VOB_PICK_STATIC_MAX_ROWS * VOB_PICK_STATIC_MAX_SPLITS * 8);
+    return (int)cudaMemsetAsync(nan_flags, 0x01, sizeof(int) * rows, stream);
 }

@@ -14,6 +14,9 @@
 namespace vob_sm100 {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+// The limit the waits use, read only on a wait's slow path. A module may export a setter (the
+// matrix-product module does, for the test that makes a wait run out in milliseconds).
+__device__ unsigned long long g_wait_limit_ns = WAIT_LIMIT_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -46,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag) return false;
             unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) {
+            else if (now - t0 > g_wait_limit_ns) {
                 *abort_flag = 1;
                 if (err_flag) atomicExch(err_flag, code);
                 return false;

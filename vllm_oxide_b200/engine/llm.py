@@ -21,6 +21,7 @@ from ..config import EngineConfig
 from ..errors import CapacityError, EngineError, NaNError, ShapeError
 from ..sampling import SamplingParams
 from .runner import ModelRunner
+from .tokenizer import TextTokenizer
 
 
 @dataclass
@@ -44,11 +45,17 @@ class GenerateOutput:
 
 
 class LLM:
-    def __init__(self, model: Union[str, ModelRunner], dtype="bfloat16", **engine_kwargs):
+    def __init__(self, model: Union[str, ModelRunner], dtype="bfloat16", random_weights_seed: Optional[int] = None,
+                 random_weights_std: float = 0.02, **engine_kwargs):
+        """`model`: a folder with config.json and safetensors weights (and, for text prompts, a
+        tokenizer.json), or a `ModelRunner`. `random_weights_seed`: read only config.json and draw
+        the weights from this seed (N(0, `random_weights_std`), norm weights 1). Everything else is
+        an `EngineConfig` field."""
         if isinstance(model, ModelRunner):
             self.runner = model
         else:
-            self.runner = ModelRunner.from_dir(model, EngineConfig(dtype=dtype, **engine_kwargs))
+            self.runner = ModelRunner.from_dir(model, EngineConfig(dtype=dtype, **engine_kwargs),
+                                               random_weights_seed=random_weights_seed, random_weights_std=random_weights_std)
         r = self.runner
         e = r.engine
         self.scheduler = r.rt.Scheduler(r.manager, e.max_batch_tokens, e.max_seqs, r.max_model_len,
@@ -70,22 +77,23 @@ class LLM:
         self._capturing = 0              # live requests that want logits (they are never run ahead of)
         self.run_ahead = bool(e.run_ahead) and bool(e.cuda_graphs)
         self.stats = {"steps": 0, "preemptions": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0}
-        tok = os.path.join(model, "tokenizer.json") if isinstance(model, str) else None
-        if tok and os.path.exists(tok):
-            try:
-                from tokenizers import Tokenizer
-                self._tokenizer = Tokenizer.from_file(tok)
-            except ImportError:
-                self._tokenizer = None
+        if isinstance(model, (str, os.PathLike)):
+            self._tokenizer = TextTokenizer.load(str(model))
 
     # ------------------------------------------------------------------ requests
     def encode(self, text: str) -> List[int]:
+        """Token ids of `text` with the special tokens the tokenizer's post-processor defines
+        (a leading BOS for Llama 3: crates/engine/src/tokenizer.rs:25-30)."""
         if self._tokenizer is None:
             raise ShapeError("generate", "text prompts need a tokenizer.json in the model folder; pass token ids")
-        return self._tokenizer.encode(text).ids
+        return self._tokenizer.encode(text)
 
     def decode(self, ids: Sequence[int]) -> Optional[str]:
-        return self._tokenizer.decode(list(ids)) if self._tokenizer is not None else None
+        """Text of `ids`, special tokens (BOS, EOS) skipped (crates/engine/src/tokenizer.rs:33-38);
+        None without a tokenizer."""
+        if self._tokenizer is None:
+            return None
+        return self._tokenizer.decode(ids)
 
     def add_request(self, prompt: Union[str, Sequence[int]], params: SamplingParams) -> int:
         ids = self.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
@@ -245,26 +253,6 @@ class LLM:
             self._params.pop(rid)
             self._generated.pop(rid)
         return outs
-
-    def step_async(self) -> None:
-        """A decode step whose picked tokens stay on the device: the next step reads them there and
-        the host does not wait. For throughput measurement of requests that never stop early; the
-        host-side token lists receive placeholders."""
-        r, sched = self.runner, self.scheduler
-        self._finish_inflight()
-        plan = sched.schedule()
-        if not plan.decode_only or plan.preempted or plan.admitted:
-            raise ShapeError("step_async", "only steady decode steps can run without reading tokens back")
-        r.decode_step_graph(sched, plan, feed_from_device=True, read=False)
-        ids = plan.sampling_ids()
-        for rid in ids:
-            self._generated[rid] += 1
-        self.stats["steps"] += 1
-        for f in sched.update(plan, [0] * len(ids)):
-            self._forget(f.id)
-
-    def drain_async(self) -> None:
-        torch.cuda.synchronize()
 
     def abort(self, request_id: int) -> None:
         self._finish_inflight()

@@ -26,7 +26,7 @@ from ..cache.pools import CachePools
 from ..config import EngineConfig, architecture_for, read_config_json
 from ..csrc.build import runtime_module
 from ..errors import CapacityError, KernelError, ShapeError
-from ..parts.base import FOLD_ROWS, LONG_CONTEXT_KEYS, ModelSpec, StepContext, Workspace
+from ..parts.base import FOLD_ROWS, LONG_CONTEXT_KEYS, ModelSpec, StepContext, Workspace, aligned
 from ..weights import load_safetensors_weights, weights_from_tensors
 
 
@@ -83,9 +83,12 @@ class ModelRunner:
         kernels.set_pdl(bool(engine.pdl))
         self.spec: ModelSpec = arch.build(config, weights, BuildContext(dtype=self.dtype, device=self.device))
         del weights
-        # what this model needs is compiled now, side by side (a fresh checkout has nothing built)
-        head_dims = {getattr(b.mixer, "hd", 0) for b in self.spec.blocks if hasattr(b, "mixer")}
-        kernels.preload(kernels.modules_for(self.dtype, head_dims, engine.max_batch_tokens))
+        if self.dtype == torch.bfloat16:
+            # the library product (many rows) must add its split-K partial sums in float32 too
+            torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        # what this model needs is compiled now, side by side (a fresh checkout has nothing built):
+        # every part names the kernel libraries it launches
+        kernels.preload(self.kernel_modules())
         # As in the reference, the longest sequence is the engine's limit, not config.json's
         # max_position_embeddings (crates/engine/src/backend/cpu/mod.rs:49-54): rotation angles are
         # computed from the position itself, so no table length binds them.
@@ -100,7 +103,10 @@ class ModelRunner:
         self.logit_chunk = min(self.logits_cap, max(engine.max_seqs, 64))
         G = self.pools.num_groups
         self.layout = self.rt.step_layout(self.rows_cap, self.seqs_cap, self.logits_cap, G, self.max_pages)
-        total = self.layout["total"]
+        # a decode step has one row per request, so never more requests than a step has rows
+        self.decode_cap = min(self.seqs_cap, self.rows_cap)
+        self.decode_layout = self.rt.step_layout(self.decode_cap, self.decode_cap, self.decode_cap, G, self.max_pages)
+        total = max(self.layout["total"], self.decode_layout["total"])
         # a ring of pinned staging buffers: the host may run several steps ahead of the device, and a
         # buffer is written again only after the copy that reads it has been executed
         self._stage = [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
@@ -123,7 +129,7 @@ class ModelRunner:
         self.steps_run = 0
         self.last_upload_bytes = 0
         self.graphs_enabled = bool(engine.cuda_graphs)
-        self.decode_layout = self.rt.step_layout(self.seqs_cap, self.seqs_cap, self.seqs_cap, G, self.max_pages)
+        self.decode_graphs = self.graphs_enabled         # turned off by a decode step that cannot be recorded
         self._graphs = {}
         self._step_graphs = collections.OrderedDict()    # shape class -> (graph, launches); least recently replayed first
         self._step_seen = {}
@@ -135,25 +141,46 @@ class ModelRunner:
         self._graph_pool = None
 
     # ------------------------------------------------------------------ sizes
+    def kernel_modules(self) -> tuple:
+        """The kernel libraries this model's parts launch, in first-use order, each once."""
+        spec, mods = self.spec, ["sampling"]
+        for part in [spec.embedding, *spec.blocks, spec.final_norm, spec.lm_head]:
+            mods += list(getattr(part, "kernel_modules", lambda d, r: ())(self.dtype, self.engine.max_batch_tokens))
+        return tuple(dict.fromkeys(mods))
+
     def workspace_formula(self, rows: int) -> int:
-        """Peak bytes of a step of `rows` tokens, read off the scopes of `_forward` (the
-        reference's arena formula, crates/engine/src/model.rs:68-90, for this arrangement)."""
+        """Peak bytes of the workspace over all steps of at most `rows` tokens, to the byte, read
+        off the scopes of `_forward` and `_head` (the reference's arena formula,
+        crates/engine/src/model.rs:68-90, for this arrangement; its test that the high-water mark
+        of a largest step equals the formula, :400-419, holds here too): the float32 residual,
+        two buffers for block outputs still to be added, and the larger of the largest block and
+        the head's chunk (logits and the normed rows)."""
         es = 2 if self.dtype == torch.bfloat16 else 4
         h, V = self.spec.hidden_size, self.spec.vocab_size
-        pad = 256
-        resid = rows * h * 4 + pad
-        pending = 2 * (rows * h * es + pad)
-        block = max((b.workspace_bytes(rows, h, es) for b in self.spec.blocks), default=0) + pad
-        head = self.logit_chunk * (h * es + V * 4) + 2 * pad
+        resid = aligned(rows * h * 4)
+        pending = 2 * aligned(rows * h * es)
+        block = max((b.workspace_bytes(rows, h, es) for b in self.spec.blocks), default=0)
+        n = min(self.logit_chunk, rows)
+        head = aligned(n * V * 4) + self.spec.final_norm.workspace_bytes(n, es)
         return resid + pending + max(block, head)
 
     @classmethod
-    def from_dir(cls, model_dir: str, engine: EngineConfig) -> "ModelRunner":
+    def from_dir(cls, model_dir: str, engine: EngineConfig, random_weights_seed: Optional[int] = None,
+                 random_weights_std: float = 0.02) -> "ModelRunner":
+        """A model folder: config.json and its safetensors. With `random_weights_seed` only
+        config.json is read and the weights are drawn on the device from that seed (values as
+        `weights.random_tensors` makes them there; a folder written by `write_random_model` is
+        drawn on the host and differs)."""
         from .. import models  # noqa: F401  (registers architectures)
         d = read_config_json(model_dir)
         arch = architecture_for(d, os.path.join(model_dir, "config.json"))
         config = arch.config_cls.from_dict(d, os.path.join(model_dir, "config.json"))
-        return cls(config, model_dir, engine, arch)
+        if random_weights_seed is None:
+            return cls(config, model_dir, engine, arch)
+        _require_cuda(engine.device)
+        from ..weights import random_tensors
+        tensors = random_tensors(arch.manifest(config), int(random_weights_seed), random_weights_std, engine.dtype, engine.device)
+        return cls(config, tensors, engine, arch)
 
     # ------------------------------------------------------------------ the step
     def context(self, rows: int, seqs: int, arrays=None, layout=None) -> StepContext:
@@ -289,7 +316,14 @@ class ModelRunner:
                 self.step_graph_replays += 1
                 return StepResult(self.sampled, None, R)
         self.workspace.reset()
-        ctx = self.context(T, S, arrays)
+        if shape is None:
+            ctx = self.context(T, S, arrays)
+        else:
+            # a step of a class that may be recorded runs with the class's padded row count and
+            # rounded-up longest portion from its first sighting on: launched one by one or
+            # replayed, it runs the same kernels (which of them a part picks depends on the rows)
+            ctx = self.context(shape[0], S, arrays)
+            ctx.max_new = shape[3]
         resid, pending = self._forward(ctx)
         if R:
             self._head(resid, pending, ctx, R, logits_out)
@@ -348,9 +382,10 @@ class ModelRunner:
         b = 1
         while b < n:
             b *= 2
-        return min(b, self.seqs_cap)
+        return min(b, self.decode_cap)
 
-    def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True, parity: int = 0):
+    def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True, parity: int = 0,
+                          arrays=None):
         """A step in which every request brings exactly one token. Its kernels are the same as any
         step's, but their launches are replayed from a CUDA graph captured once per batch-size
         class (1, 2, 4, ... requests, the batch padded with rows that attend to nothing) and per
@@ -358,10 +393,12 @@ class ModelRunner:
         at small batches launching ~10 kernels per layer costs more than running them
         (the reference's estimate: docs/decisions/0003-backend-trait-and-memory.md:51).
         The picked tokens land in pinned host buffer `parity`. With `read` the call waits and
-        returns them; without, it returns an event to hand to `read_decode` later."""
+        returns them; without, it returns an event to hand to `read_decode` later. `arrays`: the
+        plan's arrays if the caller has built them already (`decode_arrays`)."""
         S = plan.num_entries
         L = self.decode_layout
-        arrays = scheduler.arrays(plan, L["rows_cap"], L["seqs_cap"], L["logits_cap"], self.max_pages, self.spec.vocab_size)
+        if arrays is None:
+            arrays = self.decode_arrays(scheduler, plan)
         if arrays.max_seq_len > self.max_model_len:
             raise CapacityError("sequence length", int(arrays.max_seq_len), self.max_model_len)
         self.upload(arrays)
@@ -369,26 +406,29 @@ class ModelRunner:
             # the tokens of this step are the previous step's picks, taken on the device (the host
             # runs ahead without reading them back; request order must not have changed)
             self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
-        b = self._bucket(S)
         long_context = bool(arrays.max_seq_len > LONG_CONTEXT_KEYS)
-        key = (b, parity, long_context)
-        graph = self._graphs.get(key)
-        if graph is None:
-            # first step of this class: run it eagerly (that is this step's result), then record
-            # the same launches for the steps to come
-            self._decode_eager(b, parity, long_context)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            n0 = kernels.launch_count()
-            with torch.cuda.graph(g, pool=self._graph_pool):
-                self._decode_eager(b, parity, long_context)
-            self._graph_launches[key] = kernels.launch_count() - n0
-            kernels.count_launches(-self._graph_launches[key])      # recorded, not run
-            self._graphs[key] = g
-            self._graph_pool = self._graph_pool or g.pool()
+        if not self.decode_graphs:
+            self._decode_eager(S, parity, long_context)      # nothing is recorded: no padding needed
         else:
-            graph.replay()
-            kernels.count_launches(self._graph_launches[key])
+            b = self._bucket(S)
+            key = (b, parity, long_context)
+            graph = self._graphs.get(key)
+            if graph is None:
+                # first step of this class: run it eagerly (that is this step's result), then record
+                # the same launches for the steps to come. Padding requests (no rows, state slot 0)
+                # are something a recorded step's kernels skip on the device; a model with
+                # per-request state is not shown them before it has proved recordable.
+                self._decode_eager(S if self.pools.state else b, parity, long_context)
+                try:
+                    self._record_decode(key)
+                except Exception as e:      # a part that cannot be recorded (it reads device data on the host, say)
+                    self.decode_graphs = False
+                    self._graphs.clear()
+                    print(f"[vllm_oxide_b200] decode steps are not recorded as CUDA graphs from here on: {type(e).__name__}: {e}",
+                          file=sys.stderr, flush=True)
+            else:
+                graph.replay()
+                kernels.count_launches(self._graph_launches[key])
         self.steps_run += 1
         if not read:
             ev = torch.cuda.Event()
@@ -397,6 +437,26 @@ class ModelRunner:
         # the picked tokens were copied to pinned host memory by the step itself
         torch.cuda.current_stream().synchronize()
         return self.sampled_host_np[parity, :S].tolist()
+
+    def decode_arrays(self, scheduler, plan):
+        """The device arrays of a decode step's plan, in the decode steps' layout."""
+        L = self.decode_layout
+        return scheduler.arrays(plan, L["rows_cap"], L["seqs_cap"], L["logits_cap"], self.max_pages, self.spec.vocab_size)
+
+    def _record_decode(self, key) -> None:
+        """Record the launches of a decode step of this class (nothing runs while recording)."""
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = kernels.launch_count()
+        try:
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                self._decode_eager(*key)
+        finally:
+            launches = kernels.launch_count() - n0
+            kernels.count_launches(-launches)                       # recorded, not run
+        self._graph_launches[key] = launches
+        self._graphs[key] = g
+        self._graph_pool = self._graph_pool or g.pool()
 
     def read_decode(self, event, count: int, parity: int) -> List[int]:
         """The picked tokens of a decode step launched without reading."""

@@ -1,8 +1,9 @@
 """Error types of the engine.
 
 One class per failure kind, after the reference's single error enum
-(crates/engine/src/error.rs:8-58): shape mismatches, capacity limits, a block
-table that does not cover its tokens, indices outside the pool, NaN in logits.
+(crates/engine/src/error.rs:8-58): shape mismatches, capacity limits, NaN in logits.
+(A block table that does not cover its tokens and a page outside the pool are raised by the
+native runtime as `RuntimeFault`.)
 The loader's errors follow crates/engine/src/weights.rs:66-89.
 """
 
@@ -32,20 +33,6 @@ class CapacityError(EngineError):
         self.what = what
         self.need = need
         self.limit = limit
-
-
-class BlockTableTooShort(EngineError):
-    """A block table covers fewer tokens than the step addresses
-    (crates/engine/src/backend/paged.rs:57-80)."""
-
-    def __init__(self, op: str, tokens: int, needed: int, have: int):
-        super().__init__(
-            f"{op}: block table too short: {tokens} tokens need {needed} blocks, table has {have}")
-        self.op, self.tokens, self.needed, self.have = op, tokens, needed, have
-
-
-class OutOfPages(EngineError):
-    """The page pool cannot serve an allocation and nothing may be preempted."""
 
 
 class NaNError(EngineError):

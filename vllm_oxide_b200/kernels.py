@@ -160,20 +160,6 @@ _pdl_on = False
 TENSOR_CORE_HEAD_DIMS = (64, 128)       # head sizes the tensor-core attention kernels are built for
 
 
-def modules_for(dtype, head_dims=(), max_rows: Optional[int] = None) -> tuple:
-    """The kernel modules an engine uses, by its compute dtype, the head sizes of its attention
-    mixers and the most rows a step may have: only these are compiled (side by side) at its first
-    start. Anything else a step turns out to need is still built when it is first called."""
-    if dtype == torch.float32:
-        return ("elementwise", "gemm_f32", "attention", "sampling")
-    mods = ["elementwise", "gemm_sm100", "attention", "sampling"]
-    if max_rows is None or max_rows >= PAIR_GEMM_FROM_ROWS:
-        mods.append("gemm_sm100_pair")
-    if any(hd in TENSOR_CORE_HEAD_DIMS for hd in head_dims):
-        mods += ["attention_mma", "attention_sm100"]
-    return tuple(mods)
-
-
 def preload(modules=_MODULES) -> None:
     """Build (side by side) and load kernel modules now, so that compile time is spent at start-up."""
     from .csrc.build import ensure_built
@@ -209,35 +195,6 @@ def set_pdl(on: bool) -> None:
             f.argtypes = [_I]
             f.restype = None
             f(1 if _pdl_on else 0)
-
-
-KERNEL_TAGS = {1: "embed", 2: "add_rmsnorm", 3: "add_residual", 4: "rope_kv_write", 5: "swiglu", 6: "paged_attention",
-               7: "attn_prefill_mma", 8: "attn_decode_mma", 9: "pick_partial", 10: "pick_final", 11: "gemm_f32",
-               12: "gemm_sm100", 13: "gemm_sm100_persistent"}
-
-
-def set_timeline(buf: Optional[torch.Tensor]) -> None:
-    """A debugging aid (needs libraries built with VOB_TIMELINE=1 in the environment; otherwise
-    nothing is recorded): with a zeroed int64 CUDA tensor of 1 + 3 * 4096 elements, block 0 of every
-    kernel launched afterwards appends (tag, time before its wait, time after its wait) in global
-    nanoseconds; `read_timeline` decodes it. None switches it off."""
-    from .csrc.build import _loaded
-    if buf is not None and (buf.dtype != torch.int64 or not buf.is_cuda or buf.numel() < 1 + 3 * 4096):
-        raise ShapeError("set_timeline", "need an int64 CUDA tensor of 1 + 3 * 4096 elements")
-    for m in _MODULES:
-        if m in _loaded:
-            f = getattr(_loaded[m], f"vob_set_timeline_{m}")
-            f.argtypes = [_P]
-            f.restype = _I
-            _check(f(_ptr(buf)), "set_timeline", launches=0)
-
-
-def read_timeline(buf: torch.Tensor):
-    """[(kernel name, ns before the wait, ns after the wait)] in the order the waits returned."""
-    h = buf.cpu().tolist()
-    n = min(h[0], 4096)
-    rows = [(KERNEL_TAGS.get(h[1 + 3 * e], str(h[1 + 3 * e])), h[2 + 3 * e], h[3 + 3 * e]) for e in range(n)]
-    return sorted(rows, key=lambda r: r[2])
 
 
 # ------------------------------------------------------------------------------------ embedding
@@ -283,18 +240,6 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     f = _fn("elementwise", "vob_add_rmsnorm", [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P])
     _check(f(_ptr(resid), _ptr(delta), _code(delta, op) if delta is not None else 0, _ptr(weight), _ptr(rows),
              _ptr(out), _code(out, op), R, h, float(eps), _stream()), op)
-
-
-@_timed
-def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
-    """resid += delta in float32."""
-    op = "add_residual"
-    _cuda(op, resid, delta)
-    if resid.dtype != torch.float32 or not resid.is_contiguous() or delta.shape != resid.shape or not delta.is_contiguous():
-        raise ShapeError(op, f"need contiguous float32 residual and a delta of the same shape, got "
-                             f"{resid.dtype} {list(resid.shape)} and {list(delta.shape)}")
-    f = _fn("elementwise", "vob_add_residual", [_P, _P, _I, _L, _P])
-    _check(f(_ptr(resid), _ptr(delta), _code(delta, op), resid.numel(), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ rope + cache write
@@ -666,6 +611,14 @@ def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mo
     f = _fn("gemm_sm100", "vob_gemm_sm100_ex", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, ctypes.POINTER(_EpiArgs), _P, _P])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _P(out_ptr), ldc, out_code, T, n_features, K, int(splits), int(mode),
              ctypes.byref(ea), _ptr(_scratch_for(a.device).err), _stream()), op)
+
+
+def gemm_sm100_test_hooks(extra_tx_bytes: int = 0, wait_limit_ms: float = 0.0) -> None:
+    """For the test of the kernels' give-up path only: the next one-block launches of the few-token
+    product expect `extra_tx_bytes` more than their loads bring (their waits then run out), and
+    waits give up after `wait_limit_ms` (0: the default of two seconds). (0, 0) restores both."""
+    f = _fn("gemm_sm100", "vob_gemm_sm100_test_hooks", [_I, ctypes.c_ulonglong])
+    _check(f(int(extra_tx_bytes), int(wait_limit_ms * 1e6)), "gemm_sm100_test_hooks", launches=0)
 
 
 def gemm_sm100_check() -> None:

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import CacheSpec, FoldedState, LayerCache, Mixer, StepContext
+from .base import CacheSpec, FoldedState, LayerCache, Mixer, StepContext, aligned
 from .linear import matmul, to_compute
 
 
@@ -66,9 +66,27 @@ class Attention(Mixer):
     def weight_bytes(self) -> int:
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
 
+    def _few_rows_path(self, rows: int) -> bool:
+        """Steps of few rows: rotary positions and the cache write happen in the projection's epilogue."""
+        return (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and rows <= kernels.FUSED_GEMM_BEST_ROWS
+                and kernels.gemm_qkv_rope_supported(self.hd) and self.hidden % 8 == 0)
+
     def workspace_bytes(self, rows: int) -> int:
+        """q (or q|k|v side by side) and the attention output, besides the result the block gives a place for."""
         es = 2 if self.dtype == torch.bfloat16 else 4
-        return rows * (self.w_qkv.shape[0] + self.H * self.hd) * es + 2 * 256
+        q_cols = self.H * self.hd if self._few_rows_path(rows) else self.w_qkv.shape[0]
+        return aligned(rows * q_cols * es) + aligned(rows * self.H * self.hd * es)
+
+    def folded_workspace_bytes(self, rows: int) -> int:
+        return 2 * aligned(rows * self.H * self.hd * 2)
+
+    def kernel_modules(self, dtype, max_rows):
+        if dtype == torch.float32:
+            return ("elementwise", "gemm_f32", "attention")
+        mods = ["elementwise", "gemm_sm100", "attention"]
+        if self.hd in kernels.TENSOR_CORE_HEAD_DIMS:
+            mods += ["attention_mma", "attention_sm100"]
+        return tuple(mods)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
         if cache is None:
@@ -76,9 +94,7 @@ class Attention(Mixer):
         T = x.shape[0]
         qd, kd = self.H * self.hd, self.KV * self.hd
         inv_freq = self.position.inv_freq if self.position is not None else None
-        if (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and cache.write
-                and T <= kernels.FUSED_GEMM_BEST_ROWS and kernels.gemm_qkv_rope_supported(self.hd)
-                and kernels.gemm_sm100_supported(x, self.w_qkv)):
+        if self._few_rows_path(T) and cache.write and kernels.gemm_sm100_supported(x, self.w_qkv):
             # few rows: rotary positions and the cache write happen in the projection's epilogue
             q = ctx.alloc((T, qd))
             kernels.gemm_qkv_rope(x, self.w_qkv, q, ctx.positions, ctx.slot_mapping[cache.group], inv_freq,

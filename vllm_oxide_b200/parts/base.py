@@ -9,13 +9,16 @@ in a `StepContext`.
 
 What each kind of part must offer:
 
-* Mixer        - `cache_spec()` (pages it needs: all keys, a window, or None),
-                 `state_spec()` (fixed-size per-request state, or None),
+* Mixer        - `cache_spec()` (pages it needs: which tensors a page holds, for all keys or a
+                 window of them; or None), `state_spec()` (fixed-size per-request state, or None),
                  `forward(x, ctx, cache, state, out=None) -> [T, hidden]` in the compute dtype.
 * FeedForward  - `forward(x, ctx, out=None) -> [T, hidden]`.
 * Norm         - `forward(resid, delta, ctx, rows=None) -> normed`; adds `delta` into the
                  float32 residual first (the residual sum is kept in 32-bit).
 * PositionEncoding - whatever its mixer asks of it; the rotary part offers `inv_freq`.
+Every part may also offer `workspace_bytes(rows)` (what it takes from the step's workspace, to
+the byte), `kernel_modules(dtype, max_rows)` (the kernel libraries it launches, so that an
+engine compiles them at its start) and `weight_bytes()`.
 """
 from __future__ import annotations
 
@@ -27,15 +30,36 @@ import torch
 
 # ------------------------------------------------------------------------------ cache / state needs
 @dataclass(frozen=True)
+class PagedTensorSpec:
+    """One tensor of a paged cache: per token `heads` vectors of `width` elements, laid out as
+    [num_pages, heads, page_size, width] (head-major inside a page). `dtype` None means the
+    engine's compute dtype."""
+    heads: int
+    width: int
+    dtype: Optional[torch.dtype] = None
+
+
+@dataclass(frozen=True)
 class CacheSpec:
-    """Pages a mixer needs: keys and values of `num_kv_heads` x `head_dim` per token."""
-    num_kv_heads: int
-    head_dim: int
+    """Pages a mixer needs. The mixer says which tensors a page holds: keys and values of
+    `num_kv_heads` x `head_dim` (the default, `CacheSpec(kv_heads, head_dim)`), or any other set
+    given as `tensors` (one latent vector per token, keys and values of different widths, ...),
+    and whether every token is kept ("full") or only the last `window` ("window")."""
+    num_kv_heads: int = 0
+    head_dim: int = 0
     kind: str = "full"          # "full": every key is kept; "window": the last `window` keys
     window: int = 0
+    tensors: Tuple[PagedTensorSpec, ...] = ()
+
+    def paged_tensors(self) -> Tuple[PagedTensorSpec, ...]:
+        """The tensors of one page: `tensors` if given, else a key and a value tensor."""
+        if self.tensors:
+            return self.tensors
+        kv = PagedTensorSpec(self.num_kv_heads, self.head_dim)
+        return (kv, kv)
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.window, self.num_kv_heads, self.head_dim)
+        return (self.kind, self.window, self.paged_tensors())
 
 
 @dataclass(frozen=True)
@@ -47,12 +71,24 @@ class StateSpec:
 
 @dataclass
 class LayerCache:
-    """One cache of one call in the schedule: this layer's pages and which group's block tables
-    address them."""
-    k: torch.Tensor             # [num_pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    """One cache of one call in the schedule: this layer's pages (one tensor per entry of its
+    `CacheSpec.paged_tensors()`, each [num_pages, heads, page_size, width]) and which group's
+    block tables address them. `k` and `v` are the first two (the default key / value pair)."""
+    tensors: Tuple[torch.Tensor, ...]
     group: int
     write: bool = True          # False: the call reads a cache that another call wrote
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.tensors[0]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors[1]
+
+    @property
+    def page_size(self) -> int:
+        return self.tensors[0].shape[2]
 
 
 # ------------------------------------------------------------------------------ per-step facts
@@ -60,13 +96,19 @@ _ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.in
                  torch.int8: 1, torch.float64: 8}
 
 
+def aligned(nbytes: int) -> int:
+    """Bytes one workspace allocation of `nbytes` takes (allocations are multiples of 256 bytes)."""
+    return (int(nbytes) + 255) & ~255
+
+
 class Workspace:
     """A bump allocator over one device buffer: a step's activations live here, so that a step
     allocates nothing and its tensors sit at the same addresses every time. The reference's
-    per-step arena (crates/engine/src/arena.rs:92-158) with scopes that rewind on close."""
+    per-step arena (crates/engine/src/arena.rs:92-158) with scopes that rewind on close. Every
+    allocation takes `aligned(nbytes)` bytes, so a part can say to the byte what it will take."""
 
     def __init__(self, nbytes: int, device):
-        self.buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        self.buf = torch.empty(max(aligned(nbytes), 256), dtype=torch.uint8, device=device)
         self.top = 0
         self.high_water = 0
 
@@ -75,11 +117,11 @@ class Workspace:
         for s in shape:
             n *= int(s)
         nbytes = n * _ELEMENT_SIZE[dtype]
-        start = (self.top + 255) & ~255
-        if start + nbytes > self.buf.numel():
+        start = self.top                       # a multiple of 256: every allocation is rounded up
+        if start + aligned(nbytes) > self.buf.numel():
             from ..errors import CapacityError
-            raise CapacityError("step workspace", start + nbytes, self.buf.numel())
-        self.top = start + nbytes
+            raise CapacityError("step workspace", start + aligned(nbytes), self.buf.numel())
+        self.top = start + aligned(nbytes)
         self.high_water = max(self.high_water, self.top)
         return self.buf[start:start + nbytes].view(dtype).view(*shape)
 
@@ -167,7 +209,13 @@ class Mixer:
         return None
 
     def workspace_bytes(self, rows: int) -> int:
+        """Bytes this part takes from the step's workspace in a step of `rows` rows or fewer."""
         return 0
+
+    def kernel_modules(self, dtype: torch.dtype, max_rows: int) -> Tuple[str, ...]:
+        """Names of the kernel libraries (csrc/<name>.cu) this part launches in an engine of
+        this compute dtype whose steps have at most `max_rows` rows."""
+        return ()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
                 state: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -180,11 +228,24 @@ class FeedForward:
     def workspace_bytes(self, rows: int) -> int:
         return 0
 
+    def kernel_modules(self, dtype: torch.dtype, max_rows: int) -> Tuple[str, ...]:
+        return ()
+
     def forward(self, x: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Norm:
+    # True for a norm that is a per-token scale times a per-feature weight (`weight`, `eps`):
+    # that form commutes with a matrix product and can be folded into it (see FoldedState).
+    scale_and_weight = False
+
+    def workspace_bytes(self, rows: int, act_bytes: int) -> int:
+        return 0
+
+    def kernel_modules(self, dtype: torch.dtype, max_rows: int) -> Tuple[str, ...]:
+        return ()
+
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
                 rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None) -> torch.Tensor:
         raise NotImplementedError

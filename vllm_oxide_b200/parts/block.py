@@ -11,8 +11,7 @@ from typing import Optional
 
 import torch
 
-from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StepContext
-from .rmsnorm import RMSNorm
+from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StepContext, aligned
 
 
 class Block:
@@ -23,20 +22,33 @@ class Block:
         return sum(getattr(p, "weight_bytes", lambda: 0)() for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
 
     def workspace_bytes(self, rows: int, hidden: int, act_bytes: int) -> int:
-        """Peak scratch of one run of the block: the mixer's output, then the larger of
-        (normed input + mixer scratch) and (normed input + feed-forward scratch)."""
-        row = rows * hidden * act_bytes + 256
-        return 2 * row + max(self.mixer.workspace_bytes(rows), self.feed_forward.workspace_bytes(rows))
+        """Peak scratch of one run of the block, read off the scopes of `forward`: the mixer's
+        output, then the larger of (first norm's output + mixer scratch) and (second norm's output +
+        feed-forward scratch)."""
+        mixed = aligned(rows * hidden * act_bytes)
+        return mixed + max(self.norm1.workspace_bytes(rows, act_bytes) + self.mixer.workspace_bytes(rows),
+                           self.norm2.workspace_bytes(rows, act_bytes) + self.feed_forward.workspace_bytes(rows))
+
+    def folded_workspace_bytes(self, rows: int) -> int:
+        """Peak scratch of `forward_folded` (0 for parts that do not say)."""
+        return max(getattr(self.mixer, "folded_workspace_bytes", lambda r: 0)(rows),
+                   getattr(self.feed_forward, "folded_workspace_bytes", lambda r: 0)(rows))
+
+    def kernel_modules(self, dtype, max_rows):
+        mods = []
+        for p in (self.norm1, self.mixer, self.norm2, self.feed_forward):
+            mods += list(getattr(p, "kernel_modules", lambda d, r: ())(dtype, max_rows))
+        return tuple(mods)
 
     def can_fold(self) -> bool:
-        """Whether this block can run in folded form (see FoldedState): both norms are RMSNorms (a
-        per-token scale and a per-feature weight, which is what folds into the neighbouring
-        products) and mixer and feed-forward both offer it."""
-        return (isinstance(self.norm1, RMSNorm) and isinstance(self.norm2, RMSNorm)
+        """Whether this block can run in folded form (see FoldedState): both norms are a per-token
+        scale and a per-feature weight (`Norm.scale_and_weight`), which is what folds into the
+        neighbouring products, and mixer and feed-forward both offer it."""
+        return (self.norm1.scale_and_weight and self.norm2.scale_and_weight
                 and getattr(self.mixer, "can_fold", lambda: False)() and getattr(self.feed_forward, "can_fold", lambda: False)()
                 and self.mixer.state_spec() is None)
 
-    def forward_folded(self, st: FoldedState, ctx: StepContext, cache: Optional[LayerCache], next_norm: RMSNorm) -> None:
+    def forward_folded(self, st: FoldedState, ctx: StepContext, cache: Optional[LayerCache], next_norm: Norm) -> None:
         """The block on the folded residual: no norm kernel, no separate residual add. `next_norm`
         is the norm that will read the residual after this block (the next block's first norm, or
         the model's final norm)."""

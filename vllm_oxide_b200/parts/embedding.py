@@ -19,11 +19,13 @@ class Embedding:
     def weight_bytes_per_row(self) -> int:
         return self.hidden * self.table.element_size()
 
+    def kernel_modules(self, dtype, max_rows):
+        return ("elementwise",)
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         resid = ctx.alloc((ctx.rows, self.hidden), torch.float32)
         kernels.embed(self.table, ctx.tokens, resid, self.err_flag)
         return resid
-
 
     def forward_folded(self, ctx: StepContext, next_norm) -> FoldedState:
         """The embedding with the first norm's input prepared (see FoldedState)."""
@@ -43,6 +45,9 @@ class LMHead:
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
+
+    def kernel_modules(self, dtype, max_rows):
+        return ("gemm_f32",) if dtype == torch.float32 else ("gemm_sm100",)
 
     def forward(self, normed: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         kernels.linear(normed, self.weight, out)

@@ -12,10 +12,12 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import Norm, StepContext
+from .base import Norm, StepContext, aligned
 
 
 class RMSNorm(Norm):
+    scale_and_weight = True       # out = weight * (x * scale(x)): folds into the products around it
+
     def __init__(self, weight: torch.Tensor, eps: float, device):
         if weight.dim() != 1:
             raise ValueError(f"RMSNorm weight must be a vector, got {list(weight.shape)}")
@@ -26,6 +28,12 @@ class RMSNorm(Norm):
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * 4
+
+    def workspace_bytes(self, rows: int, act_bytes: int) -> int:
+        return aligned(rows * self.width * act_bytes)
+
+    def kernel_modules(self, dtype, max_rows):
+        return ("elementwise",)
 
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
                 rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None) -> torch.Tensor:

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import FeedForward, FoldedState, StepContext
+from .base import FeedForward, FoldedState, StepContext, aligned
 from .linear import matmul, to_compute
 
 
@@ -25,9 +25,39 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
+    def _path(self, rows: int, aligned_input: bool = True) -> str:
+        """Which kernels a step of `rows` rows runs: "few" (one tcgen05 kernel, activation in its
+        epilogue), "pair" (the two-SM product with the activation in its epilogue) or "separate"
+        (a product to gate|up, then the activation kernel)."""
+        ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0
+        if ok and rows <= kernels.FUSED_GEMM_BEST_ROWS:
+            return "few"
+        if ok and rows >= kernels.PAIR_GEMM_FROM_ROWS:
+            return "pair"
+        return "separate"
+
     def workspace_bytes(self, rows: int) -> int:
+        """The activation [rows, inter]; on the "separate" path gate|up [rows, 2 * inter] beside it.
+        The largest of any step of at most `rows` rows (a step just below the row count where
+        the two-SM kernel takes over needs more than one just above)."""
         es = 2 if self.dtype == torch.bfloat16 else 4
-        return rows * 3 * self.inter * es + 2 * 256
+
+        def at(r):
+            act = aligned(r * self.inter * es)
+            return act + aligned(r * 2 * self.inter * es) if self._path(r) == "separate" else act
+        below = kernels.PAIR_GEMM_FROM_ROWS - 1
+        return max(at(rows), at(below)) if rows > below else at(rows)
+
+    def folded_workspace_bytes(self, rows: int) -> int:
+        return aligned(rows * self.inter * 2)
+
+    def kernel_modules(self, dtype, max_rows):
+        if dtype == torch.float32:
+            return ("elementwise", "gemm_f32")
+        mods = ["elementwise", "gemm_sm100"]
+        if max_rows >= kernels.PAIR_GEMM_FROM_ROWS:
+            mods.append("gemm_sm100_pair")
+        return tuple(mods)
 
     def can_fold(self) -> bool:
         return self.dtype == torch.bfloat16 and self.fused and self.hidden % 8 == 0 and self.inter % 8 == 0
@@ -43,12 +73,11 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]
         act = ctx.alloc((T, self.inter))
-        if (self.dtype == torch.bfloat16 and T <= kernels.FUSED_GEMM_BEST_ROWS and self.fused
-                and kernels.gemm_sm100_supported(x, self.w_gate_up)):
+        path = self._path(T, kernels.gemm_sm100_supported(x, self.w_gate_up))
+        if path == "few":
             # few rows: one kernel, the activation applied in the product's epilogue
             kernels.gemm_swiglu(x, self.w_gate_up, act)
-        elif (self.dtype == torch.bfloat16 and T >= kernels.PAIR_GEMM_FROM_ROWS and self.fused
-                and kernels.gemm_sm100_supported(x, self.w_gate_up)):
+        elif path == "pair":
             # many rows: the two-SM product with the activation in its epilogue (gate and up never
             # go to memory)
             kernels.gemm_pair_swiglu(x, self.w_gate_up, act)

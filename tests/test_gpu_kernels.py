@@ -743,7 +743,7 @@ def test_a_wait_that_runs_out_raises_the_error_word_and_harms_nothing():
     torch.cuda.synchronize()
     kernels.gemm_sm100_check()                                   # nothing wrong so far
     want = a.double().cpu() @ w.double().cpu().t()
-    assert max_rel_diff(out.cpu(), want) <= 1e-5
+    assert rel(out.cpu(), want) <= 1e-5
     kernels.gemm_sm100_test_hooks(extra_tx_bytes=16, wait_limit_ms=10.0)
     try:
         kernels.gemm_sm100(a, w, torch.zeros_like(out), splits=1)
@@ -760,5 +760,5 @@ def test_a_wait_that_runs_out_raises_the_error_word_and_harms_nothing():
     kernels.gemm_sm100(a, w2, big)                               # and a launch with a cluster split
     torch.cuda.synchronize()
     kernels.gemm_sm100_check()
-    assert max_rel_diff(out2.cpu(), want) <= 1e-5
-    assert max_rel_diff(big.cpu(), a.double().cpu() @ w2.double().cpu().t()) <= 1e-5
+    assert rel(out2.cpu(), want) <= 1e-5
+    assert rel(big.cpu(), a.double().cpu() @ w2.double().cpu().t()) <= 1e-5

@@ -271,6 +271,44 @@ def test_long_context_beside_a_short_one(tmp_path_factory):
     print(f"long context: worst rel diff {worst:.2e}")
 
 
+@pytest.mark.parametrize("name", ["D", "1Bv"])
+def test_a_wrong_page_in_one_layer_is_seen_in_bfloat16(tmp_path_factory, name):
+    """What the bfloat16 tolerance cannot hide: the traces above run once more while ONE layer's
+    attention reads a wrong page in place of one of the request's own (its third page where the
+    second should be; the cache itself is right, the other layers read it rightly). Rows that see
+    that page then differ from the plain implementation by more than the tolerance the tests allow,
+    for a portion kernel's rows and for the decode kernel's alike: a fault of that kind fails the
+    bfloat16 tests, not only the 32-bit ones. (Pages in swapped ORDER would not show in rows behind
+    them: a softmax-weighted sum does not depend on the order of its keys.)"""
+    dtype = torch.bfloat16
+    cfg, _, page = TINY[name]
+    model_dir = make_model_dir(tmp_path_factory.getbasetemp(), name)
+    reqs = _requests(cfg.vocab_size, [127], 100)
+    s = _session(model_dir, dtype, 128, page)
+    mixer = s.runner.spec.blocks[-1].mixer
+    attend = mixer.attend
+
+    def swapped(q, out, ctx, cache):
+        bt = ctx.block_tables[cache.group]
+        keep = bt[:, 1].clone()
+        bt[:, 1] = bt[:, 2]
+        try:
+            attend(q, out, ctx, cache)
+        finally:
+            bt[:, 1] = keep
+    for what, steps in (("whole", whole_steps(reqs)), ("bulk+tail", bulk_tail_steps(reqs))):
+        check(run_trace(s, steps), model_dir, reqs, dtype, what)          # the engine as it is: within the tolerance
+        mixer.attend = swapped
+        try:
+            got = run_trace(s, steps)
+        finally:
+            mixer.attend = attend
+        ref = oracle(model_dir, reqs["r0"])
+        late = [max_rel_diff(got[k], ref[k[1]]) for k in got if k[1] >= 3 * page]
+        print(f"{name} {what}: rows behind the wrong page differ by {min(late):.2e} .. {max(late):.2e} (tolerance {TOL[dtype]:.0e})")
+        assert late and min(late) > TOL[dtype], f"{what}: a wrong page changed the logits by only {min(late):.2e}"
+
+
 def test_f32_cuts_agree_closely(tmp_path_factory):
     """In 32-bit, the same position computed whole, token by token and in portions agrees far
     inside the tolerance against the oracle: the reference's bound between two of its own paths

@@ -84,6 +84,7 @@ def max_rel_diff(a: torch.Tensor, b: torch.Tensor) -> float:
 # two float32 paths (crates/engine/src/model.rs:492,536), twice that against float64 here.
 # bfloat16: activations, cache and weights are rounded to 8 mantissa bits (relative 2^-9 per
 # rounding); about ten roundings per layer, independent, over <= 3 layers, on top of products
-# accumulated in float32: 2^-9 * sqrt(30) ~ 1.1e-2 of the largest logit; 3e-2 leaves room for the
-# vocabulary-wide maximum of that error.
-TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
+# accumulated in float32: 2^-9 * sqrt(30) ~ 1.1e-2 of the largest logit; 2e-2 leaves room for the
+# vocabulary-wide maximum of that error (the worst seen over all traces is 1.5e-2). One wrong page
+# read by one layer shows as 6e-2 and more (test_a_wrong_page_in_one_layer_is_seen_in_bfloat16).
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}

@@ -254,6 +254,11 @@ class LLM:
             self._generated.pop(rid)
         return outs
 
+    def drain(self) -> None:
+        """Wait for the step that was launched ahead, if any, and book its tokens; requests it ends
+        are handed out by the next `step`. Afterwards nothing of this engine is in flight."""
+        self._finish_inflight()
+
     def abort(self, request_id: int) -> None:
         self._finish_inflight()
         if request_id not in self._params:

@@ -445,18 +445,20 @@ def kernel_case(argv):
             out = torch.empty(a.rows, a.out // 2, dtype=bf, device=dev)
             launches = [lambda w=w: kernels.gemm_pair_swiglu(x, w, out) for w in ws]
         elif a.kernel == "gemm_fused":
+            fused = kernels.gemm_fused
             if a.epilogue == "swiglu":
                 out = torch.empty(a.rows, a.out // 2, dtype=bf, device=dev)
-                launches = [lambda w=w: kernels.gemm_fused(x, w, out, kernels.EPI_SWIGLU, a.out // 2) for w in ws]
+                launches = [lambda w=w: fused(x, w, out, kernels.EPI_SWIGLU, a.out // 2) for w in ws]
             elif a.epilogue == "resid":
                 out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
                 resid = torch.zeros(a.rows, a.out, dtype=torch.float32, device=dev)
                 nw = torch.ones(a.out, dtype=torch.float32, device=dev)
                 ssq = torch.zeros(-(-a.out // 128), 64, dtype=torch.float32, device=dev)
-                launches = [lambda w=w: kernels.gemm_fused(x, w, None, kernels.EPI_RESID, a.out, resid=(resid, nw, out, ssq)) for w in ws]
+                ssq = torch.zeros(-(-a.out // 128), 64, dtype=torch.float32, device=dev)
+                launches = [lambda w=w: fused(x, w, None, kernels.EPI_RESID, a.out, resid=(resid, nw, out, ssq)) for w in ws]
             else:
                 out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
-                launches = [lambda w=w: kernels.gemm_fused(x, w, out, kernels.EPI_STORE, a.out) for w in ws]
+                launches = [lambda w=w: fused(x, w, out, kernels.EPI_STORE, a.out) for w in ws]
         else:
             out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
             if a.kernel == "gemm_library":           # the library product the engine uses for many rows, for comparison
@@ -632,6 +634,9 @@ def main():
     ap.add_argument("--serve-min", type=int, default=128)
     ap.add_argument("--serve-max", type=int, default=4096)
     ap.add_argument("--timeline", action="store_true", help="per-kernel times of one decode step (VOB_TIMELINE=1 build)")
+    ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
+                    help="an experiment: steps of up to R rows (at most 64) take the fused few-row kernels instead of the "
+                         "engine's own switch-over point")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -653,6 +658,12 @@ def main():
         return 2
 
     import torch
+    if a.fold_rows is not None:
+        import vllm_oxide_b200.engine.runner as er
+        import vllm_oxide_b200.parts.base as pb
+        import vllm_oxide_b200.parts.embedding as pe
+        from vllm_oxide_b200 import kernels
+        kernels.FUSED_GEMM_BEST_ROWS = kernels.LIBRARY_GEMM_ABOVE_ROWS = pb.FOLD_ROWS = pe.FOLD_ROWS = er.FOLD_ROWS = a.fold_rows
     sz = SIZES[a.sizes]
     full_layers = sz["layers"]
     layers = a.layers or full_layers

@@ -281,7 +281,9 @@ def test_run_order_is_data(dt, kind):
     toks = [(7 * i + 3) % 50 for i in range(41)]
     want = _toy_plain(W, dims, kind, toks)
     whole = s.run_step({"step": 0, "entries": [{"id": "a", "tokens": toks, "want": list(range(41))}], "end": ["a"]})
-    tol = TOL[dt]
+    # these toy models run three layer calls with weights of standard deviation 0.3: more and larger
+    # roundings than the Llama configurations the shared bfloat16 tolerance is stated for
+    tol = TOL[dt] if dt == torch.float32 else 3e-2
     assert max_rel_diff(whole, want) <= tol
     got, p = [], 0
     for i, n in enumerate([5, 11, 2, 1, 16, 6]):

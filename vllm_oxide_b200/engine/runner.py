@@ -115,6 +115,7 @@ class ModelRunner:
         self._stage_next = 0
         self.step_dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         # workspace: residual + two pending buffers + the largest block + the head's chunk
+        self._foldable = None
         V = self.spec.vocab_size
         self.workspace_bytes = self.workspace_formula(self.rows_cap)
         self.workspace = Workspace(self.workspace_bytes, self.device)
@@ -135,7 +136,6 @@ class ModelRunner:
         self._step_seen = {}
         self.step_graph_after = int(getattr(engine, "step_graphs", 0))
         self.step_graph_replays = 0
-        self._foldable = None
         self._folded = None
         self._graph_launches = {}
         self._graph_pool = None
@@ -162,7 +162,16 @@ class ModelRunner:
         block = max((b.workspace_bytes(rows, h, es) for b in self.spec.blocks), default=0)
         n = min(self.logit_chunk, rows)
         head = aligned(n * V * 4) + self.spec.final_norm.workspace_bytes(n, es)
-        return resid + pending + max(block, head)
+        total = resid + pending + max(block, head)
+        if self._can_fold(1):
+            # steps of few rows run in folded form (FoldedState): residual, the next norm's input, the
+            # partial sums of squares, and the blocks' folded scratch or the head
+            r = min(rows, FOLD_ROWS)
+            state = aligned(r * h * 4) + aligned(r * h * 2) + aligned(-(-h // 128) * FOLD_ROWS * 4)
+            fblock = max((b.folded_workspace_bytes(r) for b in self.spec.blocks), default=0)
+            fhead = aligned(min(self.logit_chunk, r) * V * 4) + self.spec.final_norm.workspace_bytes(min(self.logit_chunk, r), es)
+            total = max(total, state + max(fblock, fhead))
+        return total
 
     @classmethod
     def from_dir(cls, model_dir: str, engine: EngineConfig, random_weights_seed: Optional[int] = None,

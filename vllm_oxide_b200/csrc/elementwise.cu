@@ -367,10 +367,11 @@ rope_kv_write_token_kernel(T* __restrict__ q, long long q_stride, T* __restrict_
     }
 }
 
-// The same with 16-byte accesses, ROPE_TOK tokens per block: the tokens' sines and cosines go to
-// shared memory once, then every thread takes 16-byte pieces of heads: it first loads all of its
-// pieces (the first half of a head and the half that pairs with it), then rotates and stores
-// them, so that a block has its whole traffic in flight at once. Needs 16-byte aligned rows.
+// The same with 16-byte accesses, ROPE_TOK tokens per block: every thread takes 16-byte pieces of
+// heads: it first requests all of its pieces (the first half of a head, the half that pairs with it
+// and, for a k head, the pieces of v that go to the cache with it), so that a block has its whole
+// traffic in flight at once; while they are on their way the tokens' sines and cosines go to shared
+// memory once; then the pieces are rotated and stored. Needs 16-byte aligned rows.
 constexpr int ROPE_TOK = 4;
 constexpr int ROPE_THREADS = 256;
 constexpr int ROPE_MAX_UNITS = 4;                  // pieces per thread handled in one go
@@ -390,37 +391,40 @@ rope_kv_write_token_vec_kernel(T* __restrict__ q, long long q_stride, T* __restr
     const int half = hd >> 1;
     float* sc = s_cs;
     float* ss = s_cs + ROPE_TOK * half;
-    for (int u = threadIdx.x; u < ntok * half; u += ROPE_THREADS) {
-        const int tt = u / half, i = u - tt * half;
-        float c = 1.f, s = 0.f;
-        if (inv_freq) {
-            float theta = (float)positions[t0 + tt] * inv_freq[i];
-            c = cosf(theta);
-            s = sinf(theta);
-        }
-        sc[u] = c;
-        ss[u] = s;
-    }
-    __syncthreads();
     const int chunks = half / E;                   // 16-byte pieces per half head
     const int heads = H + (k ? KV : 0);            // q heads, then k heads
     const int per_tok = heads * chunks;
     const int total = ntok * per_tok;
-    for (int base = 0; base < total; base += ROPE_THREADS * ROPE_MAX_UNITS) {
-        uint4 ua[ROPE_MAX_UNITS], ub[ROPE_MAX_UNITS];
-        T* pa[ROPE_MAX_UNITS];
+    uint4 ua[ROPE_MAX_UNITS], ub[ROPE_MAX_UNITS], va[ROPE_MAX_UNITS], vb[ROPE_MAX_UNITS];
+    T* pa[ROPE_MAX_UNITS];
+    long long cb[ROPE_MAX_UNITS];                  // where in the cache a piece of a k head (and of its v) goes; -1: nowhere
+    // every piece a thread handles in one round is requested before anything is computed
+    auto load_round = [&](int base) {
 #pragma unroll
         for (int j = 0; j < ROPE_MAX_UNITS; ++j) {
             const int u = base + j * ROPE_THREADS + threadIdx.x;
             pa[j] = nullptr;
+            cb[j] = -1;
             if (u < total) {
                 const int tt = u / per_tok, r = u - tt * per_tok, head = r / chunks, ch = r - head * chunks;
                 pa[j] = head < H ? q + (size_t)(t0 + tt) * q_stride + (size_t)head * hd + ch * E
                                  : k + (size_t)(t0 + tt) * k_stride + (size_t)(head - H) * hd + ch * E;
                 ua[j] = *reinterpret_cast<const uint4*>(pa[j]);
                 ub[j] = *reinterpret_cast<const uint4*>(pa[j] + half);
+                if (head >= H) {
+                    const int kh = head - H;
+                    const int slot = slots ? slots[t0 + tt] : -1;
+                    if (slot >= 0) {
+                        cb[j] = (long long)(((((size_t)(slot / page_size)) * KV + kh) * page_size + slot % page_size) * (size_t)hd) + ch * E;
+                        const T* vr = v + (size_t)(t0 + tt) * v_stride + (size_t)kh * hd + ch * E;
+                        va[j] = *reinterpret_cast<const uint4*>(vr);
+                        vb[j] = *reinterpret_cast<const uint4*>(vr + half);
+                    }
+                }
             }
         }
+    };
+    auto finish_round = [&](int base) {
 #pragma unroll
         for (int j = 0; j < ROPE_MAX_UNITS; ++j) {
             const int u = base + j * ROPE_THREADS + threadIdx.x;
@@ -443,19 +447,32 @@ rope_kv_write_token_vec_kernel(T* __restrict__ q, long long q_stride, T* __restr
                 *reinterpret_cast<uint4*>(pa[j]) = ra;
                 *reinterpret_cast<uint4*>(pa[j] + half) = rb;
             }
-            if (head >= H) {
-                const int kh = head - H;
-                const int slot = slots ? slots[t0 + tt] : -1;
-                if (slot >= 0) {
-                    const size_t cb = ((((size_t)(slot / page_size)) * KV + kh) * page_size + slot % page_size) * (size_t)hd;
-                    const T* vr = v + (size_t)(t0 + tt) * v_stride + (size_t)kh * hd;
-                    *reinterpret_cast<uint4*>(kcache + cb + ch * E) = ra;
-                    *reinterpret_cast<uint4*>(kcache + cb + half + ch * E) = rb;
-                    *reinterpret_cast<uint4*>(vcache + cb + ch * E) = *reinterpret_cast<const uint4*>(vr + ch * E);
-                    *reinterpret_cast<uint4*>(vcache + cb + half + ch * E) = *reinterpret_cast<const uint4*>(vr + half + ch * E);
-                }
+            if (cb[j] >= 0) {
+                *reinterpret_cast<uint4*>(kcache + cb[j]) = ra;
+                *reinterpret_cast<uint4*>(kcache + cb[j] + half) = rb;
+                *reinterpret_cast<uint4*>(vcache + cb[j]) = va[j];
+                *reinterpret_cast<uint4*>(vcache + cb[j] + half) = vb[j];
             }
         }
+    };
+    load_round(0);
+    // the tokens' cosines and sines, while the first round's pieces are on their way
+    for (int u = threadIdx.x; u < ntok * half; u += ROPE_THREADS) {
+        const int tt = u / half, i = u - tt * half;
+        float c = 1.f, s = 0.f;
+        if (inv_freq) {
+            float theta = (float)positions[t0 + tt] * inv_freq[i];
+            c = cosf(theta);
+            s = sinf(theta);
+        }
+        sc[u] = c;
+        ss[u] = s;
+    }
+    __syncthreads();
+    finish_round(0);
+    for (int base = ROPE_THREADS * ROPE_MAX_UNITS; base < total; base += ROPE_THREADS * ROPE_MAX_UNITS) {
+        load_round(base);
+        finish_round(base);
     }
 }
 

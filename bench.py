@@ -154,6 +154,9 @@ def make_config(sz, layers):
                        bos_token_id=128000, eos_token_ids=(128001,))
 
 
+ENGINE_OVERRIDES = {}          # EngineConfig fields set from the command line (experiments)
+
+
 def make_engine(sz, layers, max_seqs, tokens_per_request, context, graphs=True):
     """(config, LLM) with random weights made on the device and a pool for `max_seqs` requests of
     `tokens_per_request` tokens."""
@@ -165,7 +168,7 @@ def make_engine(sz, layers, max_seqs, tokens_per_request, context, graphs=True):
     cfg = make_config(sz, layers)
     pages_per_req = -(-(tokens_per_request + 16) // 16)
     engine = EngineConfig(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
-                          num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=graphs)
+                          num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=graphs, **ENGINE_OVERRIDES)
     tensors = random_tensors(models.llama_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
     runner = ModelRunner(cfg, tensors, engine)
     del tensors
@@ -433,6 +436,7 @@ def kernel_case(argv):
                     help="attn_decode: how the blocks of a request merge (auto: the engine's choice)")
     ap.add_argument("--impl-attn", default="sm100", choices=["sm100", "mma"], help="attn_prefill: the tcgen05 or the mma.sync kernel")
     ap.add_argument("--epilogue", default="store", choices=["store", "swiglu", "resid"], help="gemm_fused: the epilogue")
+    ap.add_argument("--splits", type=int, default=None, help="attn_decode: blocks per request and kv head (default: the engine's choice)")
     a = ap.parse_args(argv)
     dev = "cuda:0"
     bf = torch.bfloat16
@@ -488,6 +492,8 @@ def kernel_case(argv):
             sms = torch.cuda.get_device_properties(dev).multi_processor_count
             wide = 3 * sms // (S * KV) >= 4 and (ctx > LONG_CONTEXT_KEYS if a.merge == "auto" else a.merge == "global")
             splits = max(1, min(64, 3 * sms // (S * KV))) if wide else max(1, min(8, -(-2 * sms // (S * KV))))
+            if a.splits:
+                splits = a.splits
             partials = torch.empty(kernels.attn_decode_partial_floats(S, KV, hd, splits), device=dev) if wide else None
             arrived = torch.zeros(S * KV, dtype=torch.int32, device=dev) if wide else None
             launches = [lambda kc=kc, vc=vc: kernels.attn_decode_mma(q, out, kc, vc, bt, pos, H, KV, hd, scale, 0, splits,
@@ -637,7 +643,12 @@ def main():
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
                     help="an experiment: steps of up to R rows (at most 64) take the fused few-row kernels instead of the "
                          "engine's own switch-over point")
+    ap.add_argument("--engine", action="append", default=[], metavar="FIELD=VALUE",
+                    help="an experiment: set an EngineConfig field (booleans as 0 / 1), e.g. --engine pick_in_head=0")
     a = ap.parse_args()
+    for kv in a.engine:
+        k, _, v = kv.partition("=")
+        ENGINE_OVERRIDES[k] = bool(int(v)) if v in ("0", "1") else int(v)
     if a.impl == "reference":
         return reference_arm()
     if a.gpus != 1:

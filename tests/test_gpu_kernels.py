@@ -762,3 +762,47 @@ def test_a_wait_that_runs_out_raises_the_error_word_and_harms_nothing():
     kernels.gemm_sm100_check()
     assert rel(out2.cpu(), want) <= 1e-5
     assert rel(big.cpu(), a.double().cpu() @ w2.double().cpu().t()) <= 1e-5
+
+
+@pytest.mark.parametrize("T,V,Kd", [(1, 128, 64), (8, 128256, 256), (5, 1000, 96), (16, 301, 128), (33, 5000, 64), (64, 2048, 320)])
+def test_output_head_that_picks_in_its_epilogue(T, V, Kd):
+    """EPI_PICK + pick_final against the logits (EPI_STORE) + pick_tokens: the same tokens for greedy
+    and sampled rows, ties kept at the first index, a NaN row flagged, with the folded norm's scale."""
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(V + T)
+    x, wn, xn, ssq = _folded_input(T, Kd, g)
+    w = (torch.randn(V, Kd, generator=g) * 0.2).to(torch.bfloat16)
+    if V > 40:
+        w[37] = w[11]                                      # a tie between two logits of every row: the first index wins
+        w[V - 1] = w[11]
+    w, xn, ssq = w.to(DEV), xn.to(DEV), ssq.to(DEV)
+    if T > 2:
+        xn[2] = float("nan")                               # row 2 holds NaN logits
+    temps = torch.tensor([0.0 if i % 3 else 0.8 for i in range(T)], device=DEV)
+    temps[0] = 0.0
+    seeds = torch.tensor([[i + 1, 7 * i] for i in range(T)], dtype=torch.int32, device=DEV)
+    steps = torch.arange(T, dtype=torch.int32, device=DEV) + 3
+    logits = torch.empty(T, V, dtype=torch.float32, device=DEV)
+    kernels.gemm_fused(xn, w, logits, kernels.EPI_STORE, V, ssq_in=ssq, eps=1e-5)
+    sp = kernels.pick_splits(V)
+    want = torch.zeros(T, dtype=torch.int32, device=DEV)
+    kernels.pick_tokens(logits, want, torch.zeros(T, dtype=torch.int32, device=DEV), torch.empty(T * sp, device=DEV),
+                        torch.empty(T * sp, dtype=torch.int32, device=DEV), temps, seeds, steps)
+    tiles = kernels.pick_tiles(V)
+    pv = torch.full((T, tiles + 3), float("nan"), device=DEV)
+    pi = torch.full((T, tiles + 3), -5, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(T, dtype=torch.int32, device=DEV)
+    got = torch.full((T,), -9, dtype=torch.int32, device=DEV)
+    kernels.gemm_fused(xn, w, None, kernels.EPI_PICK, V, ssq_in=ssq, eps=1e-5, pick=(temps, seeds, steps, pv, pi, flags))
+    kernels.pick_final(pv[:, :tiles].contiguous(), pi[:, :tiles].contiguous(), T, V, flags, got)
+    assert got.tolist() == want.tolist()
+    if T > 2:
+        assert got[2].item() == -1 and int(flags.sum()) == 0          # flagged, and the flag was put back
+    if V > 40:
+        assert got[0].item() != 37 and got[0].item() != V - 1         # never the later twin of a tie
+    # greedy without sampling parameters at all
+    got2 = torch.full((T,), -9, dtype=torch.int32, device=DEV)
+    kernels.gemm_fused(xn, w, None, kernels.EPI_PICK, V, ssq_in=ssq, eps=1e-5, pick=(None, None, None, pv, pi, flags))
+    kernels.pick_final(pv[:, :tiles].contiguous(), pi[:, :tiles].contiguous(), T, V, flags, got2)
+    ref = torch.where(torch.isnan(logits).any(1), torch.full_like(want, -1), logits.argmax(1).to(torch.int32))
+    assert got2.tolist() == ref.tolist()

@@ -49,6 +49,7 @@ class EngineConfig:
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
     pdl: bool = True                   # programmatic dependent launch between the engine's kernels
     fold_norms: bool = True            # steps of few rows: norms and residual adds folded into the products
+    pick_in_head: bool = True          # decode steps of few rows: the output head's epilogue does the pick's first pass
     step_graphs: int = 2               # other steps: record a CUDA graph when a step of the same shape class comes the
                                        # n-th time and replay it from then on (0: never; needs cuda_graphs)
     run_ahead: bool = True             # steady decode: launch step n + 1 before reading step n's tokens (needs cuda_graphs)

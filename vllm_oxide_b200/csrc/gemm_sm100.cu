@@ -63,7 +63,13 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 //               per 128-feature tile and token, the sum of the residual's squares. The next product
 //               multiplies its accumulator by 1 / sqrt(mean(residual^2) + eps), a per-token scalar
 //               that commutes with the product, so the RMSNorm (:182-197) needs no kernel of its own.
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_RESID = 3 };
+//   EPI_PICK    the product is the output head and only the picked token is wanted: the block reduces
+//               its 128 logits of every token to the best (value, index) pair, by the rule of
+//               sampling.cu (greedy: first index of the maximum, crates/engine/src/backend/cpu/mod.rs:370-388;
+//               temperature: logit / temperature + Gumbel noise from the row's seed), and writes one pair
+//               per (token, tile); a row that holds a NaN is flagged. The logits never go to memory: the
+//               pick's first pass over them, and its launch, are gone. No split of K.
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_RESID = 3, EPI_PICK = 4 };
 
 // Everything an epilogue may need beyond C; a plain struct that the host fills (same layout in
 // kernels.py). Unused members are null / 0.
@@ -86,8 +92,21 @@ struct EpiArgs {
     int ssq_tiles, ld_ssq;
     float inv_h, eps;
     int pad_;
+    // EPI_PICK
+    const float* temperature;          // [T] or null (greedy)
+    const uint32_t* seeds;             // [T][2]
+    const int* steps;                  // [T] index of the generated token
+    float* part_val;                   // [T][ld_part] best value of each tile
+    int* part_idx;                     // [T][ld_part] its vocabulary index
+    int* nan_flags;                    // [T] raised for a row that holds a NaN
+    long long ld_part;
 };
 typedef EpiArgs QkvArgs;
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {          // the hash of sampling.cu
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    return x;
+}
 
 template <int BT, int EPI> __host__ __device__ constexpr int stage_bytes() { return BM * BK * 2 + BT * BK * 2; }
 template <int BT> __host__ __device__ constexpr int stage_bytes() { return stage_bytes<BT, EPI_STORE>(); }
@@ -128,6 +147,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(done_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     float* sc = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 2);       // BT floats: per-token scales
+    float* s_tau = sc + 64;                                                        // EPI_PICK: per-token temperature,
+    uint32_t* s_ctr = reinterpret_cast<uint32_t*>(s_tau + 64);                     // and the token's noise counter
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x, n_tile = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -267,6 +288,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             if (ln == 0) sc[tk] = (qa.ssq_in && t0 + tk < T) ? 1.0f / sqrtf(part * qa.inv_h + qa.eps) : 1.f;
+            if (EPI == EPI_PICK && ln == 0) {
+                const int t = t0 + tk;
+                float tau = 0.f;
+                uint32_t ctr = 0;
+                if (t < T && qa.temperature) tau = qa.temperature[t];
+                if (tau > 0.f) {
+                    const uint32_t key = mix32(qa.seeds[2 * t] ^ mix32(qa.seeds[2 * t + 1] + 0x85EBCA6Bu));
+                    ctr = mix32(key ^ mix32((uint32_t)qa.steps[t] + 0x9E3779B9u));
+                }
+                s_tau[tk] = tau;
+                s_ctr[tk] = ctr;
+            }
         }
         float next_w = 0.f;
         if (EPI == EPI_RESID) next_w = f < N ? qa.next_w[f] : 0.f;      // the next norm's weight of this feature
@@ -292,6 +325,68 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, r[j] * sc[c + j]);
                 }
             }
+        } else if (ok && EPI == EPI_PICK) {
+            // every warp reduces its 32 logits of a token to the best pair; the four pairs of a token
+            // meet in shared memory (over the operand stages, which are free now)
+            float* wv = reinterpret_cast<float*>(tiles);                    // [4][BT]
+            int* wi = reinterpret_cast<int*>(wv + 4 * BT);                  // [4][BT]
+            int* wn = wi + 4 * BT;                                          // [4][BT] a NaN was seen
+#pragma unroll
+            for (int c = 0; c < BT; c += 16) {
+                if (t0 + c >= T) break;                                     // the same in all threads
+                float r[16];
+                load_acc<BT>(taddr + c, r);
+                // sixteen tokens side by side: their five exchange steps are independent chains
+                float bv[16];
+                int bi[16];
+                unsigned nan_bits = 0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float x = r[j] * sc[c + j];
+                    const float tau = s_tau[c + j];
+                    float v = x;
+                    if (tau > 0.f) {
+                        const uint32_t h = mix32(s_ctr[c + j] ^ (uint32_t)f);
+                        const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+                        v = x / tau + (-logf(-logf(u)));
+                    }
+                    const bool take = f < N && v > -INFINITY;               // NaN and -inf never win, as in a scan by "greater than"
+                    bv[j] = take ? v : -INFINITY;
+                    bi[j] = take ? f : 0x7fffffff;
+                    if (f < N && x != x) nan_bits |= 1u << j;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, bv[j], o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, bi[j], o);
+                        if (ov > bv[j] || (ov == bv[j] && oi < bi[j])) { bv[j] = ov; bi[j] = oi; }      // larger value; equal: smaller index
+                    }
+                    nan_bits |= __shfl_xor_sync(0xffffffffu, nan_bits, o);
+                }
+                if (lane < 16) {                                            // lane j writes token c + j (every lane holds every result)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (lane == j) { wv[quad * BT + c + j] = bv[j]; wi[quad * BT + c + j] = bi[j]; wn[quad * BT + c + j] = (nan_bits >> j) & 1; }
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (col < BT && t0 + col < T) {
+                float bv = wv[col];
+                int bi = wi[col], nn = wn[col];
+#pragma unroll
+                for (int w = 1; w < 4; ++w) {
+                    const float ov = wv[w * BT + col];
+                    const int oi = wi[w * BT + col];
+                    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                    nn |= wn[w * BT + col];
+                }
+                qa.part_val[(size_t)(t0 + col) * qa.ld_part + m_tile] = bv;
+                qa.part_idx[(size_t)(t0 + col) * qa.ld_part + m_tile] = bi;
+                if (nn) atomicExch(qa.nan_flags + t0 + col, 1);
+            }
         } else if (ok) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
@@ -310,7 +405,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         // the same answer in all 128 threads (a wait that gave up has raised the block's flag)
-        const bool go = !*abort_flag && !(splits == 1 && EPI == EPI_STORE);
+        const bool go = !*abort_flag && !(splits == 1 && EPI == EPI_STORE) && EPI != EPI_PICK;
         if (go) {
             // Step one, all tokens at once (independent loads): under a split, add the peers'
             // partials up through distributed shared memory in rank order; a residual epilogue adds
@@ -789,6 +884,7 @@ VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, lo
     if (e) return e;
     if (!ea || n_features <= 0) return VOB_ERR_BAD_ARG;
     if (ea->ssq_in && (ea->ssq_tiles <= 0 || ea->ld_ssq < T)) return VOB_ERR_BAD_ARG;
+    if (mode == EPI_PICK) { splits = 1; kb_per = (K + BK - 1) / BK; }     // a tile's best pair is found by one block
     const int N = n_features;
     const long long w_rows = mode == EPI_SWIGLU ? 2LL * N : N;
     int bt = pick_bt(T);
@@ -822,6 +918,13 @@ VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, lo
             if (bt == 16) GOX(16, __nv_bfloat16, EPI_RESID);
             if (bt == 32) GOX(32, __nv_bfloat16, EPI_RESID);
             GOX(64, __nv_bfloat16, EPI_RESID);
+        case EPI_PICK:
+            if (!ea->part_val || !ea->part_idx || !ea->nan_flags || ea->ld_part < (N + BM - 1) / BM || splits != 1 ||
+                (ea->temperature && (!ea->seeds || !ea->steps)))
+                return VOB_ERR_BAD_ARG;
+            if (bt == 16) GOX(16, float, EPI_PICK);
+            if (bt == 32) GOX(32, float, EPI_PICK);
+            GOX(64, float, EPI_PICK);
         default:
             return VOB_ERR_BAD_ARG;
     }

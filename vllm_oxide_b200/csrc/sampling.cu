@@ -134,6 +134,17 @@ VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, 
                       nan_flags, out);
 }
 
+// The second launch alone: the pairs come from elsewhere (the output head's own epilogue reduces
+// each of its tiles to a pair: EPI_PICK in gemm_sm100.cu), `splits` of them per row.
+VOB_EXPORT int vob_pick_final(const float* part_val, const int* part_idx, int R, int splits, int V, int* nan_flags, int* out,
+                              cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || splits <= 0 || R > 65535) return VOB_ERR_BAD_ARG;
+    // one pair per thread where that is possible: a thread that walks many pairs pays a memory round trip for each
+    const int threads = splits > 512 ? 1024 : splits > 256 ? 512 : splits > 64 ? 256 : 64;
+    return vob_launch(pick_final_kernel, dim3(R), dim3(threads), 0, stream, part_val, part_idx, splits, V, nan_flags, out);
+}
+
 // ---------------------------------------------------------------------------------------------
 // The same pick for callers that cannot allocate: scratch in a fixed device array of this
 // library (see no_alloc.h for who needs this and the rules that come with it).

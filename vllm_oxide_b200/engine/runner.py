@@ -119,9 +119,11 @@ class ModelRunner:
         V = self.spec.vocab_size
         self.workspace_bytes = self.workspace_formula(self.rows_cap)
         self.workspace = Workspace(self.workspace_bytes, self.device)
-        splits = kernels.pick_splits(V)
-        self.pick_val = torch.empty(self.logit_chunk * splits, dtype=torch.float32, device=self.device)
-        self.pick_idx = torch.empty(self.logit_chunk * splits, dtype=torch.int32, device=self.device)
+        # scratch of the token pick: a (value, index) pair per row and slice of the vocabulary, or per
+        # row and 128-logit tile when the head's own epilogue does the first pass
+        pairs = max(kernels.pick_splits(V), kernels.pick_tiles(V))
+        self.pick_val = torch.empty(self.logit_chunk * pairs, dtype=torch.float32, device=self.device)
+        self.pick_idx = torch.empty(self.logit_chunk * pairs, dtype=torch.int32, device=self.device)
         self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         # two pinned buffers: a step's picks may still be unread when the next step writes its own
@@ -283,6 +285,18 @@ class ModelRunner:
         spec, L = self.spec, layout or self.layout
         d = self.step_dev
         V = spec.vocab_size
+        if (self.engine.pick_in_head and logits_out is None and self._folded is not None and ctx.decode_only
+                and num_logit_rows == ctx.rows <= self.logit_chunk
+                and getattr(spec.lm_head, "can_fold", lambda: False)() and hasattr(spec.lm_head, "pick_folded")):
+            # every row is wanted, in order, and only its token: the head reads the folded residual and
+            # picks in its own epilogue; the logits never exist in memory
+            n = num_logit_rows
+            tiles = kernels.pick_tiles(V)
+            spec.lm_head.pick_folded(self._folded, spec.final_norm.eps, n, d[L["temperature"]:L["temperature"] + n].view(torch.float32),
+                                     d[L["seeds"]:L["seeds"] + 2 * n], d[L["sample_steps"]:L["sample_steps"] + n],
+                                     self.pick_val[:n * tiles].view(n, tiles), self.pick_idx[:n * tiles].view(n, tiles),
+                                     self.nan_flags[:n], self.sampled[:n])
+            return
         for c0 in range(0, num_logit_rows, self.logit_chunk):
             n = min(self.logit_chunk, num_logit_rows - c0)
             with ctx.workspace.scope():

@@ -494,7 +494,7 @@ def gemm_qkv_rope(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
 
 
 # ------------------------------------------------------------------------------------ folded norms (few rows)
-EPI_STORE, EPI_SWIGLU, EPI_QKV, EPI_RESID = 0, 1, 2, 3
+EPI_STORE, EPI_SWIGLU, EPI_QKV, EPI_RESID, EPI_PICK = 0, 1, 2, 3, 4
 
 
 class _EpiArgs(ctypes.Structure):
@@ -503,7 +503,9 @@ class _EpiArgs(ctypes.Structure):
                 ("ssq_in", _P), ("resid", _P), ("next_w", _P), ("xn_out", _P), ("ssq_out", _P),
                 ("ld_resid", _L), ("ld_xn", _L),
                 ("q_dim", _I), ("kv_dim", _I), ("hd", _I), ("KV", _I), ("page_size", _I),
-                ("ssq_tiles", _I), ("ld_ssq", _I), ("inv_h", _F), ("eps", _F), ("pad_", _I)]
+                ("ssq_tiles", _I), ("ld_ssq", _I), ("inv_h", _F), ("eps", _F), ("pad_", _I),
+                ("temperature", _P), ("seeds", _P), ("steps", _P), ("part_val", _P), ("part_idx", _P), ("nan_flags", _P),
+                ("ld_part", _L)]
 
 
 def _dp(t: Optional[torch.Tensor]) -> int:
@@ -535,7 +537,7 @@ def embed_fold(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n
 
 @_timed
 def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mode: int, n_features: int, *,
-               ssq_in: Optional[torch.Tensor] = None, eps: float = 0.0, qkv=None, resid=None,
+               ssq_in: Optional[torch.Tensor] = None, eps: float = 0.0, qkv=None, resid=None, pick=None,
                splits: Optional[int] = None) -> None:
     """The tcgen05 product for at most 64 rows with a fused epilogue and, optionally, the RMSNorm of
     its input folded in: `a` holds bf16(x * norm weight), `ssq_in` [tiles, ld] the per-tile sums of
@@ -545,7 +547,11 @@ def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mo
       EPI_QKV    qkv = (positions, slots, inv_freq, kcache, vcache, H, KV, hd): out[T, H*hd] = rotated q,
                  rotated k and v go to their cache slots
       EPI_RESID  resid = (resid float32 [T, n] updated in place, next_w float32 [n], xn_out bfloat16 [T, n],
-                 ssq_out float32 [tiles(n), ld]); out is None"""
+                 ssq_out float32 [tiles(n), ld]); out is None
+      EPI_PICK   the output head when only the picked tokens are wanted: pick = (temperature float32 [T] or None,
+                 seeds int32 [T, 2], steps int32 [T], part_val float32 [T, ld], part_idx int32 [T, ld],
+                 nan_flags int32 [T]), ld >= pick_tiles(n): every block leaves the best (value, index) pair of
+                 its 128 logits per token (the rule of `pick_tokens`); `pick_final` finishes; out is None"""
     op = "gemm_fused"
     _cuda(op, a, w, out, ssq_in)
     if not gemm_sm100_supported(a, w):
@@ -604,6 +610,26 @@ def gemm_fused(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], mo
             ea.ld_ssq = ssq_out.shape[1]
         elif ea.ld_ssq != ssq_out.shape[1]:
             raise ShapeError(op, "ssq_in and ssq_out must have the same row length")
+    elif mode == EPI_PICK:
+        temperature, seeds, steps, part_val, part_idx, nan_flags = pick
+        _cuda(op, temperature, seeds, steps, part_val, part_idx, nan_flags)
+        tiles = pick_tiles(n_features)
+        for name, t_, dt in (("part_val", part_val, torch.float32), ("part_idx", part_idx, torch.int32)):
+            if t_.dtype != dt or t_.dim() != 2 or t_.shape[0] < T or t_.shape[1] < tiles or not t_.is_contiguous():
+                raise ShapeError(op, f"{name} must be contiguous {dt} [>={T}, >={tiles}], got {t_.dtype} {list(t_.shape)}")
+        if part_val.shape[1] != part_idx.shape[1]:
+            raise ShapeError(op, "part_val and part_idx must have the same row length")
+        _int32_vec(nan_flags, T, op, "nan_flags")
+        if temperature is not None:
+            if temperature.dtype != torch.float32 or temperature.numel() < T or not temperature.is_contiguous():
+                raise ShapeError(op, f"temperature must be float32 [{T}]")
+            if seeds is None or steps is None or seeds.dtype != torch.int32 or seeds.numel() < 2 * T or not seeds.is_contiguous():
+                raise ShapeError(op, f"temperature sampling needs seeds int32 [{T}, 2] and steps")
+            _int32_vec(steps, T, op, "steps")
+        ea.temperature, ea.seeds, ea.steps = _dp(temperature), _dp(seeds), _dp(steps)
+        ea.part_val, ea.part_idx, ea.nan_flags, ea.ld_part = _dp(part_val), _dp(part_idx), _dp(nan_flags), part_val.shape[1]
+        out_code = 0
+        splits = 1
     else:
         raise ShapeError(op, f"unknown epilogue mode {mode}")
     if splits is None:
@@ -853,6 +879,28 @@ def attn_decode_partial_floats(num_seqs: int, num_kv_heads: int, head_dim: int, 
 
 
 # ------------------------------------------------------------------------------------ sampling
+def pick_tiles(vocab: int) -> int:
+    """Pairs per row that the output head's picking epilogue (EPI_PICK) leaves: one per 128 logits."""
+    return -(-int(vocab) // 128)
+
+
+@_timed
+def pick_final(part_val: torch.Tensor, part_idx: torch.Tensor, rows: int, vocab: int, nan_flags: torch.Tensor,
+               out: torch.Tensor) -> None:
+    """The pick's second pass alone: out[r] = index of the best of row r's (value, index) pairs
+    (part_val / part_idx [>= rows, pairs per row]); -1 for a row whose NaN flag is up (the flag is cleared)."""
+    op = "pick_final"
+    _cuda(op, part_val, part_idx, nan_flags, out)
+    if (part_val.dtype != torch.float32 or part_idx.dtype != torch.int32 or part_val.dim() != 2 or part_val.shape != part_idx.shape
+            or part_val.shape[0] < rows or not part_val.is_contiguous() or not part_idx.is_contiguous()):
+        raise ShapeError(op, f"part_val float32 and part_idx int32 must be contiguous [>={rows}, pairs], got {list(part_val.shape)} "
+                             f"and {list(part_idx.shape)}")
+    _int32_vec(out, rows, op, "out")
+    _int32_vec(nan_flags, rows, op, "nan_flags")
+    f = _fn("sampling", "vob_pick_final", [_P, _P, _I, _I, _I, _P, _P, _P])
+    _check(f(_ptr(part_val), _ptr(part_idx), rows, part_val.shape[1], int(vocab), _ptr(nan_flags), _ptr(out), _stream()), op)
+
+
 def pick_splits(vocab: int) -> int:
     f = _fn("sampling", "vob_pick_splits", [_I])
     return int(f(vocab))

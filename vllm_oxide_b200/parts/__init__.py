@@ -1,4 +1,4 @@
-from .base import (CacheSpec, StateSpec, LayerCache, Workspace, StepContext, Mixer, FeedForward, Norm,
+from .base import (CacheSpec, PagedTensorSpec, StateSpec, LayerCache, Workspace, StepContext, Mixer, FeedForward, Norm,
                    PositionEncoding, LayerCall, ModelSpec, FoldedState, FOLD_ROWS)
 from .rmsnorm import RMSNorm
 from .rotary import Rotary, rotary_inv_freq
@@ -7,6 +7,6 @@ from .swiglu import SwiGLU
 from .embedding import Embedding, LMHead
 from .block import Block
 
-__all__ = ["CacheSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
+__all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
            "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "FOLD_ROWS", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
            "SwiGLU", "Embedding", "LMHead", "Block"]

@@ -23,6 +23,20 @@
 // order (a fixed order: the result does not depend on timing) and writes C. Nothing goes through
 // global memory and nothing needs resetting between launches.
 //
+// Tiles of 16 tokens (decode steps of up to 16 requests) do the products another way. Measured on
+// this GPU: a tcgen05.mma costs the tensor pipe some 160 clocks however few tokens it has (its A
+// operand, 128 weight rows x 32 bytes, is fetched from shared memory at about 32 bytes a clock), so a
+// stage of 64 k took 0.33 us of products whatever the token count, and the product phase of a block
+// whose weights had all been prefetched was as long as its whole epilogue. For these tiles the four
+// epilogue warps therefore do the products themselves: 32 weight rows each, fragments by ldmatrix
+// straight from the TMA ring's swizzled tiles, mma.sync.m16n8k16 with float32 accumulators in
+// registers (one 8-token half only when the step has at most 8 tokens); no tensor memory, no issuing
+// threads, and the per-token scale's round trip to L2 hides behind the product loop. The rest of
+// the kernel (TMA ring, cluster split of K, epilogues) is the same. A decode step at batch 1 / 8 / 16
+// went from 0.750 / 0.858 / 1.002 to 0.733 / 0.848 / 0.966 ms. (Two or four accumulator sets to
+// shorten the chain of dependent products cost registers, a second block no longer fitted the SM,
+// and the step took 0.88 / 1.04 ms: dropped.)
+//
 // Every wait on an mbarrier is bounded (two seconds): on expiry the block raises the error flag,
 // stops issuing work, frees its tensor memory and returns; the host turns the flag into an
 // exception. No TMA load uses cluster multicast.
@@ -42,6 +56,22 @@ constexpr int ISSUERS = 2;          // MMA-issuing threads of the kernel for few
 constexpr int NTHREADS_FEW = 192 + 32 * (ISSUERS - 1);
 // kind::f16 instruction descriptor of this file's products: M = 128 weight rows, N = n tokens, both K-major.
 __host__ __device__ constexpr uint32_t umma_idesc(int n) { return umma_idesc_bf16(BM, n, false); }
+
+// For tiles of 16 tokens the products are done by mma.sync from the TMA ring (see the kernel's header
+// comment below): 8 x 8 matrices of 16-bit elements from shared memory, four at a time, and the
+// 16 x 8 x 16 product with float32 accumulators in registers.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+#ifdef VOB_FEW16_TCGEN05
+constexpr bool FEW16_MMA_SYNC = false;
+#else
+constexpr bool FEW16_MMA_SYNC = true;
+#endif
 
 template <typename OutT> __device__ __forceinline__ void store_out(OutT* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
@@ -135,6 +165,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                   const QkvArgs qa, int test_extra_tx) {
     constexpr int SB = stage_bytes<BT, EPI>();
     constexpr int A_BYTES = BM * BK * 2;
+    // Tiles of 16 tokens: the four epilogue warps do the products themselves with mma.sync, reading the
+    // ring's tiles with ldmatrix; no tensor memory, no issuing threads (see the note above the kernel).
+    constexpr bool MS = BT == 16 && FEW16_MMA_SYNC;
     constexpr int PRE = BT >= 64 ? 12 : (BT >= 32 ? 8 : 4);   // tokens per block whose rotation is worked out ahead
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
@@ -158,20 +191,20 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int nkb = kb1 - kb0;                    // >= 1 by the launcher's choice of splits
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, ISSUERS); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, MS ? 4 : ISSUERS); }
         mbar_init(acc_bar, ISSUERS);                     // both issuing threads commit to these
         mbar_init(done_bar, splits);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (!MS && warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(tmem_cols<BT, EPI>()) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = *tmem_holder;
+    const uint32_t tmem_base = MS ? 0u : *tmem_holder;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -207,7 +240,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n_tile * BT, full_bar + s);
             }
         }
-    } else if (warp == 1 || warp >= 6) {
+    } else if (!MS && (warp == 1 || warp >= 6)) {
         // ISSUERS issuing threads. One thread gets a tcgen05.mma through about every 125 clocks
         // whatever its size, and an instruction of 128 x 16 x 16 consumes only 4 KB of weights: a
         // single issuer just about keeps pace with HBM, and its chain is what a block with few
@@ -239,7 +272,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
             if (ok) umma_commit(acc_bar);         // the accumulator is complete
         }
-    } else if (warp < 6) {
+    } else if (warp >= 2 && warp < 6) {
         // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) ... + 31
         const int quad = warp & 3;
         const int col = quad * 32 + lane;
@@ -276,73 +309,148 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         pdl_wait();
         // per-token scale of the accumulator (the folded RMSNorm of this product's input): it comes
         // from kernels in front, so it is fetched after the wait, while the product itself runs
-        {
-            // 128 threads = BT tokens x (128 / BT) lanes: lane l adds the tiles l, l + L, ... of its
-            // token, then the lanes' sums are added pairwise in a fixed tree (one L2 round trip
-            // instead of one per tile)
-            constexpr int L = 128 / BT;
-            const int tk = col / L, ln = col % L;
-            float part = 0.f;
-            if (qa.ssq_in && t0 + tk < T)
-                for (int i = ln; i < qa.ssq_tiles; i += L) part += qa.ssq_in[(size_t)i * qa.ld_ssq + t0 + tk];
+        // 128 threads = BT tokens x (128 / BT) lanes: lane l adds the tiles l, l + L, ... of its token,
+        // then the lanes' sums are added pairwise in a fixed tree (one L2 round trip instead of one per
+        // tile). The values are requested here; where this warp does the products itself they are
+        // only added up behind the product loop, so that the round trip is hidden by it.
+        constexpr int L = 128 / BT;
+        const int tk = col / L, ln = col % L;
+        float ssq_v[4] = {0.f, 0.f, 0.f, 0.f};
+        float ssq_rest = 0.f;
+        if (qa.ssq_in && t0 + tk < T) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (ln + u * L < qa.ssq_tiles) ssq_v[u] = qa.ssq_in[(size_t)(ln + u * L) * qa.ld_ssq + t0 + tk];
+            for (int i = ln + 4 * L; i < qa.ssq_tiles; i += L) ssq_rest += qa.ssq_in[(size_t)i * qa.ld_ssq + t0 + tk];
+        }
+        float tau = 0.f;
+        uint32_t ctr = 0;
+        if (EPI == EPI_PICK && ln == 0) {
+            const int t = t0 + tk;
+            if (t < T && qa.temperature) tau = qa.temperature[t];
+            if (tau > 0.f) {
+                const uint32_t key = mix32(qa.seeds[2 * t] ^ mix32(qa.seeds[2 * t + 1] + 0x85EBCA6Bu));
+                ctr = mix32(key ^ mix32((uint32_t)qa.steps[t] + 0x9E3779B9u));
+            }
+        }
+        auto finish_scales = [&]() {
+            float part = (((ssq_v[0] + ssq_v[1]) + ssq_v[2]) + ssq_v[3]) + ssq_rest;      // the order a walk over the tiles adds them in
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             if (ln == 0) sc[tk] = (qa.ssq_in && t0 + tk < T) ? 1.0f / sqrtf(part * qa.inv_h + qa.eps) : 1.f;
-            if (EPI == EPI_PICK && ln == 0) {
-                const int t = t0 + tk;
-                float tau = 0.f;
-                uint32_t ctr = 0;
-                if (t < T && qa.temperature) tau = qa.temperature[t];
-                if (tau > 0.f) {
-                    const uint32_t key = mix32(qa.seeds[2 * t] ^ mix32(qa.seeds[2 * t + 1] + 0x85EBCA6Bu));
-                    ctr = mix32(key ^ mix32((uint32_t)qa.steps[t] + 0x9E3779B9u));
-                }
-                s_tau[tk] = tau;
-                s_ctr[tk] = ctr;
-            }
-        }
+            if (EPI == EPI_PICK && ln == 0) { s_tau[tk] = tau; s_ctr[tk] = ctr; }
+        };
+        if (!MS) finish_scales();
         float next_w = 0.f;
         if (EPI == EPI_RESID) next_w = f < N ? qa.next_w[f] : 0.f;      // the next norm's weight of this feature
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const bool ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        // Shared memory over the operand stages (every MMA that read them has completed once acc_bar
-        // has flipped): `tile` [BT][128] is this block's tile (a partial one under a split, which
+        // Shared memory over the operand stages (every product that read them has completed by the time
+        // it is written): `tile` [BT][128] is this block's tile (a partial one under a split, which
         // peers read); `fin` [nk][128] the finished values of the tokens this block completes, in
         // which partners of a fused epilogue find each other; `red` [nk][4] sums of squares by warp.
         float* tile = reinterpret_cast<float*>(tiles);
         float* fin = splits > 1 ? tile + BT * BM : tile;
         float* red = fin + (splits > 1 ? (BT / 2) * BM : BT * BM);
+        bool ok = true;
+        if (MS) {
+            // This warp's 32 weight rows of the tile against the 16 tokens, stage by stage: A fragments
+            // (weights) and B fragments (tokens) by ldmatrix from the 128-byte-swizzled tiles (row r,
+            // 16-byte piece c lies at piece c ^ (r & 7)), 16 mma.sync per stage and warp.
+            float acc[2][2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.f;
+            const int mtx = lane >> 3, r8 = lane & 7;
+            const int a_row = quad * 32 + r8 + ((mtx & 1) << 3), a_k = mtx >> 1;     // + 16 for the second 16 rows
+            const int x_row = r8 + ((mtx >> 1) << 3), x_k = mtx & 1;
+            const bool more_than_8 = T - t0 > 8;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, err_flag, 2)) { ok = false; break; }
+                const uint32_t a_base = smem_u32(tiles + s * SB), x_base = a_base + A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                    uint32_t b[4], a0[4], a1[4];
+                    ldmatrix_x4(b, x_base + x_row * 128 + (((ks * 2 + x_k) ^ (x_row & 7)) << 4));
+                    ldmatrix_x4(a0, a_base + a_row * 128 + (((ks * 2 + a_k) ^ (a_row & 7)) << 4));
+                    ldmatrix_x4(a1, a_base + (a_row + 16) * 128 + (((ks * 2 + a_k) ^ (a_row & 7)) << 4));
+                    mma_16816(acc[0][0], a0, b[0], b[1]);
+                    mma_16816(acc[1][0], a1, b[0], b[1]);
+                    if (more_than_8) {                                    // tokens 8..15 (the same in all threads)
+                        mma_16816(acc[0][1], a0, b[2], b[3]);
+                        mma_16816(acc[1][1], a1, b[2], b[3]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar + s);        // this warp has read the stage
+            }
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+            finish_scales();
+            // every warp is through with the stages (and the scales are written) before the tile is written over them
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ok && !*abort_flag) {
+                const int g = lane >> 2, t2 = (lane & 3) * 2;
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < 2; ++ni) {
+                        const int row = quad * 32 + mi * 16 + g, tok = ni * 8 + t2;
+                        tile[tok * BM + row] = acc[mi][ni][0] * sc[tok];
+                        tile[(tok + 1) * BM + row] = acc[mi][ni][1] * sc[tok + 1];
+                        tile[tok * BM + row + 8] = acc[mi][ni][2] * sc[tok];
+                        tile[(tok + 1) * BM + row + 8] = acc[mi][ni][3] * sc[tok + 1];
+                    }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ok = ok && !*abort_flag;
+        } else {
+            ok = mbar_wait(acc_bar, 0, abort_flag, err_flag, 3);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        // 16 tokens of this thread's feature, scaled: from the tile in shared memory, or from tensor memory
+        auto get16 = [&](int c, float* r) {
+            if (MS) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = tile[(c + j) * BM + col];
+            } else {
+                load_acc<BT>(taddr + c, r);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] *= sc[c + j];
+            }
+        };
         if (ok && splits == 1 && EPI == EPI_STORE) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 float r[16];
-                load_acc<BT>(taddr + c, r);
+                get16(c, r);
                 if (f < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, r[j] * sc[c + j]);
+                        if (t0 + c + j < T) store_out<OutT>(C + (size_t)(t0 + c + j) * ldc + f, r[j]);
                 }
             }
         } else if (ok && EPI == EPI_PICK) {
             // every warp reduces its 32 logits of a token to the best pair; the four pairs of a token
             // meet in shared memory (over the operand stages, which are free now)
-            float* wv = reinterpret_cast<float*>(tiles);                    // [4][BT]
+            float* wv = reinterpret_cast<float*>(tiles) + (MS ? BT * BM : 0);   // [4][BT] (behind the tile where that is in use)
             int* wi = reinterpret_cast<int*>(wv + 4 * BT);                  // [4][BT]
             int* wn = wi + 4 * BT;                                          // [4][BT] a NaN was seen
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 if (t0 + c >= T) break;                                     // the same in all threads
                 float r[16];
-                load_acc<BT>(taddr + c, r);
+                get16(c, r);
                 // sixteen tokens side by side: their five exchange steps are independent chains
                 float bv[16];
                 int bi[16];
                 unsigned nan_bits = 0;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float x = r[j] * sc[c + j];
+                    const float x = r[j];
                     const float tau = s_tau[c + j];
                     float v = x;
                     if (tau > 0.f) {
@@ -387,13 +495,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 qa.part_idx[(size_t)(t0 + col) * qa.ld_part + m_tile] = bi;
                 if (nn) atomicExch(qa.nan_flags + t0 + col, 1);
             }
-        } else if (ok) {
+        } else if (ok && !MS) {
 #pragma unroll
             for (int c = 0; c < BT; c += 16) {
                 float r[16];
-                load_acc<BT>(taddr + c, r);
+                get16(c, r);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = r[j] * sc[c + j];
+                for (int j = 0; j < 16; ++j) tile[(c + j) * BM + col] = r[j];
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -534,7 +642,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 1) {
+    if (!MS && warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols<BT, EPI>()) : "memory");
     }

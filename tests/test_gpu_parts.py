@@ -172,6 +172,70 @@ def test_attention_part_in_portions(dt, window, rope, scale):
 
 
 @pytest.mark.parametrize("dt", DT, ids=IDS)
+def test_partial_interleaved_rotation_is_a_table_and_a_row_order(dt):
+    """Another position rule through the unchanged mixer and kernels: only the first `rot` features of
+    a head rotate, in interleaved pairs (2j, 2j + 1), angle position * theta^(-2j / rot). The kernels
+    rotate pairs (i, i + hd / 2) by position * table[i]; so the toy encoding below (defined here, no
+    model of anyone's) offers a table whose entries beyond rot / 2 are zero (angle 0: the pair stays as
+    it is) and an order of the q and k projections' rows, the same for both, that brings the partners of
+    a pair to i and i + hd / 2. Scores are dot products, so the common order changes nothing else. The
+    plain side rotates the interleaved pairs of the unpermuted projections directly."""
+    from vllm_oxide_b200.parts import Attention, LayerCache, PositionEncoding
+    hidden, H, KV, hd, rot, page, theta = 40, 6, 2, 16, 6, 8, 100.0
+    half = hd // 2
+
+    class PartialInterleaved(PositionEncoding):
+        def __init__(self):
+            freq = [theta ** (-2.0 * j / rot) for j in range(rot // 2)] + [0.0] * (half - rot // 2)
+            self.inv_freq = torch.tensor(freq, dtype=torch.float32, device=DEV)
+            order = [0] * hd
+            rest = iter(range(rot, hd))
+            for i in range(half):
+                if i < rot // 2:
+                    order[i], order[i + half] = 2 * i, 2 * i + 1
+                else:
+                    order[i], order[i + half] = next(rest), next(rest)
+            self.order = order
+
+        def reorder(self, w, heads):                    # rows of a q or k projection, head by head
+            return torch.cat([w[h * hd:(h + 1) * hd][self.order] for h in range(heads)])
+
+    g = torch.Generator().manual_seed(12)
+    wq, wk, wv, wo = _attn_weights(g, hidden, H, KV, hd)
+    pos = PartialInterleaved()
+    assert sorted(pos.order) == list(range(hd))
+    part = Attention(pos.reorder(wq, H), pos.reorder(wk, KV), wv, wo, H, KV, hd, position=pos, dtype=dt, device=DEV)
+    h = Harness(dt, page=page, kv=(KV, hd))
+    cache = LayerCache((h.kv[0][0], h.kv[0][1]), 0, True)
+    T = 63
+    x = torch.randn(T, hidden, generator=g).to(dt)
+
+    def rotate(t, heads):                                # [T, heads * hd] float64, interleaved pairs of the first `rot` features
+        t = t.clone().view(T, heads, hd)
+        for j in range(rot // 2):
+            ang = torch.arange(T, dtype=torch.float64) * theta ** (-2.0 * j / rot)
+            c, s_ = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+            a, b = t[:, :, 2 * j].clone(), t[:, :, 2 * j + 1].clone()
+            t[:, :, 2 * j], t[:, :, 2 * j + 1] = a * c - b * s_, a * s_ + b * c
+        return t.view(T, heads * hd)
+
+    xd = x.double()
+    q, k, v = rotate(plain.linear(xd, wq.double()), H), rotate(plain.linear(xd, wk.double()), KV), plain.linear(xd, wv.double())
+    want = plain.linear(plain.causal_attention(q, k, v, H, KV, hd), wo.double())
+    got, p = [], 0
+    for n in [9, 1, 1, 40, 2, 10]:                       # few-row steps (rotation in the projection's epilogue) and a larger one
+        ctx = h.ctx([(1, [0] * n)])
+        got.append(part.forward(x[p:p + n].to(DEV), ctx, cache).clone())
+        h.done()
+        p += n
+    assert p == T
+    assert max_rel_diff(torch.cat(got).cpu(), want) <= (2e-5 if dt == torch.float32 else 3e-2)
+    # the rule is seen: without the rotation the result is another one
+    plain_no = plain.linear(plain.causal_attention(plain.linear(xd, wq.double()), plain.linear(xd, wk.double()), v, H, KV, hd), wo.double())
+    assert max_rel_diff(plain_no, want) > 0.05
+
+
+@pytest.mark.parametrize("dt", DT, ids=IDS)
 def test_block_part_and_bad_sizes(dt):
     from vllm_oxide_b200.parts import Attention, Block, LayerCache, RMSNorm, Rotary, SwiGLU
     hidden, H, KV, hd, inter = 48, 3, 3, 16, 56

@@ -415,7 +415,7 @@ def kernel_case(argv):
     counters mean something; device time per launch is printed from CUDA events."""
     import torch
     from vllm_oxide_b200 import kernels
-    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    from vllm_oxide_b200.tuning import TUNING
     ap = argparse.ArgumentParser(prog="bench.py --kernel")
     ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_pair", "gemm_pair_swiglu", "gemm_library", "gemm_fused",
                                                          "attn_decode", "attn_prefill"])
@@ -490,7 +490,7 @@ def kernel_case(argv):
             # the engine's choice (parts/attention.py decode_splits): a cluster of up to 8 blocks per request
             # and kv head, or, for few requests with long contexts, up to 64 that merge through global memory
             sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            wide = 3 * sms // (S * KV) >= 4 and (ctx > LONG_CONTEXT_KEYS if a.merge == "auto" else a.merge == "global")
+            wide = 3 * sms // (S * KV) >= 4 and (ctx > TUNING.long_context_keys if a.merge == "auto" else a.merge == "global")
             splits = max(1, min(64, 3 * sms // (S * KV))) if wide else max(1, min(8, -(-2 * sms // (S * KV))))
             if a.splits:
                 splits = a.splits
@@ -670,11 +670,8 @@ def main():
 
     import torch
     if a.fold_rows is not None:
-        import vllm_oxide_b200.engine.runner as er
-        import vllm_oxide_b200.parts.base as pb
-        import vllm_oxide_b200.parts.embedding as pe
-        from vllm_oxide_b200 import kernels
-        kernels.FUSED_GEMM_BEST_ROWS = kernels.LIBRARY_GEMM_ABOVE_ROWS = pb.FOLD_ROWS = pe.FOLD_ROWS = er.FOLD_ROWS = a.fold_rows
+        from vllm_oxide_b200.tuning import TUNING
+        TUNING.few_rows = a.fold_rows
     sz = SIZES[a.sizes]
     full_layers = sz["layers"]
     layers = a.layers or full_layers

@@ -248,7 +248,8 @@ def test_running_ahead_changes_no_token_and_sees_stop_tokens(tmp_path_factory, d
 def test_generation_crosses_into_long_contexts(tmp_path_factory):
     """A request grows past the length from which decode steps count as long-context ones: the
     replayed graphs change kind on the way, and the tokens are those of steps launched one by one."""
-    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    from vllm_oxide_b200.tuning import TUNING
+    LONG_CONTEXT_KEYS = TUNING.long_context_keys
     cfg, _, page = TINY["DL"]
     d = make_model_dir(tmp_path_factory.getbasetemp(), "DL")
     prompts = [random_tokens(LONG_CONTEXT_KEYS - 6, cfg.vocab_size, 41), random_tokens(40, cfg.vocab_size, 42)]

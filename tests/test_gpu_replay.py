@@ -264,7 +264,8 @@ def test_long_context_beside_a_short_one(tmp_path_factory):
                                              {"id": "r1", "tokens": [short_toks[130 + i]], "want": [0]}],
                       "end": ["r0", "r1"] if i == 19 else []})
         n += 1
-    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    from vllm_oxide_b200.tuning import TUNING
+    LONG_CONTEXT_KEYS = TUNING.long_context_keys
     assert LONG_CONTEXT_KEYS < 6280
     worst = check(run_trace(s, steps), model_dir, reqs, dtype, "long beside short")
     assert s.runner.manager.num_free_pages(0) == s.runner.manager.num_pages(0)

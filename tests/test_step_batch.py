@@ -93,7 +93,8 @@ def test_shape_class_of_a_step():
     """What a recorded step is replayed for: rows are padded up, the longest portion is an upper
     bound, requests / wanted rows / leading single tokens are exact; decode steps have their own graphs."""
     from vllm_oxide_b200.engine.runner import step_shape_class
-    from vllm_oxide_b200.parts.base import LONG_CONTEXT_KEYS
+    from vllm_oxide_b200.tuning import TUNING
+    LONG_CONTEXT_KEYS = TUNING.long_context_keys
     assert step_shape_class(8, 8, 8, 1, 8, 300, 2048) is None                 # a decode step
     assert step_shape_class(100, 2, 0, 60, 0, 300, 2048) is None              # no logits wanted
     assert step_shape_class(1, 1, 1, 1, 1, 5, 2048) is None

@@ -26,7 +26,8 @@ from ..cache.pools import CachePools
 from ..config import EngineConfig, architecture_for, read_config_json
 from ..csrc.build import runtime_module
 from ..errors import CapacityError, KernelError, ShapeError
-from ..parts.base import FOLD_ROWS, LONG_CONTEXT_KEYS, ModelSpec, StepContext, Workspace, aligned
+from ..tuning import TUNING
+from ..parts.base import ModelSpec, StepContext, Workspace, aligned
 from ..weights import load_safetensors_weights, weights_from_tensors
 
 
@@ -51,7 +52,7 @@ def step_shape_class(rows: int, seqs: int, logit_count: int, max_new: int, lead_
         return None
     padded = min(16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else -(-rows // 128) * 128, rows_cap)
     longest = min(-(-max_new // 64) * 64, padded)
-    return (padded, seqs, logit_count, longest, int(lead_single), bool(max_seq_len > LONG_CONTEXT_KEYS))
+    return (padded, seqs, logit_count, longest, int(lead_single), bool(max_seq_len > TUNING.long_context_keys))
 
 
 def _require_cuda(device: str) -> None:
@@ -116,6 +117,8 @@ class ModelRunner:
         self.step_dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         # workspace: residual + two pending buffers + the largest block + the head's chunk
         self._foldable = None
+        if not 0 <= TUNING.few_rows <= kernels.FUSED_GEMM_MAX_ROWS:
+            raise ValueError(f"TUNING.few_rows must be 0..{kernels.FUSED_GEMM_MAX_ROWS} (what the fused kernels take), got {TUNING.few_rows}")
         V = self.spec.vocab_size
         self.workspace_bytes = self.workspace_formula(self.rows_cap)
         self.workspace = Workspace(self.workspace_bytes, self.device)
@@ -168,8 +171,8 @@ class ModelRunner:
         if self._can_fold(1):
             # steps of few rows run in folded form (FoldedState): residual, the next norm's input, the
             # partial sums of squares, and the blocks' folded scratch or the head
-            r = min(rows, FOLD_ROWS)
-            state = aligned(r * h * 4) + aligned(r * h * 2) + aligned(-(-h // 128) * FOLD_ROWS * 4)
+            r = min(rows, TUNING.few_rows)
+            state = aligned(r * h * 4) + aligned(r * h * 2) + aligned(-(-h // 128) * TUNING.few_rows * 4)
             fblock = max((b.folded_workspace_bytes(r) for b in self.spec.blocks), default=0)
             fhead = aligned(min(self.logit_chunk, r) * V * 4) + self.spec.final_norm.workspace_bytes(min(self.logit_chunk, r), es)
             total = max(total, state + max(fblock, fhead))
@@ -216,7 +219,7 @@ class ModelRunner:
             max_new=arrays.max_new if arrays is not None else 0,
             max_seq_len=arrays.max_seq_len if arrays is not None else 0, host=arrays,
             decode_only=bool(arrays is not None and arrays.max_new == 1 and arrays.rows == arrays.seqs),
-            long_context=bool(arrays is not None and arrays.max_seq_len > LONG_CONTEXT_KEYS),
+            long_context=bool(arrays is not None and arrays.max_seq_len > TUNING.long_context_keys),
             lead_single=int(arrays.lead_single) if arrays is not None else 0)
 
     def upload(self, arrays) -> None:
@@ -248,7 +251,7 @@ class ModelRunner:
                 and hasattr(spec.embedding, "forward_folded") and isinstance(spec.final_norm, RMSNorm)
                 and all(getattr(spec.blocks[c.layer], "can_fold", lambda: False)() and c.cache is not None and c.write
                         for c in spec.schedule))
-        return self._foldable and rows <= FOLD_ROWS
+        return self._foldable and rows <= TUNING.few_rows
 
     def _forward_folded(self, ctx: StepContext):
         spec = self.spec
@@ -429,7 +432,7 @@ class ModelRunner:
             # the tokens of this step are the previous step's picks, taken on the device (the host
             # runs ahead without reading them back; request order must not have changed)
             self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
-        long_context = bool(arrays.max_seq_len > LONG_CONTEXT_KEYS)
+        long_context = bool(arrays.max_seq_len > TUNING.long_context_keys)
         if not self.decode_graphs:
             self._decode_eager(S, parity, long_context)      # nothing is recorded: no padding needed
         else:

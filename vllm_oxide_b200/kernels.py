@@ -14,6 +14,7 @@ import torch
 
 from .csrc.build import load_cuda_module
 from .errors import KernelError, ShapeError
+from .tuning import TUNING
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
 _P = ctypes.c_void_p
@@ -422,8 +423,6 @@ def _pick_splits(T: int, N: int, K: int, device) -> int:
 
 
 FUSED_GEMM_MAX_ROWS = 64      # what the fused kernels take
-PAIR_GEMM_FROM_ROWS = 1024    # from here the two-SM product with the SwiGLU epilogue beats the library product plus the activation kernel
-FUSED_GEMM_BEST_ROWS = 32     # up to here they beat the library product plus separate kernels (a decode step of 64 rows: 15 % slower)
 
 
 @_timed
@@ -659,16 +658,11 @@ def gemm_sm100_check() -> None:
                               "18-21 softmax rows); its result is not valid")
 
 
-# Above this many rows the library product is used for bfloat16 (None: the tensor-core kernel of this
-# package always). The hand-written kernel is the faster one for the few rows of a decode step.
-LIBRARY_GEMM_ABOVE_ROWS = 32
-
-
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out = a @ w^T. float32 operands: the true 32-bit kernel. bfloat16 operands: this package's
     tcgen05 kernel (TMA operands, float32 accumulation in tensor memory); for many rows, or
     operands TMA cannot address (K not a multiple of 8, unaligned rows), the library product
-    (cuBLAS through torch, float32 accumulation), as the reference plans for its own matrix
+    (cuBLAS through torch, float32 accumulation; above `TUNING.few_rows` rows), as the reference plans for its own matrix
     products (CLAUDE.md:107). `out` may be bfloat16 or float32."""
     op = "linear"
     if a.dtype == torch.float32:
@@ -681,7 +675,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
-    if (LIBRARY_GEMM_ABOVE_ROWS is None or a.shape[0] <= LIBRARY_GEMM_ABOVE_ROWS) and gemm_sm100_supported(a, w):
+    if a.shape[0] <= TUNING.few_rows and gemm_sm100_supported(a, w):
         gemm_sm100(a, w, out)
     else:
         _library_gemm_bf16(a, w, out)

@@ -1,5 +1,5 @@
 from .base import (CacheSpec, PagedTensorSpec, StateSpec, LayerCache, Workspace, StepContext, Mixer, FeedForward, Norm,
-                   PositionEncoding, LayerCall, ModelSpec, FoldedState, FOLD_ROWS)
+                   PositionEncoding, LayerCall, ModelSpec, FoldedState)
 from .rmsnorm import RMSNorm
 from .rotary import Rotary, rotary_inv_freq
 from .attention import Attention
@@ -8,5 +8,5 @@ from .embedding import Embedding, LMHead
 from .block import Block
 
 __all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
-           "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "FOLD_ROWS", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
+           "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
            "SwiGLU", "Embedding", "LMHead", "Block"]

@@ -19,6 +19,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
+from ..tuning import TUNING
 from .base import CacheSpec, FoldedState, LayerCache, Mixer, StepContext, aligned
 from .linear import matmul, to_compute
 
@@ -68,7 +69,7 @@ class Attention(Mixer):
 
     def _few_rows_path(self, rows: int) -> bool:
         """Steps of few rows: rotary positions and the cache write happen in the projection's epilogue."""
-        return (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and rows <= kernels.FUSED_GEMM_BEST_ROWS
+        return (self.dtype == torch.bfloat16 and self.fused and self.owns_cache and rows <= TUNING.few_rows
                 and kernels.gemm_qkv_rope_supported(self.hd) and self.hidden % 8 == 0)
 
     def workspace_bytes(self, rows: int) -> int:

@@ -174,7 +174,7 @@ class StepContext:
     decode_only: bool = False       # every request brings exactly one token and row i is request i
     lead_single: int = 0            # the first so many requests bring exactly one token each (host fact):
                                     # rows 0 .. lead_single - 1 are theirs, row i belonging to request i
-    long_context: bool = False      # some request is longer than LONG_CONTEXT_KEYS (host fact; a replayed
+    long_context: bool = False      # some request is longer than TUNING.long_context_keys (host fact; a replayed
                                     # step was recorded with the same value)
     host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them
 
@@ -191,11 +191,9 @@ class FoldedState:
     norm kernel runs. Parts that can work on this form offer `can_fold()` and `forward_folded`."""
     resid: torch.Tensor     # float32 [rows, hidden]
     xn: torch.Tensor        # bfloat16 [rows, hidden]
-    ssq: torch.Tensor       # float32 [ceil(hidden / 128), FOLD_ROWS]
+    ssq: torch.Tensor       # float32 [ceil(hidden / 128), TUNING.few_rows]
 
 
-FOLD_ROWS = 32              # most rows a step may have for the folded form
-LONG_CONTEXT_KEYS = 6144    # beyond this a step counts as one of long contexts (parts may pick other kernels)
 
 
 # ------------------------------------------------------------------------------ part interfaces

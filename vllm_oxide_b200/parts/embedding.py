@@ -6,7 +6,8 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import FOLD_ROWS, FoldedState, StepContext
+from ..tuning import TUNING
+from .base import FoldedState, StepContext
 from .linear import to_compute
 
 
@@ -31,7 +32,7 @@ class Embedding:
         """The embedding with the first norm's input prepared (see FoldedState)."""
         h = self.hidden
         st = FoldedState(resid=ctx.alloc((ctx.rows, h), torch.float32), xn=ctx.alloc((ctx.rows, h), torch.bfloat16),
-                         ssq=ctx.alloc((-(-h // 128), FOLD_ROWS), torch.float32))
+                         ssq=ctx.alloc((-(-h // 128), TUNING.few_rows), torch.float32))
         kernels.embed_fold(self.table, ctx.tokens, st.resid, next_norm.weight, st.xn, st.ssq, self.err_flag)
         return st
 

@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from ..tuning import TUNING
 from .base import FeedForward, FoldedState, StepContext, aligned
 from .linear import matmul, to_compute
 
@@ -30,9 +31,9 @@ class SwiGLU(FeedForward):
         epilogue), "pair" (the two-SM product with the activation in its epilogue) or "separate"
         (a product to gate|up, then the activation kernel)."""
         ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0
-        if ok and rows <= kernels.FUSED_GEMM_BEST_ROWS:
+        if ok and rows <= TUNING.few_rows:
             return "few"
-        if ok and rows >= kernels.PAIR_GEMM_FROM_ROWS:
+        if ok and rows >= TUNING.pair_gemm_from_rows:
             return "pair"
         return "separate"
 
@@ -45,7 +46,7 @@ class SwiGLU(FeedForward):
         def at(r):
             act = aligned(r * self.inter * es)
             return act + aligned(r * 2 * self.inter * es) if self._path(r) == "separate" else act
-        below = kernels.PAIR_GEMM_FROM_ROWS - 1
+        below = TUNING.pair_gemm_from_rows - 1
         return max(at(rows), at(below)) if rows > below else at(rows)
 
     def folded_workspace_bytes(self, rows: int) -> int:
@@ -55,7 +56,7 @@ class SwiGLU(FeedForward):
         if dtype == torch.float32:
             return ("elementwise", "gemm_f32")
         mods = ["elementwise", "gemm_sm100"]
-        if max_rows >= kernels.PAIR_GEMM_FROM_ROWS:
+        if max_rows >= TUNING.pair_gemm_from_rows:
             mods.append("gemm_sm100_pair")
         return tuple(mods)
 

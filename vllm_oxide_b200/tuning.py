@@ -1,0 +1,27 @@
+"""Where one kernel path hands over to another. These numbers change speed, never results: the tests
+run the paths on both sides of each. They were measured on one B200 at the layer sizes named beside
+them; a model of other sizes may want others. Set them on `TUNING` before an engine is built (a
+recorded CUDA graph keeps the path it was recorded with)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass
+class Tuning:
+    # Steps of at most so many rows run in the folded form (five kernels a layer: the products'
+    # epilogues do norm, rotation, cache write, activation and residual) on this package's few-token
+    # product; above it the library product and separate kernels take over. Measured at hidden 2,048 /
+    # intermediate 8,192: a decode step of 64 rows is 15 % slower in the folded form, one of 32 rows
+    # 22 % faster. At most 64 (what the fused kernels take).
+    few_rows: int = 32
+    # From so many rows the gate/up product runs on the two-SM kernel with the SwiGLU epilogue instead
+    # of the library product plus the activation kernel (measured at 2,048 x 16,384 x 2,048).
+    pair_gemm_from_rows: int = 1024
+    # A step in which some request has more keys than this counts as one of long contexts: decode
+    # attention then shares a request's keys over up to 64 blocks that merge through global memory
+    # instead of a cluster of 8 (measured with 8 kv heads of 64 and of 128: the cluster wins below).
+    long_context_keys: int = 6144
+
+
+TUNING = Tuning()

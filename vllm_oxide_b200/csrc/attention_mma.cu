@@ -373,10 +373,13 @@ __device__ __noinline__ void merge_partials(const float* __restrict__ all, int s
 // Steps of single decoded tokens. Grid (requests, kv heads, splits): a block reads its share of
 // the request's key tiles once for all G heads of the group; its 4 warps split every tile's 64
 // keys (16 each) and combine through shared memory. The `splits` blocks of one (request, kv
-// head) form a thread-block cluster: each leaves its unnormalised partial (running maximum, sum,
-// weighted values) in its own shared memory, the cluster meets at a barrier, and every block
-// then finishes a share of the outputs by reading its peers' partials through distributed shared
-// memory in rank order (a fixed order, so the result does not depend on timing). K/V tiles go
+// head) form a thread-block cluster: every block finishes a share of the outputs, and each sends
+// the pieces of its unnormalised partial (running maximum, sum, weighted values) to the blocks
+// that finish them, by stores into their shared memory (a region that nothing else uses, so a
+// fast peer may write while the owner still works on its tiles); the cluster meets at a barrier
+// once, and every block then adds up what it was sent in rank order (a fixed order, so the result
+// does not depend on timing) and leaves: nobody reads a peer's memory, so nobody has to wait for
+// the others to finish. K/V tiles go
 // through a cp.async ring of three stages (two when the grid is so large that the smaller
 // footprint lets one more block live on an SM). Bound: the K/V reads (memory).
 //
@@ -386,6 +389,15 @@ __device__ __noinline__ void merge_partials(const float* __restrict__ all, int s
 // block writes its partial to global memory and counts itself in, and the block that arrives
 // last adds the partials up in rank order and puts the counter back to zero. Nobody waits.
 // ---------------------------------------------------------------------------------------------
+
+// Shared memory of a decode block: the K/V ring (used again for the combine of the four warps),
+// then what the cluster's peers send, then the block's page list.
+template <int HD, int DEC_STAGES> __host__ __device__ constexpr size_t decode_ring_bytes() {
+    size_t ring = (size_t)(16 + 2 * DEC_STAGES * BN) * (HD + 8) * sizeof(__nv_bfloat16);
+    size_t combine = 16 * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)(128 + 4 * 16 * HD + 16 * HD + 32) * sizeof(float);
+    return ((ring > combine ? ring : combine) + 15) / 16 * 16;
+}
+__host__ __device__ constexpr size_t decode_recv_bytes(int G, int HD) { return (size_t)(G * HD + 8 + 256) * sizeof(float); }
 
 template <int HD, int DEC_STAGES>
 __global__ void __launch_bounds__(NTHREADS)
@@ -402,7 +414,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // 16 x LD
     __nv_bfloat16* sK0 = sQ + 16 * LD;                                          // DEC_STAGES x BN x LD
     __nv_bfloat16* sV0 = sK0 + DEC_STAGES * BN * LD;
-    int* s_pages = reinterpret_cast<int*>(sV0 + DEC_STAGES * BN * LD);  // this block's pages
+    // what the peers of a cluster send this block: [splits][chunk] values, [8][16] maxima, [8][16] sums
+    float* recv_val = reinterpret_cast<float*>(smem_raw + decode_ring_bytes<HD, DEC_STAGES>());
+    float* recv_m = recv_val + (H / KV) * HD + 8;
+    float* recv_l = recv_m + 128;
+    // this block's pages (a launch without a cluster has no region for what peers send)
+    int* s_pages = (!partials && gridDim.z > 1) ? reinterpret_cast<int*>(recv_l + 128) : reinterpret_cast<int*>(recv_val);
 
     // Positions and block tables were put on the device before this step's kernels began, and
     // every key but the newest was written by earlier steps: all of that may be read before the
@@ -410,6 +427,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     const int G = H / KV;
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     int splits = gridDim.z;
+    // every block of the cluster has started (and owns its shared memory) before anyone is sent
+    // anything: arrive now, wait just before the first store to a peer
+    if (!partials && splits > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     const int p = positions[seq];                 // one row per request: row index == request index
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_tables + (size_t)seq * max_pages;
@@ -525,6 +545,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         }
     }
     __syncthreads();
+    const bool push = splits > 1 && !partials;
+    const int chunk = (G * HD + splits - 1) / splits;          // outputs each block of a cluster finishes
+    if (push) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");       // the peers have started (they arrived at their start)
     for (int e = threadIdx.x; e < G * HD; e += NTHREADS) {
         int r = e / HD, d = e - r * HD;
         float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
@@ -538,6 +561,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         }
         if (splits == 1) {
             out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else if (push) {
+            // to the block that finishes this output; the row's maximum and sum to every block
+            const int owner = e / chunk;
+            uint32_t dst;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_u32(recv_val + split * chunk + (e - owner * chunk))), "r"(owner));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(acc) : "memory");
+            if (d == 0) {
+                for (int k = 0; k < splits; ++k) {
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(smem_u32(recv_m + split * 16 + r)), "r"(k));
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(M) : "memory");
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + 128 * 4), "f"(L) : "memory");
+                }
+            }
         } else {
             fin[r * HD + d] = acc;
             if (d == 0) { fin[16 * HD + r] = M; fin[16 * HD + 16 + r] = L; }
@@ -558,10 +594,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
                            out + (size_t)seq * out_stride + (size_t)kvh * G * HD);
         if (threadIdx.x == 0) arrived[seq * KV + kvh] = 0;      // ready for the next launch
     } else if (splits > 1) {
+        // what was sent is there once everyone has passed this barrier
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        const uint32_t fin_local = smem_u32(fin);
         const int total = G * HD;
-        const int chunk = (total + splits - 1) / splits;
         const int e0 = split * chunk, e1 = min(total, e0 + chunk);
         for (int e = e0 + threadIdx.x; e < e1; e += NTHREADS) {
             int r = e / HD, d = e - r * HD;
@@ -569,13 +604,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 pm[k] = -INFINITY; pl[k] = 0.f; po[k] = 0.f;
-                if (k < splits) {
-                    uint32_t base;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base) : "r"(fin_local), "r"(k));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(po[k]) : "r"(base + (uint32_t)((r * HD + d) * 4)) : "memory");
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pm[k]) : "r"(base + (uint32_t)((16 * HD + r) * 4)) : "memory");
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pl[k]) : "r"(base + (uint32_t)((16 * HD + 16 + r) * 4)) : "memory");
-                }
+                if (k < splits) { po[k] = recv_val[k * chunk + (e - e0)]; pm[k] = recv_m[k * 16 + r]; pl[k] = recv_l[k * 16 + r]; }
             }
             float M = -INFINITY;
 #pragma unroll
@@ -590,16 +619,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             }
             out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         }
-        // nobody leaves (and frees its shared memory) while a peer may still be reading it
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // nothing of this block is read by a peer: it may leave at once
     }
 }
 
 template <int HD> constexpr size_t prefill_smem() { return (size_t)(64 + 4 * BN) * (HD + 8) * sizeof(__nv_bfloat16); }
-template <int HD, int DEC_STAGES> constexpr size_t decode_smem() {
-    size_t ring = (size_t)(16 + 2 * DEC_STAGES * BN) * (HD + 8) * sizeof(__nv_bfloat16);
-    size_t combine = 16 * (HD + 8) * sizeof(__nv_bfloat16) + (size_t)(128 + 4 * 16 * HD + 16 * HD + 32) * sizeof(float);
-    return ring > combine ? ring : combine;
+template <int HD, int DEC_STAGES> size_t decode_smem(int G, bool cluster) {
+    return decode_ring_bytes<HD, DEC_STAGES>() + (cluster ? decode_recv_bytes(G, HD) : 0);
 }
 
 inline int log2_exact(int v) {
@@ -649,7 +675,7 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     long long per_max = (tiles_max + splits - 1) / splits;
     if (partials && per_max < 2 * DEC_MIN_TILES) per_max = 2 * DEC_MIN_TILES;
     long long pages_cta = per_max * (BN / page_size) + 1;
-    size_t smem = decode_smem<HD, ST>() + (size_t)pages_cta * sizeof(int);
+    size_t smem = decode_smem<HD, ST>(H / KV, splits > 1 && !partials) + (size_t)pages_cta * sizeof(int);
     int e = ensure_smem(attn_decode_mma_kernel<HD, ST>, smem, &configured);
     if (e) return e;
     cudaLaunchConfig_t cfg = {};
@@ -685,7 +711,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     }
     // three stages while every block of the grid can be resident at once with them; else two
     long long blocks = (long long)S * KV * splits;
-    long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>() + 2048));
+    long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>(H / KV, splits > 1 && !partials) + 2048));
     if (blocks <= fit3)
         return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
                                        window, scale, splits, partials, arrived, stream);

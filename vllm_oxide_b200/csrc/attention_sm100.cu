@@ -41,9 +41,11 @@
 // wait is bounded (see sm100.cuh); on expiry the block raises the error flag, frees its tensor
 // memory and returns.
 //
-// Head size 128 is the same kernel with every operand tile in two 64-wide halves (two TMA boxes,
-// twice the products per tile), O in 128 columns of tensor memory, Q read from shared memory (no
-// room for it in tensor memory) and a ring of two K and two V tiles freed separately. A group
+// Head size 128 is the same kernel with every operand tile in two 64-wide halves (two TMA boxes;
+// Q K^T takes both halves of the head dimension in turn, P V fills all 128 columns of O with one
+// instruction per 16 keys, the V tile's halves being one MN-major operand), O in 128 columns of
+// tensor memory, Q read from shared memory (no room for it in tensor memory) and a ring of two K
+// and two V tiles freed separately. A group
 // size G that does not divide 128 leaves the last 128 mod G rows of a block unused.
 //
 // Takes head_dim 64 or 128, any G up to 128, page sizes 8..128 (powers of two), no window. The
@@ -213,6 +215,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, 64, true);          // one 64-wide half of O at a time
+            constexpr uint32_t idesc_pv_wide = umma_idesc_bf16(BM, HD, true);
+            constexpr bool PV_WIDE = NH == 2;
             const uint32_t tO = tmem_base + COL_O;
             const uint32_t tQ = tmem_base + COL_Q;
             // S[j & 1] = Q K_j^T; tcgen05.mma of one thread run in issue order, so a product may be
@@ -245,12 +249,21 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 if (!mbar_wait(v_full + s, (j / ST) & 1, abort_flag, err_flag, 17)) break;
                 tcgen05_fence_after();
                 const uint32_t tP = tmem_base + (uint32_t)(j & 1) * BN;
+                if (PV_WIDE) {
+                    // all HD columns of O in one instruction per 16 keys: the V tile is an MN-major operand
+                    // whose 64-wide halves lie HALF_KV bytes apart (the descriptor's leading byte offset)
+                    const uint64_t vdesc = umma_desc_sw128(sV + s * tile_bytes<HD>(), HALF_KV);
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const uint64_t vdesc = umma_desc_sw128(sV + s * tile_bytes<HD>() + h * HALF_KV);
+                    for (int k = 0; k < BN / 16; ++k)
+                        umma_bf16_ts(tO, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv_wide, (j > 0 || k > 0) ? 1u : 0u);
+                } else {
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k)      // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
-                        umma_bf16_ts(tO + h * 64, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    for (int h = 0; h < NH; ++h) {
+                        const uint64_t vdesc = umma_desc_sw128(sV + s * tile_bytes<HD>() + h * HALF_KV);
+#pragma unroll
+                        for (int k = 0; k < BN / 16; ++k)      // 16 keys: 8 packed columns of P, 16 rows (2048 bytes) of V
+                            umma_bf16_ts(tO + h * 64, tP + 8 * k, vdesc + (uint64_t)k * (2048 >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
                 umma_commit(kv_free + s);                   // V (and K) of the tile may be overwritten; O holds the tile
                 if (j + 2 < n_tiles) ok = issue_qk(j + 2);

@@ -337,7 +337,7 @@ def serve_measure(llm, cfg, layers, n_requests, len_min, len_max, gen_len, peaks
             ctx = runner.manager.length(rid)
             flops += attn_flops * n * (ctx + (n + 1) / 2.0)
             keys += ctx + n
-        nbytes = runner.spec.weight_bytes + keys * runner.pools.bytes_per_token()
+        nbytes = runner.step_read_bytes(keys)
         ideal[0] += max(flops / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9))
         return upload(arrays)
     runner.upload = logging_upload
@@ -381,7 +381,7 @@ def all_config_points(peaks, steps, warmup):
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (8192,), generator=g).tolist() for _ in range(64)]
     ms, ctx_sum, _, regions = decode_device(llm, prompts, 64, k, warmup, 8192, gen)
-    nbytes = llm.runner.spec.weight_bytes + ctx_sum * llm.runner.pools.bytes_per_token()
+    nbytes = llm.runner.step_read_bytes(ctx_sum)
     gbs = nbytes / (ms / 1e3) / 1e9
     points["decode_b64_ctx8192_8b"] = {"value": 64 / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms, "steps": k, "regions": regions,
                                        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -707,7 +707,7 @@ def main():
     # ---------------------------------------------------------------- decode, device-timed and end to end
     ms_step, ctx_sum, launches, regions = decode_device(llm, prompts, a.batch, a.steps, a.warmup, prompt_len, gen_len)
     value = a.batch / (ms_step / 1e3)
-    read_bytes = runner.spec.weight_bytes + ctx_sum * runner.pools.bytes_per_token()
+    read_bytes = runner.step_read_bytes(ctx_sum)
     achieved = read_bytes / (ms_step / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]}
@@ -718,7 +718,7 @@ def main():
         for B in (1, 64):
             ms_b, ctx_b, _, _ = decode_device(llm, prompts, B, min(a.steps, 64), a.warmup, prompt_len, gen_len)
             points[f"decode_b{B}"] = B / (ms_b / 1e3)
-            gbs = (runner.spec.weight_bytes + ctx_b * runner.pools.bytes_per_token()) / (ms_b / 1e3) / 1e9
+            gbs = runner.step_read_bytes(ctx_b) / (ms_b / 1e3) / 1e9
             points[f"decode_b{B}_hbm_frac"] = gbs / peaks["hbm_gbs"]
     weights_gb = runner.spec.weight_bytes / 1e9
     graphs_on = bool(runner.graphs_enabled)

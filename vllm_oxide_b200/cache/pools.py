@@ -111,5 +111,3 @@ class CachePools:
     def bytes_per_token(self) -> int:
         return sum(self.page_bytes) // self.page_size
 
-    def total_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for ts in self.kv.values() for t in ts)

@@ -45,7 +45,7 @@ template <> struct Vec16<__nv_bfloat16> {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 8)
 paged_attention_warp_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
                             const T* __restrict__ kcache, const T* __restrict__ vcache,
                             const int* __restrict__ block_tables, int max_pages,

@@ -512,7 +512,7 @@ class ModelRunner:
             self.pools.reset_slot(slot)
         return slot
 
-    def decode_read_bytes(self, context_lens) -> int:
-        """Bytes a decode step of these contexts must read: every weight once, plus the cache of
-        the live requests."""
-        return self.spec.weight_bytes + sum(int(c) for c in context_lens) * self.pools.bytes_per_token()
+    def step_read_bytes(self, cached_tokens: int) -> int:
+        """Bytes a step must read at least: every weight once, plus the cache of `cached_tokens`
+        tokens (the contexts of the live requests, summed)."""
+        return self.spec.weight_bytes + int(cached_tokens) * self.pools.bytes_per_token()

@@ -17,9 +17,6 @@ class Embedding:
         self.vocab, self.hidden = self.table.shape
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
-    def weight_bytes_per_row(self) -> int:
-        return self.hidden * self.table.element_size()
-
     def kernel_modules(self, dtype, max_rows):
         return ("elementwise",)
 

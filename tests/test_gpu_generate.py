@@ -318,6 +318,51 @@ def test_tight_pool_and_replayed_steps_change_no_token_in_f32():
     assert outs[0] == outs[1]
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_models_and_engine_settings_change_no_token_in_f32(seed):
+    """Drawn from the seed: a small model (head size 16 to 128, heads and groups, widths that are no
+    power of two, tied or own output head, llama3 scaling or none), a handful of requests with greedy
+    and temperature sampling and stop tokens, and engine settings (page size, token budget, requests
+    per step, a pool from just enough for one request to most of what all need, graphs of either kind
+    on or off, running ahead or not). In float32 the tokens equal those of a roomy engine that
+    launches step by step, and no page is lost."""
+    import random
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import EngineConfig, LlamaConfig, RopeScaling
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    rnd = random.Random(1000 + seed)
+    hd, kv, group = rnd.choice([16, 32, 64, 128]), rnd.choice([1, 2, 4]), rnd.choice([1, 2, 4])
+    vocab = rnd.choice([500, 1000, 1531])
+    cfg = LlamaConfig(hidden_size=rnd.choice([96, 160, 192, 256]), intermediate_size=rnd.choice([200, 320, 512]),
+                      num_hidden_layers=rnd.choice([1, 2, 3]), num_attention_heads=kv * group, num_key_value_heads=kv, head_dim=hd,
+                      vocab_size=vocab, max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      rope_scaling=rnd.choice([None, RopeScaling(8.0, 1.0, 4.0, 64)]), tie_word_embeddings=rnd.choice([True, False]))
+    tensors = random_tensors(models.llama_manifest(cfg), seed, 0.08, torch.float32, "cuda:0")
+    n = rnd.randint(6, 24)
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(2, rnd.choice([60, 300]), (n,), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (k,), generator=g).tolist() for k in lens]
+    params = [sp(max_new_tokens=rnd.randint(1, 40), temperature=0.0 if rnd.random() < 0.6 else 0.8, seed=i,
+                 stop_token_ids=rnd.choice([(), (3, 7, 11)])) for i in range(n)]
+    page = rnd.choice([8, 16, 32])
+    longest = max(k + p.max_new_tokens for k, p in zip(lens, params))
+    max_len = -(-longest // page) * page + page
+    per_request = max_len // page
+    roomy = dict(max_batch_tokens=1024, max_seqs=n, num_pages=n * per_request + 8, step_graphs=0, cuda_graphs=False, run_ahead=False)
+    drawn = dict(max_batch_tokens=rnd.choice([16, 64, 256]), max_seqs=rnd.choice([2, 4, 8, 16]),
+                 num_pages=max(per_request + 1, int(rnd.uniform(0.15, 0.7) * n * per_request)),
+                 step_graphs=rnd.choice([0, 1, 2]), cuda_graphs=rnd.choice([True, False]), run_ahead=rnd.choice([True, False]))
+    outs = []
+    for kw in (roomy, drawn):
+        llm = LLM(ModelRunner(cfg, tensors, EngineConfig(max_model_len=max_len, block_size=page, dtype="float32", **kw)))
+        outs.append([o.token_ids for o in llm.generate(prompts, params)])
+        r = llm.runner
+        assert r.manager.check_invariants() == "" and r.manager.num_free_pages(0) == r.manager.num_pages(0), kw
+    assert outs[0] == outs[1], drawn
+    assert all(1 <= len(t) <= p.max_new_tokens for t, p in zip(outs[0], params))
+
+
 @pytest.mark.parametrize("run_ahead", [False, True])
 def test_tokens_are_reported_as_they_are_read(tmp_path_factory, run_ahead):
     """`on_token`: every generated token once, in order, the stop token included, nothing that was

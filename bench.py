@@ -436,7 +436,7 @@ def kernel_case(argv):
                     help="attn_decode: how the blocks of a request merge (auto: the engine's choice)")
     ap.add_argument("--impl-attn", default="sm100", choices=["sm100", "mma"], help="attn_prefill: the tcgen05 or the mma.sync kernel")
     ap.add_argument("--epilogue", default="store", choices=["store", "swiglu", "resid"], help="gemm_fused: the epilogue")
-    ap.add_argument("--splits", type=int, default=None, help="attn_decode: blocks per request and kv head (default: the engine's choice)")
+    ap.add_argument("--splits", type=int, default=None, help="attn_decode: blocks per request and kv head; gemm_fused: blocks that share K (default: the engine's choice)")
     a = ap.parse_args(argv)
     dev = "cuda:0"
     bf = torch.bfloat16
@@ -452,17 +452,17 @@ def kernel_case(argv):
             fused = kernels.gemm_fused
             if a.epilogue == "swiglu":
                 out = torch.empty(a.rows, a.out // 2, dtype=bf, device=dev)
-                launches = [lambda w=w: fused(x, w, out, kernels.EPI_SWIGLU, a.out // 2) for w in ws]
+                launches = [lambda w=w: fused(x, w, out, kernels.EPI_SWIGLU, a.out // 2, splits=a.splits) for w in ws]
             elif a.epilogue == "resid":
                 out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
                 resid = torch.zeros(a.rows, a.out, dtype=torch.float32, device=dev)
                 nw = torch.ones(a.out, dtype=torch.float32, device=dev)
                 ssq = torch.zeros(-(-a.out // 128), 64, dtype=torch.float32, device=dev)
                 ssq = torch.zeros(-(-a.out // 128), 64, dtype=torch.float32, device=dev)
-                launches = [lambda w=w: fused(x, w, None, kernels.EPI_RESID, a.out, resid=(resid, nw, out, ssq)) for w in ws]
+                launches = [lambda w=w: fused(x, w, None, kernels.EPI_RESID, a.out, resid=(resid, nw, out, ssq), splits=a.splits) for w in ws]
             else:
                 out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
-                launches = [lambda w=w: fused(x, w, out, kernels.EPI_STORE, a.out) for w in ws]
+                launches = [lambda w=w: fused(x, w, out, kernels.EPI_STORE, a.out, splits=a.splits) for w in ws]
         else:
             out = torch.empty(a.rows, a.out, dtype=bf, device=dev)
             if a.kernel == "gemm_library":           # the library product the engine uses for many rows, for comparison

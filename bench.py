@@ -487,11 +487,15 @@ def kernel_case(argv):
         scale = 1.0 / math.sqrt(hd)
         if a.kernel == "attn_decode":
             pos = torch.full((S,), L - 1, dtype=torch.int32, device=dev)
-            # the engine's choice (parts/attention.py decode_splits): a cluster of up to 8 blocks per request
-            # and kv head, or, for few requests with long contexts, up to 64 that merge through global memory
+            # auto: the engine's choice (parts/attention.py decode_split_rule): a cluster of up to 8 blocks per
+            # request and kv head, or, for few requests with long contexts, up to 64 that merge through global memory
+            from vllm_oxide_b200.parts.attention import decode_split_rule
             sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            wide = 3 * sms // (S * KV) >= 4 and (ctx > TUNING.long_context_keys if a.merge == "auto" else a.merge == "global")
-            splits = max(1, min(64, 3 * sms // (S * KV))) if wide else max(1, min(8, -(-2 * sms // (S * KV))))
+            if a.merge == "auto":
+                splits, wide = decode_split_rule(S, KV, sms, ctx > TUNING.long_context_keys)
+            else:
+                wide = a.merge == "global" and 3 * sms // (S * KV) >= 4
+                splits = max(1, min(64, 3 * sms // (S * KV))) if wide else max(1, min(8, -(-2 * sms // (S * KV))))
             if a.splits:
                 splits = a.splits
             partials = torch.empty(kernels.attn_decode_partial_floats(S, KV, hd, splits), device=dev) if wide else None

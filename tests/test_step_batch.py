@@ -104,3 +104,20 @@ def test_shape_class_of_a_step():
     assert step_shape_class(1999, 5, 4, 1930, 3, LONG_CONTEXT_KEYS + 1, 2048) == (2048, 5, 4, 1984, 3, True)
     assert step_shape_class(130, 2, 2, 129, 0, 500, 192) == (192, 2, 2, 192, 0, False)    # never beyond the engine's rows
     assert step_shape_class(40, 4, 4, 37, 0, 90, 48) == (48, 4, 4, 48, 0, False)
+
+
+def test_how_decode_attention_shares_a_request_over_blocks():
+    """The rule that picks blocks per request and kv head and the way they merge: whatever the counts,
+    it names something the kernel takes (a cluster of at most 8, or with the merge through global
+    memory at most 64 blocks), and the measured cases keep their choices."""
+    from vllm_oxide_b200.parts.attention import decode_split_rule
+    for sms in (1, 7, 108, 132, 148, 200):
+        for kv in (1, 2, 3, 8, 16):
+            for seqs in (1, 2, 3, 8, 17, 64, 500):
+                for long_context in (False, True):
+                    splits, wide = decode_split_rule(seqs, kv, sms, long_context)
+                    assert 1 <= splits <= (64 if wide else 8) and (long_context or not wide)
+    assert decode_split_rule(8, 8, 148, False) == (5, False)          # the benchmark's decode step
+    assert decode_split_rule(64, 8, 148, False) == (1, False)
+    assert decode_split_rule(1, 8, 148, True) == (55, True)           # one long request
+    assert decode_split_rule(8, 8, 148, True) == (6, True)

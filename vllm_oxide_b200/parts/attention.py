@@ -24,6 +24,24 @@ from .base import CacheSpec, FoldedState, LayerCache, Mixer, StepContext, aligne
 from .linear import matmul, to_compute
 
 
+def decode_split_rule(num_seqs: int, kv_heads: int, num_sms: int, long_context: bool = False):
+    """(splits, wide): how many blocks share one request's keys in a decode step and whether they
+    merge through global memory. Up to 8 blocks form a cluster and merge through shared memory:
+    enough that the grid fills the GPU twice over. With long contexts and few requests (at least 4
+    blocks per request and kv head at three blocks per SM, which is what fits with the three-stage
+    ring), up to 64 blocks merge through global memory instead (`wide`), and a request uses as many
+    of them as its length is worth. Measured with 8 kv heads of 64: one request of 131,072 keys
+    175 us in clusters of 8, 51 us wide; 8 requests of 32,768 keys 107 / 94 us; below some 6,000
+    keys the cluster is faster. (Merging in clusters of 8 first and only the clusters' sums through
+    global memory was built and measured for one request: a decode step at batch 1 took 0.824
+    instead of 0.865 ms with 8,192 keys, but 1.019 instead of 0.998 ms with 32,768, where 48 longer
+    blocks per kv head replace 55. Not kept.)"""
+    blocks = max(1, num_seqs * kv_heads)
+    if long_context and 3 * num_sms // blocks >= 4:
+        return min(64, 3 * num_sms // blocks), True
+    return max(1, min(8, -(-2 * num_sms // blocks))), False
+
+
 class Attention(Mixer):
     def __init__(self, wq: torch.Tensor, wk: Optional[torch.Tensor], wv: Optional[torch.Tensor], wo: torch.Tensor,
                  num_heads: int, num_kv_heads: int, head_dim: int, position=None, window: Optional[int] = None,
@@ -180,15 +198,4 @@ class Attention(Mixer):
                                 self.scale, self.window, splits, self._partials if wide else None, self._arrived if wide else None)
 
     def decode_splits(self, num_seqs: int, long_context: bool = False):
-        """(splits, wide): how many blocks share one request's keys in a decode step. Up to 8 blocks
-        form a cluster and merge through shared memory: enough that the grid fills the GPU twice
-        over. With long contexts and few requests (at least 4 blocks per request and kv head at
-        three blocks per SM, which is what fits with the three-stage ring), up to 64 blocks merge
-        through global memory instead (`wide`), and a request uses as many of them as its length
-        is worth. Measured with 8 kv heads of 64: one request of 131,072 keys 175 us in clusters
-        of 8, 51 us wide; 8 requests of 32,768 keys 107 / 94 us; below some 6,000 keys the cluster
-        is faster."""
-        blocks = max(1, num_seqs * self.KV)
-        if long_context and 3 * self.num_sms // blocks >= 4:
-            return min(64, 3 * self.num_sms // blocks), True
-        return max(1, min(8, -(-2 * self.num_sms // blocks))), False
+        return decode_split_rule(num_seqs, self.KV, self.num_sms, long_context)

@@ -231,8 +231,9 @@ def decode_device(llm, prompts, B, steps, warmup, prompt_len, gen_len):
         n0 = kernels.launch_count()
         e0, e1 = ev(), ev()
         e0.record()
-        for plan, arrays in planned[region * steps:(region + 1) * steps]:
-            r.decode_step_graph(None, plan, feed_from_device=True, read=False, arrays=arrays)
+        for i, (plan, arrays) in enumerate(planned[region * steps:(region + 1) * steps]):
+            # alternating result and metadata buffers, as the engine's loop does when it runs ahead
+            r.decode_step_graph(None, plan, feed_from_device=True, read=False, parity=i & 1, arrays=arrays)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) / steps)

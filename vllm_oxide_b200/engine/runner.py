@@ -115,6 +115,17 @@ class ModelRunner:
         self._stage_done = [None] * len(self._stage)
         self._stage_next = 0
         self.step_dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        # Decode steps launched ahead of the host's reads alternate between two buffers (`parity`): the
+        # metadata of step n + 1 is then copied to the device on a stream of its own WHILE step n runs,
+        # instead of between the two (a copy of 20 KB takes some 10 us from request to arrival).
+        # Buffer 0 is also the one every other step uses.
+        self._devs = [self.step_dev, torch.zeros(total, dtype=torch.int32, device=self.device)]
+        self._dev = self.step_dev               # the buffer the step being launched reads
+        self._dev_read = [torch.cuda.Event(), torch.cuda.Event()]    # the last launch that reads buffer p has been executed
+        self._dev_read_set = [False, False]
+        self._uploaded = torch.cuda.Event()
+        self._feed_ready = None                 # the buffer whose token rows hold the last decode step's picks
+        self._copy_stream = torch.cuda.Stream(device=self.device)
         # workspace: residual + two pending buffers + the largest block + the head's chunk
         self._foldable = None
         if not 0 <= TUNING.few_rows <= kernels.FUSED_GEMM_MAX_ROWS:
@@ -198,7 +209,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     def context(self, rows: int, seqs: int, arrays=None, layout=None) -> StepContext:
-        L, d = layout or self.layout, self.step_dev
+        L, d = layout or self.layout, self._dev
         mp = self.max_pages
         seqs_cap = L["seqs_cap"]
 
@@ -222,19 +233,39 @@ class ModelRunner:
             long_context=bool(arrays is not None and arrays.max_seq_len > TUNING.long_context_keys),
             lead_single=int(arrays.lead_single) if arrays is not None else 0)
 
-    def upload(self, arrays) -> None:
-        """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic."""
+    def upload(self, arrays, parity: int = 0, beside: bool = False, first: int = 0) -> None:
+        """One pinned host buffer, one asynchronous copy: the step's only host-to-device traffic.
+        `beside`: the copy goes to buffer `parity` on the copy stream, ordered only behind the last
+        launch that read that buffer, so it runs beside whatever the main stream still has to do; the
+        main stream then waits for it. `first`: where the copy starts (a step whose tokens are already
+        on the device leaves the token rows, which lie in front, alone)."""
         n = arrays.used
-        self.last_upload_bytes = 4 * n
+        self.last_upload_bytes = 4 * (n - first)
         i = self._stage_next
         self._stage_next = (i + 1) % len(self._stage)
         if self._stage_done[i] is not None:
             self._stage_done[i].synchronize()        # the copy that last read this buffer has run
-        arrays.copy_into(self._stage_np[i])
-        self.step_dev[:n].copy_(self._stage[i][:n], non_blocking=True)
-        if self._stage_done[i] is None:
+        else:
             self._stage_done[i] = torch.cuda.Event()
-        self._stage_done[i].record()
+        arrays.copy_into(self._stage_np[i])
+        dst = self._devs[parity]
+        if not beside:
+            dst[first:n].copy_(self._stage[i][first:n], non_blocking=True)
+            self._stage_done[i].record()
+            return
+        cs = self._copy_stream
+        if self._dev_read_set[parity]:
+            cs.wait_event(self._dev_read[parity])
+        with torch.cuda.stream(cs):
+            dst[first:n].copy_(self._stage[i][first:n], non_blocking=True)
+            self._stage_done[i].record(cs)
+            self._uploaded.record(cs)
+        torch.cuda.current_stream().wait_event(self._uploaded)
+
+    def _mark_read(self, parity: int) -> None:
+        """Everything launched so far that reads metadata buffer `parity` lies before this point of the stream."""
+        self._dev_read[parity].record()
+        self._dev_read_set[parity] = True
 
     def build_arrays(self, entries):
         """Lay out a batch given as runtime StepEntry objects (pages must be reserved already)."""
@@ -286,7 +317,7 @@ class ModelRunner:
         """Final norm and output head on the wanted rows, in chunks; a token is picked from every
         row; logits are copied out only where the caller gave a place for them."""
         spec, L = self.spec, layout or self.layout
-        d = self.step_dev
+        d = self._dev
         V = spec.vocab_size
         if (self.engine.pick_in_head and logits_out is None and self._folded is not None and ctx.decode_only
                 and num_logit_rows == ctx.rows <= self.logit_chunk
@@ -331,6 +362,7 @@ class ModelRunner:
                                        or logits_out.shape[1] != self.spec.vocab_size or logits_out.dtype != torch.float32):
             raise ShapeError("step", f"logits_out must be float32 [>={R}, {self.spec.vocab_size}]")
         self.upload(arrays)
+        self._feed_ready = None
         shape = self._step_shape(arrays) if logits_out is None else None
         if shape is not None:
             entry = self._step_graphs.get(shape)
@@ -340,6 +372,7 @@ class ModelRunner:
                 kernels.count_launches(entry[1])
                 self.steps_run += 1
                 self.step_graph_replays += 1
+                self._mark_read(0)
                 return StepResult(self.sampled, None, R)
         self.workspace.reset()
         if shape is None:
@@ -354,6 +387,7 @@ class ModelRunner:
         if R:
             self._head(resid, pending, ctx, R, logits_out)
         self.steps_run += 1
+        self._mark_read(0)
         if shape is not None:
             if len(self._step_seen) > 4096:
                 self._step_seen.clear()                 # a count per shape class ever seen: keep it bounded
@@ -427,11 +461,16 @@ class ModelRunner:
             arrays = self.decode_arrays(scheduler, plan)
         if arrays.max_seq_len > self.max_model_len:
             raise CapacityError("sequence length", int(arrays.max_seq_len), self.max_model_len)
-        self.upload(arrays)
         if feed_from_device:
-            # the tokens of this step are the previous step's picks, taken on the device (the host
-            # runs ahead without reading them back; request order must not have changed)
-            self.step_dev[L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
+            # The tokens of this step are the previous step's picks, taken on the device (the host runs
+            # ahead without reading them back; request order must not have changed): a decode step
+            # leaves its picks in the token rows of the OTHER buffer itself. The rest of the metadata
+            # is copied beside the step in front, which reads its own buffer.
+            self.upload(arrays, parity, beside=not read, first=L["positions"])
+            if self._feed_ready != parity:
+                self._devs[parity][L["tokens"]:L["tokens"] + S].copy_(self.sampled[:S])
+        else:
+            self.upload(arrays, parity)
         long_context = bool(arrays.max_seq_len > TUNING.long_context_keys)
         if not self.decode_graphs:
             self._decode_eager(S, parity, long_context)      # nothing is recorded: no padding needed
@@ -456,6 +495,8 @@ class ModelRunner:
                 graph.replay()
                 kernels.count_launches(self._graph_launches[key])
         self.steps_run += 1
+        self._mark_read(parity)
+        self._feed_ready = 1 - parity
         if not read:
             ev = torch.cuda.Event()
             ev.record()
@@ -492,11 +533,17 @@ class ModelRunner:
     def _decode_eager(self, b: int, parity: int = 0, long_context: bool = False) -> None:
         L = self.decode_layout
         self.workspace.reset()
-        ctx = self.context(b, b, None, L)
-        ctx.decode_only, ctx.max_new, ctx.long_context = True, 1, long_context
-        resid, pending = self._forward(ctx)
-        self._head(resid, pending, ctx, b, None, L)
+        self._dev = self._devs[parity]          # this step's metadata (a recorded step keeps reading this buffer)
+        try:
+            ctx = self.context(b, b, None, L)
+            ctx.decode_only, ctx.max_new, ctx.long_context = True, 1, long_context
+            resid, pending = self._forward(ctx)
+            self._head(resid, pending, ctx, b, None, L)
+        finally:
+            self._dev = self.step_dev
         self.sampled_host[parity, :b].copy_(self.sampled[:b], non_blocking=True)
+        # the picks as the next decode step's tokens, should it be fed from the device
+        self._devs[1 - parity][L["tokens"]:L["tokens"] + b].copy_(self.sampled[:b])
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def check_kernels(self) -> None:

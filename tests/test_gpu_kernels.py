@@ -294,6 +294,44 @@ def test_pick_tokens_greedy_cases():
     assert out.tolist()[:4] == want
 
 
+def test_pick_writes_its_tokens_to_further_places():
+    """`also`: the pick kernel writes the same tokens to up to two more places, a device tensor and a
+    page-locked host buffer that the device addresses directly (no copy behind the kernel); both the
+    two-pass pick and the final pass alone; what lies around the rows stays as it was."""
+    from vllm_oxide_b200.errors import ShapeError
+    V = 10007
+    logits = torch.full((5, V), -1.0, device=DEV)
+    for r, i in enumerate([5000, 3, V - 1, 0, 77]):
+        logits[r, i] = 2.0 + r
+    logits[4, 78] = float("nan")
+    k = K()
+    sp = k.pick_splits(V)
+    host = k.HostInts((2, 8))
+    host.tensor.fill_(-7)
+    dev2 = torch.full((9,), -7, dtype=torch.int32, device=DEV)
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(5, dtype=torch.int32, device=DEV)
+    val, idx = torch.empty(5 * sp, device=DEV), torch.empty(5 * sp, dtype=torch.int32, device=DEV)
+    k.pick_tokens(logits, out, flags, val, idx, also=[dev2[2:7], host.at(8 + 1)])
+    torch.cuda.synchronize()
+    want = [5000, 3, V - 1, 0, -1]
+    assert out.tolist() == want and dev2.tolist() == [-7, -7] + want + [-7, -7]
+    assert host.tensor.tolist() == [[-7] * 8, [-7] + want + [-7, -7]]
+    # the final pass alone, pairs given: one destination only
+    part_val = torch.tensor([[1.0, 5.0, 5.0], [0.0, -1.0, 7.0]], device=DEV)
+    part_idx = torch.tensor([[9, 4, 6], [1, 2, 3]], dtype=torch.int32, device=DEV)
+    out2 = torch.zeros(2, dtype=torch.int32, device=DEV)
+    k.pick_final(part_val, part_idx, 2, 100, torch.zeros(2, dtype=torch.int32, device=DEV), out2, also=[host.at(0)])
+    torch.cuda.synchronize()
+    assert out2.tolist() == [4, 3] and host.tensor[0].tolist() == [4, 3] + [-7] * 6
+    with pytest.raises(ShapeError, match="room for"):
+        k.pick_final(part_val, part_idx, 2, 100, flags, out2, also=[host.at(15)])
+    with pytest.raises(ShapeError, match="at most two"):
+        k.pick_final(part_val, part_idx, 2, 100, flags, out2, also=[out2, out2, out2])
+    with pytest.raises(ShapeError):
+        k.pick_tokens(logits, out, flags, val, idx, also=[dev2[:3]])
+
+
 def test_pick_tokens_temperature_matches_plain_and_law():
     V = 997
     g = torch.Generator().manual_seed(5)

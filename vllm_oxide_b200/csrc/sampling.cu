@@ -92,8 +92,12 @@ pick_partial_kernel(const float* __restrict__ logits, long long ld, int V, const
     }
 }
 
+// `also_a`, `also_b` (either may be null): two more places the picked token of every row is written
+// to, e.g. the next step's token rows and a host buffer the device can address, so that no copy has
+// to follow the kernel.
 __global__ void pick_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
-                                  int splits, int V, int* __restrict__ nan_flags, int* __restrict__ out) {
+                                  int splits, int V, int* __restrict__ nan_flags, int* __restrict__ out,
+                                  int* also_a, int* also_b) {
     pdl_launch_dependents();
     pdl_wait(10);
     __shared__ Best sh[32];
@@ -108,6 +112,8 @@ __global__ void pick_final_kernel(const float* __restrict__ part_val, const int*
         int tok = (b.i >= 0 && b.i < V) ? b.i : 0;
         if (nan_flags[r]) { tok = -1; nan_flags[r] = 0; }
         out[r] = tok;
+        if (also_a) also_a[r] = tok;
+        if (also_b) also_b[r] = tok;
     }
 }
 
@@ -120,9 +126,9 @@ VOB_EXPORT int vob_pick_splits(int V) {
     return s < 1 ? 1 : (s > 256 ? 256 : s);
 }
 
-VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, const float* temperature,
-                               const uint32_t* seeds, const int* steps, int splits, float* part_val,
-                               int* part_idx, int* nan_flags, int* out, cudaStream_t stream) {
+VOB_EXPORT int vob_pick_tokens_to(const float* logits, long long ld, int R, int V, const float* temperature,
+                                  const uint32_t* seeds, const int* steps, int splits, float* part_val,
+                                  int* part_idx, int* nan_flags, int* out, int* also_a, int* also_b, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || splits <= 0 || ld < V || R > 65535) return VOB_ERR_BAD_ARG;
     if (temperature && (!seeds || !steps)) return VOB_ERR_BAD_ARG;
@@ -131,18 +137,39 @@ VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, 
                        part_val, part_idx, nan_flags);
     if (e) return e;
     return vob_launch(pick_final_kernel, dim3(R), dim3(64), 0, stream, (const float*)part_val, (const int*)part_idx, splits, V,
-                      nan_flags, out);
+                      nan_flags, out, also_a, also_b);
+}
+
+VOB_EXPORT int vob_pick_tokens(const float* logits, long long ld, int R, int V, const float* temperature,
+                               const uint32_t* seeds, const int* steps, int splits, float* part_val,
+                               int* part_idx, int* nan_flags, int* out, cudaStream_t stream) {
+    return vob_pick_tokens_to(logits, ld, R, V, temperature, seeds, steps, splits, part_val, part_idx, nan_flags, out, nullptr,
+                              nullptr, stream);
 }
 
 // The second launch alone: the pairs come from elsewhere (the output head's own epilogue reduces
 // each of its tiles to a pair: EPI_PICK in gemm_sm100.cu), `splits` of them per row.
-VOB_EXPORT int vob_pick_final(const float* part_val, const int* part_idx, int R, int splits, int V, int* nan_flags, int* out,
-                              cudaStream_t stream) {
+VOB_EXPORT int vob_pick_final_to(const float* part_val, const int* part_idx, int R, int splits, int V, int* nan_flags, int* out,
+                                 int* also_a, int* also_b, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || splits <= 0 || R > 65535) return VOB_ERR_BAD_ARG;
     // one pair per thread where that is possible: a thread that walks many pairs pays a memory round trip for each
     const int threads = splits > 512 ? 1024 : splits > 256 ? 512 : splits > 64 ? 256 : 64;
-    return vob_launch(pick_final_kernel, dim3(R), dim3(threads), 0, stream, part_val, part_idx, splits, V, nan_flags, out);
+    return vob_launch(pick_final_kernel, dim3(R), dim3(threads), 0, stream, part_val, part_idx, splits, V, nan_flags, out, also_a,
+                      also_b);
+}
+
+VOB_EXPORT int vob_pick_final(const float* part_val, const int* part_idx, int R, int splits, int V, int* nan_flags, int* out,
+                              cudaStream_t stream) {
+    return vob_pick_final_to(part_val, part_idx, R, splits, V, nan_flags, out, nullptr, nullptr, stream);
+}
+
+// The address under which the device reaches a page-locked host buffer (0 on success). A kernel may
+// then write there directly; what it wrote is the host's to read once the kernel has completed.
+VOB_EXPORT int vob_host_device_pointer(void* host, void** device) {
+    if (!host || !device) return VOB_ERR_BAD_ARG;
+    *device = nullptr;
+    return (int)cudaHostGetDevicePointer(device, host, 0);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -140,8 +140,11 @@ class ModelRunner:
         self.pick_idx = torch.empty(self.logit_chunk * pairs, dtype=torch.int32, device=self.device)
         self.nan_flags = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
         self.sampled = torch.zeros(self.logits_cap, dtype=torch.int32, device=self.device)
-        # two pinned buffers: a step's picks may still be unread when the next step writes its own
-        self.sampled_host = torch.zeros((2, self.seqs_cap), dtype=torch.int32, pin_memory=True)
+        # two pinned buffers: a step's picks may still be unread when the next step writes its own.
+        # The pick kernel of a decode step writes them there itself (page-locked host memory that the
+        # device can address), so no copy follows the step's last kernel.
+        self._sampled_host_ints = kernels.HostInts((2, self.seqs_cap))
+        self.sampled_host = self._sampled_host_ints.tensor
         self.sampled_host_np = self.sampled_host.numpy()
         self.steps_run = 0
         self.last_upload_bytes = 0
@@ -313,9 +316,10 @@ class ModelRunner:
         return resid, pending
 
     def _head(self, resid, pending, ctx: StepContext, num_logit_rows: int, logits_out: Optional[torch.Tensor],
-              layout=None) -> None:
+              layout=None, also=()) -> None:
         """Final norm and output head on the wanted rows, in chunks; a token is picked from every
-        row; logits are copied out only where the caller gave a place for them."""
+        row; logits are copied out only where the caller gave a place for them. `also`: functions
+        (first row, rows) -> a further place the picked tokens of those rows are written to."""
         spec, L = self.spec, layout or self.layout
         d = self._dev
         V = spec.vocab_size
@@ -329,7 +333,7 @@ class ModelRunner:
             spec.lm_head.pick_folded(self._folded, spec.final_norm.eps, n, d[L["temperature"]:L["temperature"] + n].view(torch.float32),
                                      d[L["seeds"]:L["seeds"] + 2 * n], d[L["sample_steps"]:L["sample_steps"] + n],
                                      self.pick_val[:n * tiles].view(n, tiles), self.pick_idx[:n * tiles].view(n, tiles),
-                                     self.nan_flags[:n], self.sampled[:n])
+                                     self.nan_flags[:n], self.sampled[:n], [f(0, n) for f in also])
             return
         for c0 in range(0, num_logit_rows, self.logit_chunk):
             n = min(self.logit_chunk, num_logit_rows - c0)
@@ -347,7 +351,7 @@ class ModelRunner:
                 seeds = d[L["seeds"] + 2 * c0:L["seeds"] + 2 * (c0 + n)]
                 steps = d[L["sample_steps"] + c0:L["sample_steps"] + c0 + n]
                 kernels.pick_tokens(logits, self.sampled[c0:c0 + n], self.nan_flags[c0:c0 + n], self.pick_val,
-                                    self.pick_idx, temp, seeds, steps)
+                                    self.pick_idx, temp, seeds, steps, [f(c0, n) for f in also])
                 if logits_out is not None:
                     logits_out[c0:c0 + n].copy_(logits, non_blocking=logits_out.is_cuda)
 
@@ -538,12 +542,14 @@ class ModelRunner:
             ctx = self.context(b, b, None, L)
             ctx.decode_only, ctx.max_new, ctx.long_context = True, 1, long_context
             resid, pending = self._forward(ctx)
-            self._head(resid, pending, ctx, b, None, L)
+            # the picks also go to the host buffer of this parity and, as the next decode step's
+            # tokens should it be fed from the device, to the token rows of the other metadata buffer:
+            # written by the pick kernel itself (two copies behind it cost a replayed step 14 us)
+            other, host, t0 = self._devs[1 - parity], self._sampled_host_ints, L["tokens"]
+            self._head(resid, pending, ctx, b, None, L,
+                       also=(lambda c0, n: other[t0 + c0:t0 + c0 + n], lambda c0, n: host.at(parity * self.seqs_cap + c0)))
         finally:
             self._dev = self.step_dev
-        self.sampled_host[parity, :b].copy_(self.sampled[:b], non_blocking=True)
-        # the picks as the next decode step's tokens, should it be fed from the device
-        self._devs[1 - parity][L["tokens"]:L["tokens"] + b].copy_(self.sampled[:b])
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def check_kernels(self) -> None:

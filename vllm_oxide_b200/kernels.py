@@ -878,11 +878,55 @@ def pick_tiles(vocab: int) -> int:
     return -(-int(vocab) // 128)
 
 
+class HostInts:
+    """A page-locked host buffer of int32 that kernels write to directly (`also` of the pick
+    functions): `tensor` is the host's view, `address` what the device reaches it under."""
+
+    def __init__(self, shape):
+        self.tensor = torch.zeros(shape, dtype=torch.int32, pin_memory=True)
+        f = _fn("sampling", "vob_host_device_pointer", [_P, _P])
+        dev = ctypes.c_void_p()
+        rc = f(_P(self.tensor.data_ptr()), ctypes.byref(dev))
+        if rc != 0 or not dev.value:
+            raise KernelError(f"the device cannot address page-locked host memory (error {rc})")
+        self.address = int(dev.value)
+
+    def at(self, element: int) -> "_Address":
+        if not 0 <= element <= self.tensor.numel():
+            raise ShapeError("HostInts", f"element {element} lies outside {self.tensor.numel()} elements")
+        return _Address(self.address + 4 * element, self.tensor.numel() - element)
+
+
+class _Address:
+    """A raw device-reachable address with the int32 elements that follow it."""
+
+    def __init__(self, address: int, elements: int):
+        self.address, self.elements = address, elements
+
+
+def _also_pointers(op: str, also, rows: int):
+    """Up to two further places the picked tokens go to: int32 device tensors or addresses of a `HostInts`."""
+    if len(also) > 2:
+        raise ShapeError(op, f"at most two further destinations, got {len(also)}")
+    ptrs = []
+    for a in also:
+        if isinstance(a, _Address):
+            if a.elements < rows:
+                raise ShapeError(op, f"a further destination has room for {a.elements} of {rows} tokens")
+            ptrs.append(_P(a.address))
+        else:
+            _cuda(op, a)
+            _int32_vec(a, rows, op, "a further destination")
+            ptrs.append(_ptr(a))
+    return ptrs + [_P(0)] * (2 - len(ptrs))
+
+
 @_timed
 def pick_final(part_val: torch.Tensor, part_idx: torch.Tensor, rows: int, vocab: int, nan_flags: torch.Tensor,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, also=()) -> None:
     """The pick's second pass alone: out[r] = index of the best of row r's (value, index) pairs
-    (part_val / part_idx [>= rows, pairs per row]); -1 for a row whose NaN flag is up (the flag is cleared)."""
+    (part_val / part_idx [>= rows, pairs per row]); -1 for a row whose NaN flag is up (the flag is cleared).
+    `also`: up to two further places the same tokens are written to."""
     op = "pick_final"
     _cuda(op, part_val, part_idx, nan_flags, out)
     if (part_val.dtype != torch.float32 or part_idx.dtype != torch.int32 or part_val.dim() != 2 or part_val.shape != part_idx.shape
@@ -891,8 +935,9 @@ def pick_final(part_val: torch.Tensor, part_idx: torch.Tensor, rows: int, vocab:
                              f"and {list(part_idx.shape)}")
     _int32_vec(out, rows, op, "out")
     _int32_vec(nan_flags, rows, op, "nan_flags")
-    f = _fn("sampling", "vob_pick_final", [_P, _P, _I, _I, _I, _P, _P, _P])
-    _check(f(_ptr(part_val), _ptr(part_idx), rows, part_val.shape[1], int(vocab), _ptr(nan_flags), _ptr(out), _stream()), op)
+    a, b = _also_pointers(op, also, rows)
+    f = _fn("sampling", "vob_pick_final_to", [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P])
+    _check(f(_ptr(part_val), _ptr(part_idx), rows, part_val.shape[1], int(vocab), _ptr(nan_flags), _ptr(out), a, b, _stream()), op)
 
 
 def pick_splits(vocab: int) -> int:
@@ -903,11 +948,12 @@ def pick_splits(vocab: int) -> int:
 @_timed
 def pick_tokens(logits: torch.Tensor, out: torch.Tensor, nan_flags: torch.Tensor, scratch_val: torch.Tensor,
                 scratch_idx: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-                seeds: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> None:
+                seeds: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None, also=()) -> None:
     """One token per row of float32 logits [R, V]: greedy where temperature is 0 or absent,
     Gumbel-max sampling elsewhere. seeds int32 [R, 2] (low, high word), steps int32 [R]
     (index of the generated token), nan_flags int32 [R] raised for rows that hold a NaN.
-    scratch_val float32 and scratch_idx int32 need R * pick_splits(V) elements each."""
+    scratch_val float32 and scratch_idx int32 need R * pick_splits(V) elements each.
+    `also`: up to two further places the same tokens are written to."""
     op = "pick_tokens"
     _cuda(op, logits, out, nan_flags, scratch_val, scratch_idx, temperature, seeds, steps)
     _rows_2d(logits, op, "logits")
@@ -929,6 +975,7 @@ def pick_tokens(logits: torch.Tensor, out: torch.Tensor, nan_flags: torch.Tensor
         if seeds.dtype != torch.int32 or seeds.numel() < 2 * R or not seeds.is_contiguous():
             raise ShapeError(op, f"seeds must be int32 [{R}, 2]")
         _int32_vec(steps, R, op, "steps")
-    f = _fn("sampling", "vob_pick_tokens", [_P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P])
+    a, b = _also_pointers(op, also, R)
+    f = _fn("sampling", "vob_pick_tokens_to", [_P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P])
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(seeds), _ptr(steps), splits,
-             _ptr(scratch_val), _ptr(scratch_idx), _ptr(nan_flags), _ptr(out), _stream()), op, launches=2)
+             _ptr(scratch_val), _ptr(scratch_idx), _ptr(nan_flags), _ptr(out), a, b, _stream()), op, launches=2)

@@ -61,11 +61,12 @@ class LMHead:
         return out
 
     def pick_folded(self, st: FoldedState, eps: float, rows: int, temperature, seeds, steps, part_val: torch.Tensor,
-                    part_idx: torch.Tensor, nan_flags: torch.Tensor, out: torch.Tensor) -> None:
+                    part_idx: torch.Tensor, nan_flags: torch.Tensor, out: torch.Tensor, also=()) -> None:
         """Tokens of the first `rows` rows straight from the folded residual, without the logits ever
         going to memory: the head product's epilogue leaves the best (value, index) pair of every
         128 logits, a second small kernel reduces a row's pairs. Same picks as `forward_folded`
-        followed by `kernels.pick_tokens` (the same values, compared by the same rule)."""
+        followed by `kernels.pick_tokens` (the same values, compared by the same rule). `also`: further
+        places the tokens are written to (see `kernels.pick_final`)."""
         kernels.gemm_fused(st.xn[:rows], self.weight, None, kernels.EPI_PICK, self.vocab, ssq_in=st.ssq, eps=eps,
                            pick=(temperature, seeds, steps, part_val, part_idx, nan_flags))
-        kernels.pick_final(part_val, part_idx, rows, self.vocab, nan_flags, out)
+        kernels.pick_final(part_val, part_idx, rows, self.vocab, nan_flags, out, also)

@@ -143,8 +143,12 @@ class ModelRunner:
         # two pinned buffers: a step's picks may still be unread when the next step writes its own.
         # The pick kernel of a decode step writes them there itself (page-locked host memory that the
         # device can address), so no copy follows the step's last kernel.
-        self._sampled_host_ints = kernels.HostInts((2, self.seqs_cap))
-        self.sampled_host = self._sampled_host_ints.tensor
+        try:
+            self._sampled_host_ints = kernels.HostInts((2, self.seqs_cap))
+            self.sampled_host = self._sampled_host_ints.tensor
+        except KernelError:                     # a device that cannot address host memory: a copy behind every step
+            self._sampled_host_ints = None
+            self.sampled_host = torch.zeros((2, self.seqs_cap), dtype=torch.int32, pin_memory=True)
         self.sampled_host_np = self.sampled_host.numpy()
         self.steps_run = 0
         self.last_upload_bytes = 0
@@ -546,10 +550,14 @@ class ModelRunner:
             # tokens should it be fed from the device, to the token rows of the other metadata buffer:
             # written by the pick kernel itself (two copies behind it cost a replayed step 14 us)
             other, host, t0 = self._devs[1 - parity], self._sampled_host_ints, L["tokens"]
-            self._head(resid, pending, ctx, b, None, L,
-                       also=(lambda c0, n: other[t0 + c0:t0 + c0 + n], lambda c0, n: host.at(parity * self.seqs_cap + c0)))
+            also = [lambda c0, n: other[t0 + c0:t0 + c0 + n]]
+            if host is not None:
+                also.append(lambda c0, n: host.at(parity * self.seqs_cap + c0))
+            self._head(resid, pending, ctx, b, None, L, also=also)
         finally:
             self._dev = self.step_dev
+        if host is None:
+            self.sampled_host[parity, :b].copy_(self.sampled[:b], non_blocking=True)
 
     # ------------------------------------------------------------------ bookkeeping helpers
     def check_kernels(self) -> None:

@@ -167,8 +167,10 @@ def make_engine(sz, layers, max_seqs, tokens_per_request, context, graphs=True):
     from vllm_oxide_b200.weights import random_tensors
     cfg = make_config(sz, layers)
     pages_per_req = -(-(tokens_per_request + 16) // 16)
-    engine = EngineConfig(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
-                          num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=graphs, **ENGINE_OVERRIDES)
+    fields = dict(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
+                  num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=graphs)
+    fields.update(ENGINE_OVERRIDES)         # --engine FIELD=VALUE replaces what the benchmark would set
+    engine = EngineConfig(**fields)
     tensors = random_tensors(models.llama_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
     runner = ModelRunner(cfg, tensors, engine)
     del tensors

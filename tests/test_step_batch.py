@@ -117,7 +117,14 @@ def test_how_decode_attention_shares_a_request_over_blocks():
                 for long_context in (False, True):
                     splits, wide = decode_split_rule(seqs, kv, sms, long_context)
                     assert 1 <= splits <= (64 if wide else 8) and (long_context or not wide)
-    assert decode_split_rule(8, 8, 148, False) == (5, False)          # the benchmark's decode step
+    assert decode_split_rule(8, 8, 148, False) == (6, False)          # the benchmark's decode step
     assert decode_split_rule(64, 8, 148, False) == (1, False)
     assert decode_split_rule(1, 8, 148, True) == (55, True)           # one long request
     assert decode_split_rule(8, 8, 148, True) == (6, True)
+
+
+def test_batch_size_classes_of_decode_steps():
+    from vllm_oxide_b200.engine.runner import decode_bucket
+    assert [decode_bucket(n) for n in range(1, 18)] == [1, 2, 3, 4, 6, 6, 8, 8, 12, 12, 12, 12, 16, 16, 16, 16, 24]
+    assert [decode_bucket(n) for n in (24, 25, 32, 33, 48, 49, 64, 65, 96, 97, 150)] == [24, 32, 32, 48, 48, 64, 64, 96, 96, 128, 192]
+    assert all(decode_bucket(n) >= n for n in range(1, 2000))

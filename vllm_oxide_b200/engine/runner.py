@@ -62,6 +62,18 @@ def _require_cuda(device: str) -> None:
         raise KernelError(f"device {device!r}: this engine runs on a CUDA device only")
 
 
+def decode_bucket(n: int) -> int:
+    """The batch-size class a decode step of `n` requests is recorded under: 1, 2, 3, 4, 6, 8, 12, 16,
+    24, 32, ... (powers of two and the sizes half way between: a step of 9 requests padded to 16 would
+    share its keys over blocks as 16 requests do, 0.90 instead of 0.87 ms at the benchmark's sizes)."""
+    b = 1
+    while b < n:
+        if b >= 2 and b + b // 2 >= n:
+            return b + b // 2
+        b *= 2
+    return b
+
+
 class ModelRunner:
     """Owns the model's parts, the cache and the step's device buffers; `step` is the only way
     tokens go through the model (generation, the scheduler's loop and trace replay all use it)."""
@@ -447,10 +459,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _bucket(self, n: int) -> int:
-        b = 1
-        while b < n:
-            b *= 2
-        return min(b, self.decode_cap)
+        return min(decode_bucket(n), self.decode_cap)
 
     def decode_step_graph(self, scheduler, plan, feed_from_device: bool = False, read: bool = True, parity: int = 0,
                           arrays=None):

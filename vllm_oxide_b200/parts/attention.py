@@ -39,7 +39,14 @@ def decode_split_rule(num_seqs: int, kv_heads: int, num_sms: int, long_context: 
     blocks = max(1, num_seqs * kv_heads)
     if long_context and 3 * num_sms // blocks >= 4:
         return min(64, 3 * num_sms // blocks), True
-    return max(1, min(8, -(-2 * num_sms // blocks))), False
+    # At least twice the SMs in blocks. One more block per request and kv head where the grid then
+    # still stays within 2.6 blocks per SM and the cluster within 6 blocks (measured inside a decode
+    # step, where the neighbouring kernels' blocks hold slots too: 8 requests on 8 kv heads 0.796 ms
+    # a step with 6 blocks each, 0.807 with 5; but 6 requests with 8 instead of 7, or 9 with 6 instead
+    # of 5, lose 5-9 %: clusters that large, or a grid that full, no longer start all at once).
+    lo = -(-2 * num_sms // blocks)
+    hi = (13 * num_sms // 5) // blocks
+    return max(1, min(8, hi if lo < hi <= 6 else lo)), False
 
 
 class Attention(Mixer):

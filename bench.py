@@ -333,7 +333,7 @@ def serve_measure(llm, cfg, layers, n_requests, len_min, len_max, gen_len, peaks
     ideal = [0.0]
     upload = runner.upload
 
-    def logging_upload(arrays):
+    def logging_upload(arrays, *args, **kwargs):
         flops = lin_flops * arrays.rows + head_flops * arrays.logit_count
         keys = 0
         for rid, n in zip(arrays.ids, arrays.new_counts):
@@ -342,7 +342,7 @@ def serve_measure(llm, cfg, layers, n_requests, len_min, len_max, gen_len, peaks
             keys += ctx + n
         nbytes = runner.step_read_bytes(keys)
         ideal[0] += max(flops / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9))
-        return upload(arrays)
+        return upload(arrays, *args, **kwargs)
     runner.upload = logging_upload
     steps0, pre0 = runner.steps_run, llm.stats.get("preemptions", 0)
     t0 = time.perf_counter()

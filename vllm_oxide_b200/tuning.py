@@ -16,8 +16,10 @@ class Tuning:
     # 22 % faster. At most 64 (what the fused kernels take).
     few_rows: int = 32
     # From so many rows the gate/up product runs on the two-SM kernel with the SwiGLU epilogue instead
-    # of the library product plus the activation kernel (measured at 2,048 x 16,384 x 2,048).
-    pair_gemm_from_rows: int = 1024
+    # of the library product plus the activation kernel. Measured on whole prefill steps at hidden
+    # 2,048 / intermediate 8,192: 512 / 640 / 768 / 896 rows take 1.47 / 1.70 / 1.78 / 2.15 ms with it
+    # and 1.53 / 1.80 / 1.89 / 2.25 ms without; at 384 rows it loses (1.33 against 1.26 ms).
+    pair_gemm_from_rows: int = 512
     # A step in which some request has more keys than this counts as one of long contexts: decode
     # attention then shares a request's keys over up to 64 blocks that merge through global memory
     # instead of a cluster of 8 (measured with 8 kv heads of 64 and of 128: the cluster wins below).

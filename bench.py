@@ -647,6 +647,8 @@ def main():
     ap.add_argument("--serve-min", type=int, default=128)
     ap.add_argument("--serve-max", type=int, default=4096)
     ap.add_argument("--timeline", action="store_true", help="per-kernel times of one decode step (VOB_TIMELINE=1 build)")
+    ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
+                    help="set a field of vllm_oxide_b200.tuning.TUNING (experiments)")
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
                     help="an experiment: steps of up to R rows (at most 64) take the fused few-row kernels instead of the "
                          "engine's own switch-over point")
@@ -676,6 +678,13 @@ def main():
         return 2
 
     import torch
+    for kv in a.tuning:
+        from vllm_oxide_b200.tuning import TUNING
+        k, _, v = kv.partition("=")
+        if not hasattr(TUNING, k):
+            print(f"bench.py: TUNING has no field {k!r}")
+            return 2
+        setattr(TUNING, k, int(v))
     if a.fold_rows is not None:
         from vllm_oxide_b200.tuning import TUNING
         TUNING.few_rows = a.fold_rows

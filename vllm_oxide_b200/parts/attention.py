@@ -31,7 +31,7 @@ def decode_split_rule(num_seqs: int, kv_heads: int, num_sms: int, long_context: 
     blocks per request and kv head at three blocks per SM, which is what fits with the three-stage
     ring), up to 64 blocks merge through global memory instead (`wide`), and a request uses as many
     of them as its length is worth. Measured with 8 kv heads of 64: one request of 131,072 keys
-    175 us in clusters of 8, 51 us wide; 8 requests of 32,768 keys 107 / 94 us; below some 6,000
+    175 us in clusters of 8, 51 us wide; 8 requests of 32,768 keys 107 / 94 us; below some 5,000
     keys the cluster is faster. (Merging in clusters of 8 first and only the clusters' sums through
     global memory was built and measured for one request: a decode step at batch 1 took 0.824
     instead of 0.865 ms with 8,192 keys, but 1.019 instead of 0.998 ms with 32,768, where 48 longer

@@ -22,8 +22,11 @@ class Tuning:
     pair_gemm_from_rows: int = 512
     # A step in which some request has more keys than this counts as one of long contexts: decode
     # attention then shares a request's keys over up to 64 blocks that merge through global memory
-    # instead of a cluster of 8 (measured with 8 kv heads of 64 and of 128: the cluster wins below).
-    long_context_keys: int = 6144
+    # instead of a cluster of 8. Measured on whole decode steps with 8 kv heads of 64: at 4,096 keys
+    # the cluster wins at batch 1, 2 and 4 (0.764 / 0.791 / 0.825 against 0.767 / 0.808 / 0.854 ms), at
+    # 6,000 keys the wider grid wins at batch 1 and 2 (0.794 / 0.837 against 0.819 / 0.857 ms) and
+    # ties at batch 4.
+    long_context_keys: int = 5120
 
 
 TUNING = Tuning()
